@@ -1,0 +1,163 @@
+/* C ABI of libttt_mlp_b200.so: the TTT-MLP forward / backward operator for NVIDIA B200
+ * (sm_100a).  Plain pointers and sizes only; every pointer is a DEVICE pointer to a
+ * contiguous array unless stated otherwise; `stream` is a cudaStream_t passed as void*.
+ *
+ * The two operator entry points stand behind the reference's PyTorch extension
+ * `test_time_training` (test_time_training.cpp:24-104) and replace its two host launchers
+ *   ttt_forward   kernels/ttt/ttt.cu:594-721
+ *   ttt_backward  kernels/ttt_backward/ttt.cu:1451-1917
+ * one struct field per positional tensor of those functions, in the same order.
+ *
+ * Fixed sizes (reference: kernels/ttt/ttt.cu:612-613, 621-630): mini-batch CS = 64 tokens,
+ * head dimension F = 64, MLP hidden width 256.  NC = sequence length / 64.
+ *
+ * Return codes: 0 ok; 1 bad arguments (nothing launched); 2 CUDA launch / runtime error;
+ * 3 a device-side bounded wait ran out (the kernel exited cleanly, results are invalid).
+ * ttt_b200_last_error() returns the calling thread's last message.
+ *
+ * Calls are stream-ordered and do not synchronise unless TTT_B200_FLAG_SYNC is set (the
+ * reference blocks on the stream and the device after every call, kernels/ttt/ttt.cu:714-715).
+ * A code-3 condition of an asynchronous call is reported by the next call on any stream, or by
+ * ttt_b200_take_status() after the caller has synchronised.
+ */
+#ifndef TTT_MLP_B200_H_
+#define TTT_MLP_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  TTT_B200_OK = 0,
+  TTT_B200_ERR_BAD_ARGS = 1,
+  TTT_B200_ERR_LAUNCH = 2,
+  TTT_B200_ERR_TIMEOUT = 3
+};
+
+enum {
+  TTT_B200_FLAG_SYNC = 1u /* synchronise the stream and report device-side status before returning */
+};
+
+/* Arguments of the forward.  Replaces ttt_forward(XQ, XK, XV, last_eta, ttt_norm_weight,
+ * ttt_norm_bias, W1, b1, W2, b2, W1_checkpoints, b1_checkpoints, W2_checkpoints,
+ * b2_checkpoints, Out, checkpoint_group_size)  -- kernels/ttt/ttt.cu:594-611.
+ * bf16: XQ XK XV last_eta Out.  fp32: everything else. */
+typedef struct ttt_b200_fwd_args {
+  const void* XQ;                /* bf16 [B,H,NC,64,64] */
+  const void* XK;                /* bf16 [B,H,NC,64,64] */
+  const void* XV;                /* bf16 [B,H,NC,64,64] */
+  const void* last_eta;          /* bf16 [B,H,NC,64] */
+  const float* ttt_norm_weight;  /* [H,64] */
+  const float* ttt_norm_bias;    /* [H,64] */
+  const float* W1;               /* [B,H,64,256] */
+  const float* b1;               /* [B,H,256] */
+  const float* W2;               /* [B,H,256,64] */
+  const float* b2;               /* [B,H,64] */
+  float* W1_checkpoints;         /* [B,H,n,64,256], n = ceil(NC / checkpoint_group_size) */
+  float* b1_checkpoints;         /* [B,H,n,256] */
+  float* W2_checkpoints;         /* [B,H,n,256,64] */
+  float* b2_checkpoints;         /* [B,H,n,64] */
+  void* Out;                     /* bf16 [B,H,NC,64,64] */
+  int32_t B, H, NC;
+  int32_t checkpoint_group_size;
+  int32_t num_checkpoints;       /* size(2) of the checkpoint tensors; must equal n */
+  uint32_t flags;
+  /* Optional (may be NULL): state after the last mini-batch, which the reference computes
+   * but never stores (kernels/ttt/ttt.cu:276-584).  Shapes as W1/b1/W2/b2. */
+  float* W1_final;
+  float* b1_final;
+  float* W2_final;
+  float* b2_final;
+} ttt_b200_fwd_args;
+
+/* Arguments of the backward.  Replaces ttt_backward(...43 positional arguments...)
+ * -- kernels/ttt_backward/ttt.cu:1451-1495; same order.  The sixteen `*_group` tensors are
+ * caller-provided scratch of the reference's shapes; this implementation uses a subset of
+ * them, in its own layout (their contents after the call are unspecified).
+ * Deviations from the reference, all towards the documented usage:
+ *   - grad_L_XQ / XK / XV / last_eta are OVERWRITTEN (the reference accumulates into them and
+ *     requires zero-filled buffers: kernels/ttt_backward/matching.py:412-415);
+ *   - `Out` is never written (the reference adds a debug term into it,
+ *     kernels/ttt_backward/ttt.cu:1313). */
+typedef struct ttt_b200_bwd_args {
+  const void* XQ;                    /* bf16 [B,H,NC,64,64] */
+  const void* XK;
+  const void* XV;
+  const void* last_eta;              /* bf16 [B,H,NC,64(,1)] */
+  const float* ttt_norm_weight;      /* [H,64] */
+  const float* ttt_norm_bias;        /* [H,64] */
+  const float* W1_checkpoints;       /* [B,H,n,64,256] */
+  const float* b1_checkpoints;       /* [B,H,n,256] */
+  const float* W2_checkpoints;       /* [B,H,n,256,64] */
+  const float* b2_checkpoints;       /* [B,H,n,64] */
+  const void* Out;                   /* bf16, unused */
+  /* scratch, one slot per mini-batch of a checkpoint group (cgs slots per (b,h)) */
+  float* W1_init_group;              /* fp32 [B,H,cgs,64,256] */
+  float* b1_init_group;              /* fp32 [B,H,cgs,256] */
+  float* W2_init_group;              /* fp32 [B,H,cgs,256,64] */
+  float* b2_init_group;              /* fp32 [B,H,cgs,64] */
+  void* x_hat_ln_group;              /* bf16 [B,H,cgs,64,64] */
+  float* std_ln_group;               /* fp32 [B,H,cgs,64] */
+  void* X2_group;                    /* bf16 [B,H,cgs,64,256] */
+  void* Z1_group;                    /* bf16 [B,H,cgs,64,256] */
+  void* Z1_bar_group;                /* bf16 [B,H,cgs,64,256] */
+  void* X2_bar_group;                /* bf16 [B,H,cgs,64,256] */
+  void* grad_l_wrt_Z2_group;         /* bf16 [B,H,cgs,64,64] */
+  void* grad_l_wrt_Z1_group;         /* bf16 [B,H,cgs,64,256] */
+  void* x_hat_fused_group;           /* bf16 [B,H,cgs,64,64] */
+  void* grad_x_hat_fused_group;      /* bf16 [B,H,cgs,64,64] */
+  void* grad_output_fused_group;     /* bf16 [B,H,cgs,64,64] */
+  float* std_fused_group;            /* fp32 [B,H,cgs,64] */
+  /* upstream gradients */
+  const float* grad_L_W1_last;       /* [B,H,64,256] */
+  const float* grad_L_b1_last;       /* [B,H,256] */
+  const float* grad_L_W2_last;       /* [B,H,256,64] */
+  const float* grad_L_b2_last;       /* [B,H,64] */
+  const void* grad_L_XQW_mini_batch; /* bf16 [B,H,NC,64,64] */
+  /* outputs */
+  float* grad_L_ttt_norm_weight;     /* [B,H,64]: one row per batch element, caller sums dim 0 */
+  float* grad_L_ttt_norm_bias;       /* [B,H,64] */
+  float* grad_L_W1_init;             /* [B,H,64,256] */
+  float* grad_L_b1_init;             /* [B,H,256] */
+  float* grad_L_W2_init;             /* [B,H,256,64] */
+  float* grad_L_b2_init;             /* [B,H,64] */
+  void* grad_L_last_eta;             /* bf16 [B,H,NC,64] */
+  void* grad_L_XQ;                   /* bf16 [B,H,NC,64,64] */
+  void* grad_L_XK;
+  void* grad_L_XV;
+  int32_t B, H, NC;
+  int32_t checkpoint_group_size;
+  int32_t num_checkpoints;
+  uint32_t flags;
+} ttt_b200_bwd_args;
+
+/* Forward: replaces kernels/ttt/ttt.cu:594-721 (validation, launch) and the device kernel
+ * fwd_ttt_mlp_ker (kernels/ttt/ttt.cu:85-586). */
+int ttt_b200_forward(const ttt_b200_fwd_args* args, void* stream);
+
+/* Backward: replaces kernels/ttt_backward/ttt.cu:1451-1917 and bwd_ttt_mlp_ker (:179-1443). */
+int ttt_b200_backward(const ttt_b200_bwd_args* args, void* stream);
+
+/* Last error text of the calling thread ("" if none). */
+const char* ttt_b200_last_error(void);
+
+/* Take (read and clear) the device-side status word: 0, or TTT_B200_ERR_TIMEOUT if a kernel of
+ * this process gave up on a bounded wait since the last take.  Call after synchronising. */
+int ttt_b200_take_status(void);
+
+/* Library / ABI version (major * 1000 + minor). */
+int ttt_b200_version(void);
+
+/* Diagnostics (no counterpart in the reference): one CTA computes
+ * D[M,N] = (+/-)A[M,K] * B[N,K]^T, `repeat` times accumulated, through the same shared-memory
+ * descriptors, instruction descriptors and tensor-memory mapping as the operator kernels.
+ * A, B, D are fp32 device arrays (operands are rounded to bf16).  Synchronises. */
+int ttt_b200_umma_selftest(const float* A, const float* B, float* D, int M, int N, int K, int a_mn, int b_mn,
+                           int neg_a, int repeat, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TTT_MLP_B200_H_ */

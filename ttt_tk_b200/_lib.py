@@ -1,0 +1,71 @@
+"""ctypes binding of libttt_mlp_b200.so (declarations: include/ttt_mlp_b200.h).
+
+There is no fallback: if the library is missing the import fails.
+"""
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "lib", "libttt_mlp_b200.so")
+
+c_void_p, c_int32, c_uint32 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_uint32
+
+FWD_FIELDS = ["XQ", "XK", "XV", "last_eta", "ttt_norm_weight", "ttt_norm_bias", "W1", "b1", "W2", "b2",
+              "W1_checkpoints", "b1_checkpoints", "W2_checkpoints", "b2_checkpoints", "Out"]
+FWD_TAIL = ["W1_final", "b1_final", "W2_final", "b2_final"]
+BWD_FIELDS = ["XQ", "XK", "XV", "last_eta", "ttt_norm_weight", "ttt_norm_bias",
+              "W1_checkpoints", "b1_checkpoints", "W2_checkpoints", "b2_checkpoints", "Out",
+              "W1_init_group", "b1_init_group", "W2_init_group", "b2_init_group",
+              "x_hat_ln_group", "std_ln_group", "X2_group", "Z1_group", "Z1_bar_group", "X2_bar_group",
+              "grad_l_wrt_Z2_group", "grad_l_wrt_Z1_group", "x_hat_fused_group", "grad_x_hat_fused_group",
+              "grad_output_fused_group", "std_fused_group",
+              "grad_L_W1_last", "grad_L_b1_last", "grad_L_W2_last", "grad_L_b2_last", "grad_L_XQW_mini_batch",
+              "grad_L_ttt_norm_weight", "grad_L_ttt_norm_bias", "grad_L_W1_init", "grad_L_b1_init",
+              "grad_L_W2_init", "grad_L_b2_init", "grad_L_last_eta", "grad_L_XQ", "grad_L_XK", "grad_L_XV"]
+_DIMS = [("B", c_int32), ("H", c_int32), ("NC", c_int32), ("checkpoint_group_size", c_int32),
+         ("num_checkpoints", c_int32), ("flags", c_uint32)]
+
+
+class FwdArgs(ctypes.Structure):
+    _fields_ = [(n, c_void_p) for n in FWD_FIELDS] + _DIMS + [(n, c_void_p) for n in FWD_TAIL]
+
+
+class BwdArgs(ctypes.Structure):
+    _fields_ = [(n, c_void_p) for n in BWD_FIELDS] + _DIMS
+
+
+EXPORTS = ["ttt_b200_forward", "ttt_b200_backward", "ttt_b200_last_error", "ttt_b200_take_status",
+           "ttt_b200_version", "ttt_b200_umma_selftest"]
+
+FLAG_SYNC = 1
+
+
+def load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m ttt_tk_b200.build` (needs nvcc); "
+            "this package has no CPU or PyTorch fallback")
+    lib = ctypes.CDLL(LIB_PATH)
+    lib.ttt_b200_forward.argtypes = [ctypes.POINTER(FwdArgs), c_void_p]
+    lib.ttt_b200_forward.restype = ctypes.c_int
+    lib.ttt_b200_backward.argtypes = [ctypes.POINTER(BwdArgs), c_void_p]
+    lib.ttt_b200_backward.restype = ctypes.c_int
+    lib.ttt_b200_last_error.argtypes = []
+    lib.ttt_b200_last_error.restype = ctypes.c_char_p
+    lib.ttt_b200_take_status.argtypes = []
+    lib.ttt_b200_take_status.restype = ctypes.c_int
+    lib.ttt_b200_version.argtypes = []
+    lib.ttt_b200_version.restype = ctypes.c_int
+    lib.ttt_b200_umma_selftest.argtypes = [c_void_p, c_void_p, c_void_p] + [ctypes.c_int] * 7 + [c_void_p]
+    lib.ttt_b200_umma_selftest.restype = ctypes.c_int
+    return lib
+
+
+_LIB = None
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        _LIB = load()
+    return _LIB

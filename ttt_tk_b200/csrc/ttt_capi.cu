@@ -1,0 +1,192 @@
+// Host side of the C ABI: argument validation, tensor-map construction, status word,
+// error text.  Replaces the host launchers of the reference
+// (kernels/ttt/ttt.cu:594-721, kernels/ttt_backward/ttt.cu:1451-1917): same checks, made on
+// every call (the reference's backward checks only on the first call of the process,
+// kernels/ttt_backward/ttt.cu:1507-1508), and errors are returned instead of printed
+// (kernels/ttt/ttt.cu:708-718).
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "ttt_internal.h"
+
+int ttt_launch_forward(const ttt_b200_fwd_args* a, cudaStream_t stream, uint32_t* status, uint64_t limit_ns);
+int ttt_launch_backward(const ttt_b200_bwd_args* a, cudaStream_t stream, uint32_t* status, uint64_t limit_ns);
+
+namespace {
+
+thread_local std::string g_last_error;
+
+std::mutex g_mu;
+uint32_t* g_status_host = nullptr;   // pinned, device-visible
+uint32_t* g_status_dev = nullptr;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+// Device-side waits give up after this long (nanoseconds).  A healthy launch never waits
+// more than microseconds; the limit only decides how fast a lost signal is reported.
+uint64_t wait_limit_ns() {
+  static uint64_t v = [] {
+    const char* e = std::getenv("TTT_B200_WAIT_LIMIT_MS");
+    long ms = e ? std::atol(e) : 2000;
+    if (ms < 1) ms = 1;
+    return static_cast<uint64_t>(ms) * 1000000ull;
+  }();
+  return v;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+int ttt_set_error(int code, const char* msg) {
+  g_last_error = msg ? msg : "";
+  return code;
+}
+
+int ttt_status_word(uint32_t** dev_ptr) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!g_status_host) {
+    cudaError_t e = cudaHostAlloc(reinterpret_cast<void**>(&g_status_host), sizeof(uint32_t),
+                                  cudaHostAllocMapped | cudaHostAllocPortable);
+    if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
+    *g_status_host = 0;
+    e = cudaHostGetDevicePointer(reinterpret_cast<void**>(&g_status_dev), g_status_host, 0);
+    if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
+  }
+  *dev_ptr = g_status_dev;
+  return TTT_B200_OK;
+}
+
+uint32_t ttt_take_status() {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!g_status_host) return 0;
+  volatile uint32_t* w = g_status_host;
+  const uint32_t v = *w;
+  *w = 0;
+  return v;
+}
+
+int ttt_check_status(cudaStream_t stream) {
+  cudaError_t e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
+  if (ttt_take_status() != 0)
+    return ttt_set_error(TTT_B200_ERR_TIMEOUT, "a device-side bounded wait ran out; results are invalid");
+  return TTT_B200_OK;
+}
+
+int ttt_make_tile_map(CUtensorMap* map, const void* base, uint64_t rows) {
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!g_encode) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult qres;
+      cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+      if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn)
+        return ttt_set_error(TTT_B200_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from the driver");
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+  }
+  const cuuint64_t dims[2] = {64, rows};
+  const cuuint64_t strides[1] = {128};           // bytes between rows
+  const cuuint32_t box[2] = {64, 64};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[96];
+    std::snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+    return ttt_set_error(TTT_B200_ERR_LAUNCH, buf);
+  }
+  return TTT_B200_OK;
+}
+
+namespace {
+
+#define TTT_REQUIRE(cond, msg) \
+  do {                         \
+    if (!(cond)) return ttt_set_error(TTT_B200_ERR_BAD_ARGS, msg); \
+  } while (0)
+
+int check_dims(int B, int H, int NC, int cgs, int nck) {
+  TTT_REQUIRE(B >= 1 && H >= 1, "B and H must be >= 1");
+  TTT_REQUIRE(NC >= 1, "NC (sequence length / 64) must be >= 1");
+  TTT_REQUIRE(cgs >= 1, "checkpoint_group_size must be >= 1");
+  TTT_REQUIRE(nck == (NC + cgs - 1) / cgs, "checkpoint tensors must hold ceil(NC / checkpoint_group_size) states");
+  TTT_REQUIRE(static_cast<uint64_t>(B) * H * NC * 64 < (1ull << 31), "B*H*NC*64 must be below 2^31");
+  return TTT_B200_OK;
+}
+
+int pre_launch(uint32_t** status) {
+  if (int rc = ttt_status_word(status)) return rc;
+  if (ttt_take_status() != 0)
+    return ttt_set_error(TTT_B200_ERR_TIMEOUT,
+                         "an earlier launch reported a device-side wait that ran out; its results are invalid");
+  return TTT_B200_OK;
+}
+
+}  // namespace
+
+extern "C" int ttt_b200_forward(const ttt_b200_fwd_args* a, void* stream_) {
+  TTT_REQUIRE(a != nullptr, "args is NULL");
+  if (int rc = check_dims(a->B, a->H, a->NC, a->checkpoint_group_size, a->num_checkpoints)) return rc;
+  const void* ptrs[] = {a->XQ, a->XK, a->XV, a->last_eta, a->ttt_norm_weight, a->ttt_norm_bias, a->W1, a->b1,
+                        a->W2, a->b2, a->W1_checkpoints, a->b1_checkpoints, a->W2_checkpoints, a->b2_checkpoints,
+                        a->Out};
+  for (const void* q : ptrs) {
+    TTT_REQUIRE(q != nullptr, "a required tensor pointer is NULL");
+    TTT_REQUIRE(aligned16(q), "tensor pointers must be 16-byte aligned");
+  }
+  const int nfinal = (a->W1_final != nullptr) + (a->b1_final != nullptr) + (a->W2_final != nullptr) +
+                     (a->b2_final != nullptr);
+  TTT_REQUIRE(nfinal == 0 || nfinal == 4, "W1/b1/W2/b2_final must be given together or not at all");
+  if (nfinal == 4)
+    TTT_REQUIRE(aligned16(a->W1_final) && aligned16(a->b1_final) && aligned16(a->W2_final) && aligned16(a->b2_final),
+                "tensor pointers must be 16-byte aligned");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  uint32_t* status = nullptr;
+  if (int rc = pre_launch(&status)) return rc;
+  if (int rc = ttt_launch_forward(a, stream, status, wait_limit_ns())) return rc;
+  if (a->flags & TTT_B200_FLAG_SYNC) return ttt_check_status(stream);
+  return TTT_B200_OK;
+}
+
+extern "C" int ttt_b200_backward(const ttt_b200_bwd_args* a, void* stream_) {
+  TTT_REQUIRE(a != nullptr, "args is NULL");
+  if (int rc = check_dims(a->B, a->H, a->NC, a->checkpoint_group_size, a->num_checkpoints)) return rc;
+  const void* ptrs[] = {a->XQ, a->XK, a->XV, a->last_eta, a->ttt_norm_weight, a->ttt_norm_bias,
+                        a->W1_checkpoints, a->b1_checkpoints, a->W2_checkpoints, a->b2_checkpoints,
+                        a->W1_init_group, a->b1_init_group, a->W2_init_group, a->b2_init_group,
+                        a->x_hat_ln_group, a->std_ln_group, a->X2_group, a->Z1_group, a->Z1_bar_group,
+                        a->X2_bar_group, a->grad_l_wrt_Z2_group, a->grad_l_wrt_Z1_group, a->x_hat_fused_group,
+                        a->grad_x_hat_fused_group, a->grad_output_fused_group, a->std_fused_group,
+                        a->grad_L_W1_last, a->grad_L_b1_last, a->grad_L_W2_last, a->grad_L_b2_last,
+                        a->grad_L_XQW_mini_batch, a->grad_L_ttt_norm_weight, a->grad_L_ttt_norm_bias,
+                        a->grad_L_W1_init, a->grad_L_b1_init, a->grad_L_W2_init, a->grad_L_b2_init,
+                        a->grad_L_last_eta, a->grad_L_XQ, a->grad_L_XK, a->grad_L_XV};
+  for (const void* q : ptrs) {
+    TTT_REQUIRE(q != nullptr, "a required tensor pointer is NULL");
+    TTT_REQUIRE(aligned16(q), "tensor pointers must be 16-byte aligned");
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  uint32_t* status = nullptr;
+  if (int rc = pre_launch(&status)) return rc;
+  if (int rc = ttt_launch_backward(a, stream, status, wait_limit_ns())) return rc;
+  if (a->flags & TTT_B200_FLAG_SYNC) return ttt_check_status(stream);
+  return TTT_B200_OK;
+}
+
+extern "C" const char* ttt_b200_last_error(void) { return g_last_error.c_str(); }
+
+extern "C" int ttt_b200_take_status(void) { return ttt_take_status() ? TTT_B200_ERR_TIMEOUT : TTT_B200_OK; }
+
+extern "C" int ttt_b200_version(void) { return 1000; }

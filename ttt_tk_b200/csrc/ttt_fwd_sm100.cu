@@ -1,0 +1,595 @@
+// TTT-MLP forward for sm_100a: one persistent CTA per (batch, head) stream.
+//
+// Replaces the reference's fwd_ttt_mlp_ker (kernels/ttt/ttt.cu:85-586); the per-mini-batch
+// math is that of kernels/ttt/matching.py:30-125.
+//
+// Orientation.  Every 64x256 / 256x64 quantity is kept "hidden-major": the 256 hidden units
+// run along the M dimension of the tensor-core tile (= TMEM lanes, = one thread per hidden
+// unit in the epilogues) and the 64 tokens or 64 features along N.  The fp32 master state
+//   W1^T [256 x 64]  and  W2 [256 x 64]
+// lives in tensor memory as the accumulator of its own update MMA; a bf16 copy in shared
+// memory, refreshed once per mini-batch, feeds the other MMAs.  b1 lives in registers (one
+// hidden unit per thread), b2 in shared memory.
+//
+// Per mini-batch (K, V, Q: 64x64 bf16 tiles brought in by TMA, eta: 64 bf16):
+//   MMA1  Z1^T  = W1^T K^T                    [256 x 64 tok]   (2 x M128, N64, K64)
+//   EPI1  X2^T = gelu(Z1^T + b1), G' = gelu'(.)  -> smem bf16
+//   MMA2  Z2    = X2 W2                       [64 tok x 64]    (M64, N64, K256)
+//   LN    fused LayerNorm + L2-gradient: U2 = -eta * dl/dZ2    -> smem bf16;  b2 += colsum(U2)
+//   MMA3  R^T   = W2 U2^T                     [256 x 64 tok]
+//   EPI3  U1^T = R^T * G'  (= -eta * dl/dZ1)   -> smem bf16;  b1 += rowsum
+//   MMA4  W1^T += U1^T K ;  W2 += X2^T U2     (accumulate into the TMEM state)
+//   EPI4  bf16 copies of the new W1^T, W2     -> smem
+//   MMA5  Z1b^T = W1^T Q^T ;  EPI5  X2b^T = gelu(. + b1)
+//   MMA6  Z2b   = X2b W2   ;  OUT   Out = Q + gamma * LN(Z2b + b2) + beta  -> TMA store
+//
+// All waits are bounded (see sm100_ptx.cuh); on expiry the CTA reports through the status
+// word, drains its own copies, frees its tensor memory and returns.
+#include "sm100_ptx.cuh"
+#include "ttt_internal.h"
+
+using namespace sm100;
+
+namespace {
+
+constexpr int kStages = 3;
+constexpr int kThreads = 256;
+constexpr uint32_t TILE = 8192;    // 64 x 64 bf16
+constexpr uint32_t BIG = 32768;    // 256 x 64 bf16
+
+constexpr uint32_t OFF_K = 0;
+constexpr uint32_t OFF_V = OFF_K + kStages * TILE;
+constexpr uint32_t OFF_Q = OFF_V + kStages * TILE;
+constexpr uint32_t OFF_OUT = OFF_Q + kStages * TILE;
+constexpr uint32_t OFF_W1 = OFF_OUT + TILE;
+constexpr uint32_t OFF_W2 = OFF_W1 + BIG;
+constexpr uint32_t OFF_X2 = OFF_W2 + BIG;
+constexpr uint32_t OFF_GP = OFF_X2 + BIG;
+constexpr uint32_t OFF_U2 = OFF_GP + BIG;
+constexpr uint32_t OFF_ETA = OFF_U2 + TILE;
+constexpr uint32_t OFF_B2 = OFF_ETA + kStages * 128;
+constexpr uint32_t OFF_GAMMA = OFF_B2 + 256;
+constexpr uint32_t OFF_BETA = OFF_GAMMA + 256;
+constexpr uint32_t OFF_BAR = OFF_BETA + 256;
+constexpr uint32_t OFF_MISC = OFF_BAR + 64;
+constexpr uint32_t SMEM_USED = OFF_MISC + 64;
+constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;  // slack for the 1024-byte alignment
+static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB per-CTA shared memory of sm_100");
+
+// tensor-memory columns (fp32): two 128-lane blocks of 64 columns per 256-row matrix
+constexpr uint32_t TM_W1 = 0;
+constexpr uint32_t TM_W2 = 128;
+constexpr uint32_t TM_A = 256;
+constexpr uint32_t TM_Z = 384;
+constexpr uint32_t TM_COLS = 512;
+
+constexpr float kG0 = 0.79788456f, kG1 = 0.044715f, kG2 = 0.1070322243f;
+
+struct FwdParams {
+  const __nv_bfloat16* eta;
+  const float* gamma;
+  const float* beta;
+  const float* W1;
+  const float* b1;
+  const float* W2;
+  const float* b2;
+  float* W1c;
+  float* b1c;
+  float* W2c;
+  float* b2c;
+  float* W1f;
+  float* b1f;
+  float* W2f;
+  float* b2f;
+  int H, NC, cgs, nck;
+  uint32_t* status;
+  uint64_t wait_limit_ns;
+};
+
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void gelu_pair(float x, float& g, float& gp) {
+  const float x2 = x * x;
+  const float t = tanh_fast(kG0 * x * fmaf(kG1, x2, 1.f));
+  const float h = 0.5f * (1.f + t);
+  g = x * h;
+  gp = fmaf(0.5f * x * (1.f - t * t), fmaf(kG2, x2, kG0), h);
+}
+__device__ __forceinline__ float gelu_only(float x) {
+  const float t = tanh_fast(kG0 * x * fmaf(kG1, x * x, 1.f));
+  return 0.5f * x * (1.f + t);
+}
+
+__device__ __forceinline__ void st_chunk(uint8_t* tile, uint32_t row, uint32_t chunk, const float* v) {
+  uint4 w;
+  w.x = pack_bf16(v[0], v[1]);
+  w.y = pack_bf16(v[2], v[3]);
+  w.z = pack_bf16(v[4], v[5]);
+  w.w = pack_bf16(v[6], v[7]);
+  *reinterpret_cast<uint4*>(tile + sw128_off(row, chunk)) = w;
+}
+__device__ __forceinline__ void ld_chunk(const uint8_t* tile, uint32_t row, uint32_t chunk, float* v) {
+  const uint4 w = *reinterpret_cast<const uint4*>(tile + sw128_off(row, chunk));
+  v[0] = bf16_lo(w.x); v[1] = bf16_hi(w.x);
+  v[2] = bf16_lo(w.y); v[3] = bf16_hi(w.y);
+  v[4] = bf16_lo(w.z); v[5] = bf16_hi(w.z);
+  v[6] = bf16_lo(w.w); v[7] = bf16_hi(w.w);
+}
+
+// [256 x 64] = A[256 rows, K-major, two M128 blocks] * B;  B K-major ([64 n][64 k]) or MN-major ([64 k][64 n])
+__device__ __forceinline__ void mma_hidden_major(uint32_t tmem_d, uint32_t a_smem, uint32_t b_smem, bool b_mn,
+                                                 bool accumulate) {
+  const uint32_t idesc = umma_idesc_bf16(128, 64, false, b_mn, false);
+#pragma unroll
+  for (int blk = 0; blk < 2; ++blk) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint64_t ad = umma_desc_sw128(a_smem + blk * 16384 + j * 32, 16);
+      const uint64_t bd = umma_desc_sw128(b_smem + (b_mn ? j * 2048 : j * 32), b_mn ? 8192 : 16);
+      umma_bf16_ss(tmem_d + blk * 64, ad, bd, idesc, (accumulate || j) ? 1u : 0u);
+    }
+  }
+}
+// [64 tok x 64] = X[64 tok x 256] * W[256 x 64], both operands stored [256][64] (MN-major)
+__device__ __forceinline__ void mma_token_major(uint32_t tmem_d, uint32_t x_smem, uint32_t w_smem) {
+  const uint32_t idesc = umma_idesc_bf16(64, 64, true, true, false);
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const uint64_t ad = umma_desc_sw128(x_smem + j * 2048, BIG);
+    const uint64_t bd = umma_desc_sw128(w_smem + j * 2048, BIG);
+    umma_bf16_ss(tmem_d, ad, bd, idesc, j ? 1u : 0u);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmOut,
+               const FwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int quad = warp & 3, wg = warp >> 2;
+  const int hrow = wg * 128 + quad * 32 + lane;          // hidden unit owned in the 256-row epilogues
+  const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+  const int tok = quad * 16 + (lane & 15);               // token owned in the 64-row epilogues (wg 0)
+  const bool tok_valid = lane < 16;
+  const long stream_id = blockIdx.x;
+  const int head = static_cast<int>(stream_id % p.H);
+
+  uint8_t* sW1 = smem + OFF_W1;
+  uint8_t* sW2 = smem + OFF_W2;
+  uint8_t* sX2 = smem + OFF_X2;
+  uint8_t* sGP = smem + OFF_GP;
+  uint8_t* sU2 = smem + OFF_U2;
+  uint8_t* sOut = smem + OFF_OUT;
+  float* sB2 = reinterpret_cast<float*>(smem + OFF_B2);
+  float* sGamma = reinterpret_cast<float*>(smem + OFF_GAMMA);
+  float* sBeta = reinterpret_cast<float*>(smem + OFF_BETA);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + OFF_BAR);   // [kStages]
+  uint64_t* mma_bar = full + kStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_MISC);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + OFF_MISC + 4);
+
+  const uint64_t limit = p.wait_limit_ns;
+  const int NC = p.NC;
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) mbar_init(&full[s], 1);
+    mbar_init(mma_bar, 1);
+    fence_mbar_init();
+    *abort_flag = 0;
+    prefetch_tmap(&tmQ);
+    prefetch_tmap(&tmK);
+    prefetch_tmap(&tmV);
+    prefetch_tmap(&tmOut);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, TM_COLS);
+    tmem_relinquish();
+  }
+  if (tid < 64) {
+    sGamma[tid] = p.gamma[head * 64 + tid];
+    sBeta[tid] = p.beta[head * 64 + tid];
+    sB2[tid] = p.b2[stream_id * 64 + tid];
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+
+  auto issue_loads = [&](int i) {   // thread 0 only
+    const int s = i % kStages;
+    const int row0 = static_cast<int>((stream_id * NC + i) * 64);
+    mbar_expect_tx(&full[s], 3 * TILE + 128);
+    tma_load_2d(smem + OFF_K + s * TILE, &tmK, &full[s], 0, row0);
+    tma_load_2d(smem + OFF_V + s * TILE, &tmV, &full[s], 0, row0);
+    tma_load_2d(smem + OFF_Q + s * TILE, &tmQ, &full[s], 0, row0);
+    bulk_load_1d(smem + OFF_ETA + s * 128, p.eta + (stream_id * NC + i) * 64, 128, &full[s]);
+  };
+  int loads_issued = 0;
+  if (tid == 0) {
+    for (; loads_issued < kStages && loads_issued < NC; ++loads_issued) issue_loads(loads_issued);
+  }
+
+  // ---- initial state: global fp32 -> tensor memory (master) + shared memory (bf16 operand copy)
+  float b1v = p.b1[stream_id * 256 + hrow];
+  {
+    const float* W1g = p.W1 + stream_id * (64 * 256);
+    const float* W2g = p.W2 + stream_id * (256 * 64) + hrow * 64;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint32_t v[32];
+      float f[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        f[j] = W1g[(half * 32 + j) * 256 + hrow];
+        v[j] = __float_as_uint(f[j]);
+      }
+      tmem_st32(tmem + lane_base + TM_W1 + wg * 64 + half * 32, v);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) st_chunk(sW1, hrow, half * 4 + c, f + c * 8);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 q4 = reinterpret_cast<const float4*>(W2g)[half * 8 + j];
+        f[j * 4 + 0] = q4.x; f[j * 4 + 1] = q4.y; f[j * 4 + 2] = q4.z; f[j * 4 + 3] = q4.w;
+      }
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(f[j]);
+      tmem_st32(tmem + lane_base + TM_W2 + wg * 64 + half * 32, v);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) st_chunk(sW2, hrow, half * 4 + c, f + c * 8);
+    }
+    tmem_wait_st();
+  }
+  fence_proxy_async_smem();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+
+  // fp32 state (tensor memory, registers, shared memory) -> global, reference layouts
+  auto store_state = [&](float* W1o, float* b1o, float* W2o, float* b2o) {
+    __syncwarp();
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint32_t v[32];
+      tmem_ld32(tmem + lane_base + TM_W1 + wg * 64 + half * 32, v);
+      tmem_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) W1o[(half * 32 + j) * 256 + hrow] = __uint_as_float(v[j]);
+      tmem_ld32(tmem + lane_base + TM_W2 + wg * 64 + half * 32, v);
+      tmem_wait_ld();
+      float4* dst = reinterpret_cast<float4*>(W2o + hrow * 64 + half * 32);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        dst[j] = make_float4(__uint_as_float(v[j * 4]), __uint_as_float(v[j * 4 + 1]),
+                             __uint_as_float(v[j * 4 + 2]), __uint_as_float(v[j * 4 + 3]));
+    }
+    b1o[hrow] = b1v;
+    if (tid < 64) b2o[tid] = sB2[tid];
+  };
+
+  uint32_t mma_phase = 0;
+  auto wait_mma = [&]() {
+    mbar_wait_bounded(mma_bar, mma_phase, abort_flag, limit);
+    mma_phase ^= 1;
+    __syncwarp();
+    tc_fence_after_sync();
+  };
+  // generic-proxy smem writes + TMEM reads done -> next MMA may be issued
+  auto publish = [&]() {
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+  };
+
+  int it = 0;
+  for (; it < NC; ++it) {
+    const int s = it % kStages;
+    const uint8_t* sK = smem + OFF_K + s * TILE;
+    const uint8_t* sV = smem + OFF_V + s * TILE;
+    const uint8_t* sQ = smem + OFF_Q + s * TILE;
+    const __nv_bfloat16* sEta = reinterpret_cast<const __nv_bfloat16*>(smem + OFF_ETA + s * 128);
+
+    if (it % p.cgs == 0) {
+      const long c = stream_id * p.nck + it / p.cgs;
+      store_state(p.W1c + c * (64 * 256), p.b1c + c * 256, p.W2c + c * (256 * 64), p.b2c + c * 64);
+      tc_fence_before_sync();
+    }
+    if (tid == 0) tma_wait_group_read<0>();   // previous Out tile has left shared memory
+
+    mbar_wait_bounded(&full[s], (it / kStages) & 1, abort_flag, limit);
+
+    // ---- MMA1: Z1^T = W1^T K^T
+    if (tid == 0) {
+      tc_fence_after_sync();
+      mma_hidden_major(tmem + TM_A, smem_u32(sW1), smem_u32(sK), false, false);
+      umma_commit(mma_bar);
+    }
+    wait_mma();
+    // ---- EPI1: X2^T = gelu(Z1^T + b1), G' = gelu'(Z1^T + b1)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint32_t v[32];
+      tmem_ld32(tmem + lane_base + TM_A + wg * 64 + half * 32, v);
+      tmem_wait_ld();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float g[8], gp[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) gelu_pair(__uint_as_float(v[c * 8 + k]) + b1v, g[k], gp[k]);
+        st_chunk(sX2, hrow, half * 4 + c, g);
+        st_chunk(sGP, hrow, half * 4 + c, gp);
+      }
+    }
+    publish();
+
+    // ---- MMA2: Z2 = X2 W2
+    if (tid == 0) {
+      tc_fence_after_sync();
+      mma_token_major(tmem + TM_Z, smem_u32(sX2), smem_u32(sW2));
+      umma_commit(mma_bar);
+    }
+    wait_mma();
+    // ---- LN: fused LayerNorm + L2 gradient, U2 = -eta * dl/dZ2
+    if (wg == 0) {
+      float xh[64];
+      {
+        uint32_t v[32];
+        tmem_ld32(tmem + lane_base + TM_Z, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) xh[j] = __uint_as_float(v[j]) + sB2[j];
+        tmem_ld32(tmem + lane_base + TM_Z + 32, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) xh[32 + j] = __uint_as_float(v[j]) + sB2[32 + j];
+      }
+      float mu = 0.f;
+#pragma unroll
+      for (int j = 0; j < 64; ++j) mu += xh[j];
+      mu *= (1.f / 64.f);
+      float var = 0.f;
+#pragma unroll
+      for (int j = 0; j < 64; ++j) {
+        xh[j] -= mu;
+        var = fmaf(xh[j], xh[j], var);
+      }
+      const float rstd = rsqrtf(var * (1.f / 64.f) + TTT_LN_EPS);
+      float g[64];
+      float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        float kk[8], vv[8];
+        ld_chunk(sK, tok, c, kk);
+        ld_chunk(sV, tok, c, vv);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int f = c * 8 + k;
+          xh[f] *= rstd;
+          const float gam = sGamma[f];
+          const float e = fmaf(gam, xh[f], sBeta[f]) - (vv[k] - kk[k]);
+          g[f] = e * gam;
+          s1 += g[f];
+          s2 = fmaf(g[f], xh[f], s2);
+        }
+      }
+      const float scale = -__bfloat162float(sEta[tok]) * rstd * (1.f / 64.f);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        float o[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int f = c * 8 + k;
+          o[k] = (64.f * g[f] - s1 - xh[f] * s2) * scale;
+        }
+        if (tok_valid) st_chunk(sU2, tok, c, o);
+      }
+    }
+    publish();
+
+    // ---- MMA3: R^T = W2 U2^T
+    if (tid == 0) {
+      tc_fence_after_sync();
+      mma_hidden_major(tmem + TM_A, smem_u32(sW2), smem_u32(sU2), false, false);
+      umma_commit(mma_bar);
+    }
+    // b2 += column sums of U2 (bf16 values, the operand the W2 update sees), fp32 accumulate
+    if (tid >= 128 && tid < 192) {
+      const int f = tid - 128;
+      float acc = 0.f;
+#pragma unroll 8
+      for (int t = 0; t < 64; ++t)
+        acc += __bfloat162float(
+            *reinterpret_cast<const __nv_bfloat16*>(sU2 + sw128_off(t, f >> 3) + (f & 7) * 2));
+      sB2[f] += acc;
+    }
+    wait_mma();
+    // ---- EPI3: U1^T = R^T * G' (= -eta dl/dZ1), b1 += row sum
+    {
+      float bsum = 0.f;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t v[32];
+        tmem_ld32(tmem + lane_base + TM_A + wg * 64 + half * 32, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          float gp[8];
+          ld_chunk(sGP, hrow, half * 4 + c, gp);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            gp[k] *= __uint_as_float(v[c * 8 + k]);
+            bsum += gp[k];
+          }
+          st_chunk(sGP, hrow, half * 4 + c, gp);
+        }
+      }
+      b1v += bsum;
+    }
+    publish();
+
+    // ---- MMA4: W1^T += U1^T K ;  W2 += X2^T U2
+    if (tid == 0) {
+      tc_fence_after_sync();
+      mma_hidden_major(tmem + TM_W1, smem_u32(sGP), smem_u32(sK), true, true);
+      mma_hidden_major(tmem + TM_W2, smem_u32(sX2), smem_u32(sU2), true, true);
+      umma_commit(mma_bar);
+    }
+    wait_mma();
+    // ---- EPI4: refresh the bf16 operand copies of the state
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint32_t v[32];
+      float f[32];
+      tmem_ld32(tmem + lane_base + TM_W1 + wg * 64 + half * 32, v);
+      tmem_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) st_chunk(sW1, hrow, half * 4 + c, f + c * 8);
+      tmem_ld32(tmem + lane_base + TM_W2 + wg * 64 + half * 32, v);
+      tmem_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) st_chunk(sW2, hrow, half * 4 + c, f + c * 8);
+    }
+    publish();
+
+    // ---- MMA5: Z1b^T = W1^T Q^T
+    if (tid == 0) {
+      tc_fence_after_sync();
+      mma_hidden_major(tmem + TM_A, smem_u32(sW1), smem_u32(sQ), false, false);
+      umma_commit(mma_bar);
+    }
+    wait_mma();
+    // ---- EPI5: X2b^T = gelu(Z1b^T + b1)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint32_t v[32];
+      tmem_ld32(tmem + lane_base + TM_A + wg * 64 + half * 32, v);
+      tmem_wait_ld();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float g[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) g[k] = gelu_only(__uint_as_float(v[c * 8 + k]) + b1v);
+        st_chunk(sX2, hrow, half * 4 + c, g);
+      }
+    }
+    publish();
+
+    // ---- MMA6: Z2b = X2b W2
+    if (tid == 0) {
+      tc_fence_after_sync();
+      mma_token_major(tmem + TM_Z, smem_u32(sX2), smem_u32(sW2));
+      umma_commit(mma_bar);
+    }
+    wait_mma();
+    // ---- OUT: Q + gamma * LN(Z2b + b2) + beta
+    if (wg == 0) {
+      float z[64];
+      {
+        uint32_t v[32];
+        tmem_ld32(tmem + lane_base + TM_Z, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) z[j] = __uint_as_float(v[j]) + sB2[j];
+        tmem_ld32(tmem + lane_base + TM_Z + 32, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) z[32 + j] = __uint_as_float(v[j]) + sB2[32 + j];
+      }
+      float mu = 0.f;
+#pragma unroll
+      for (int j = 0; j < 64; ++j) mu += z[j];
+      mu *= (1.f / 64.f);
+      float var = 0.f;
+#pragma unroll
+      for (int j = 0; j < 64; ++j) {
+        z[j] -= mu;
+        var = fmaf(z[j], z[j], var);
+      }
+      const float rstd = rsqrtf(var * (1.f / 64.f) + TTT_LN_EPS);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        float q[8];
+        ld_chunk(sQ, tok, c, q);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int f = c * 8 + k;
+          q[k] += fmaf(sGamma[f], z[f] * rstd, sBeta[f]);
+        }
+        if (tok_valid) st_chunk(sOut, tok, c, q);
+      }
+    }
+    publish();
+    if (tid == 0) {
+      tma_store_2d(&tmOut, sOut, 0, static_cast<int>((stream_id * NC + it) * 64));
+      tma_commit_group();
+      if (!*abort_flag && loads_issued < NC && loads_issued == it + kStages) {
+        issue_loads(loads_issued);
+        ++loads_issued;
+      }
+    }
+    if (*abort_flag) break;
+  }
+
+  // ---- epilogue: optional final state, then teardown
+  const bool aborted = *abort_flag != 0;
+  if (!aborted && p.W1f != nullptr) {
+    store_state(p.W1f + stream_id * (64 * 256), p.b1f + stream_id * 256, p.W2f + stream_id * (256 * 64),
+                p.b2f + stream_id * 64);
+  }
+  if (tid == 0) {
+    tma_wait_group<0>();
+    if (aborted) {
+      // wait (bounded) for our own loads still in flight before the CTA's shared memory goes away
+      for (int j = it + 1; j < loads_issued; ++j)
+        mbar_wait_bounded(&full[j % kStages], (j / kStages) & 1, abort_flag, limit);
+      atomicExch(p.status, static_cast<uint32_t>(TTT_B200_ERR_TIMEOUT));
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, TM_COLS);
+}
+
+}  // namespace
+
+int ttt_launch_forward(const ttt_b200_fwd_args* a, cudaStream_t stream, uint32_t* status, uint64_t limit_ns) {
+  const uint64_t rows = static_cast<uint64_t>(a->B) * a->H * a->NC * 64;
+  CUtensorMap tmQ, tmK, tmV, tmOut;
+  if (int rc = ttt_make_tile_map(&tmQ, a->XQ, rows)) return rc;
+  if (int rc = ttt_make_tile_map(&tmK, a->XK, rows)) return rc;
+  if (int rc = ttt_make_tile_map(&tmV, a->XV, rows)) return rc;
+  if (int rc = ttt_make_tile_map(&tmOut, a->Out, rows)) return rc;
+  FwdParams p;
+  p.eta = static_cast<const __nv_bfloat16*>(a->last_eta);
+  p.gamma = a->ttt_norm_weight;
+  p.beta = a->ttt_norm_bias;
+  p.W1 = a->W1; p.b1 = a->b1; p.W2 = a->W2; p.b2 = a->b2;
+  p.W1c = a->W1_checkpoints; p.b1c = a->b1_checkpoints; p.W2c = a->W2_checkpoints; p.b2c = a->b2_checkpoints;
+  const bool want_final = a->W1_final && a->b1_final && a->W2_final && a->b2_final;
+  p.W1f = want_final ? a->W1_final : nullptr;
+  p.b1f = a->b1_final; p.W2f = a->W2_final; p.b2f = a->b2_final;
+  p.H = a->H; p.NC = a->NC; p.cgs = a->checkpoint_group_size; p.nck = a->num_checkpoints;
+  p.status = status;
+  p.wait_limit_ns = limit_ns;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(ttt_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
+    if (dev >= 0 && dev < 64) attr_done[dev] = true;
+  }
+  ttt_fwd_kernel<<<dim3(a->B * a->H), dim3(kThreads), SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmOut, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
+  return TTT_B200_OK;
+}
