@@ -1,4 +1,1119 @@
+// TTT-MLP backward for sm_100a: one persistent CTA per (batch, head) stream.
+//
+// Replaces the reference's bwd_ttt_mlp_ker (kernels/ttt_backward/ttt.cu:179-1443); the math is
+// that of kernels/ttt_backward/matching.py:57-342 (forward with saved intermediates, then the
+// hand-derived reverse step), driven like kernels/ttt_backward/matching.py:539-663: for every
+// checkpoint group, last to first, recompute the forward from the group's checkpoint, then
+// sweep the group in reverse.
+//
+// Layout conventions are those of the forward kernel: every 64x256 / 256x64 quantity is
+// "hidden-major" (hidden unit = TMEM lane = one thread in the epilogues), every 64x64
+// quantity "token-major" (token = TMEM lane, M = 64).  All contractions are one of two MMA
+// forms (ttt_device.cuh).  Tensor memory (512 columns):
+//   [  0,256)  fp32 state: W1^T | W2 while recomputing, dL/dW1^T | dL/dW2 while sweeping
+//              (the gradient state is parked in the grad_L_W*_init output buffers in between)
+//   [256,384)  accumulator A (256 x 64, or a 64 x 64 one in its first 64 columns)
+//   [384,512)  accumulator B (256 x 64, or two 64 x 64 ones)
+//
+// Scratch.  The recompute phase writes, per mini-batch slot of the group, into the caller's
+// `*_group` tensors (raw images of 128-byte-swizzled shared-memory tiles, so the sweep can
+// bring them back with plain bulk copies):
+//   Z1_group, X2_group, grad_l_wrt_Z1_group, Z1_bar_group, X2_bar_group : [256][64 tok] bf16
+//   W1_init_group / W2_init_group (first 32 KB of each slot): bf16 W1^T / W2 before the update
+//   x_hat_fused, grad_output_fused, grad_l_wrt_Z2, x_hat_ln_group : [64 tok][64] bf16
+//   std_fused_group, std_ln_group : fp32 [64]
+//
+// Reverse step for mini-batch i (G* = gradient w.r.t. the state after the update, go = dL/dOut):
+//   S4   gZ2b = LNbwd(go * gamma; x_hat_ln, std_ln);  d_gamma, d_beta += column sums
+//   G1   gX2b^T = W2+ gZ2b^T          E1  gZ1b^T = gX2b^T * gelu'(Z1b^T);  G_b1 += row sums
+//   G2   G_W2 += X2b^T gZ2b     G3  G_W1^T += gZ1b^T Q     G7  dQ = go + gZ1b W1+^T
+//   E2   bf16 snapshots of G_W1^T, G_W2 (the "last" values the update-rule terms use)
+//   G4   A1raw^T = G_W1^T K^T   G8  T1 = gZ1 G_W1          G5  acc1 = X2 G_W2
+//   E3   A1^T = -eta (A1raw^T + G_b1);  P^T = A1^T gelu'(Z1^T);  S^T = A1^T gelu''(Z1^T)
+//   G6   acc2 = P W2            G10 G_W2 += P^T gZ2
+//   E4   A2 = -eta (acc1 + G_b2) + acc2, second-order LayerNorm terms -> gZ2in, dV, d_gamma,
+//        d_beta, d_eta, dK (partial)
+//   G11  gX2^T = W2 gZ2in^T + G_W2snap (-eta gZ2)^T        G12 R^T = W2 gZ2^T
+//   E5   gZ1in^T = gX2^T gelu'(Z1^T) + R^T S^T;  G_b1 += row sums
+//   G13  dK += gZ1in W1^T       G14 G_W2 += X2^T gZ2in     G15 G_W1^T += gZ1in^T K
+//
+// Deviations from the reference kernel (see include/ttt_mlp_b200.h): outputs are overwritten,
+// not accumulated; `Out` is never touched.  Every wait is bounded.
+#include "ttt_device.cuh"
 #include "ttt_internal.h"
-int ttt_launch_backward(const ttt_b200_bwd_args*, cudaStream_t, uint32_t*, uint64_t) {
-  return ttt_set_error(TTT_B200_ERR_LAUNCH, "backward kernel not built yet");
+
+using namespace tttdev;
+
+namespace {
+
+constexpr int kThreads = 256;
+
+// ---- shared memory map (offsets from a 1024-byte aligned base)
+constexpr uint32_t OFF_BIG = 0;                      // 5 hidden-major buffers of 32 KB
+constexpr uint32_t OFF_T = 5 * BIG;                  // 7 token tiles of 8 KB
+constexpr uint32_t OFF_B2 = OFF_T + 7 * TILE;        // fp32[64]  b2 (recompute)
+constexpr uint32_t OFF_GB2 = OFF_B2 + 256;           // fp32[64]  dL/db2 state
+constexpr uint32_t OFF_GAMMA = OFF_GB2 + 256;
+constexpr uint32_t OFF_BETA = OFF_GAMMA + 256;
+constexpr uint32_t OFF_DG = OFF_BETA + 256;          // fp32[64]  d_gamma accumulator
+constexpr uint32_t OFF_DB = OFF_DG + 256;            // fp32[64]  d_beta accumulator
+constexpr uint32_t OFF_SIGLN = OFF_DB + 256;         // fp32[64]
+constexpr uint32_t OFF_SIGF = OFF_SIGLN + 256;       // fp32[64]
+constexpr uint32_t OFF_GB1 = OFF_SIGF + 256;         // fp32[256] copy of the per-thread dL/db1
+constexpr uint32_t OFF_PART = OFF_GB1 + 1024;        // fp32[4][64] partial sums for d_eta
+constexpr uint32_t OFF_ETA = OFF_PART + 1024;        // bf16[2][64]
+constexpr uint32_t OFF_BAR = OFF_ETA + 256;          // 16 mbarriers
+constexpr uint32_t OFF_MISC = OFF_BAR + 128;
+constexpr uint32_t SMEM_USED = OFF_MISC + 64;
+constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;
+static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB per-CTA shared memory of sm_100");
+
+// barrier indices
+constexpr int BAR_BIG = 0;     // +buffer index (0..4)
+constexpr int BAR_T = 5;       // +tile index (0..6)
+constexpr int BAR_IN = 12;     // +stage (0..1), recompute inputs
+constexpr int BAR_MMA = 14;
+
+constexpr uint32_t TM_S1 = 0;      // W1^T / dL/dW1^T
+constexpr uint32_t TM_S2 = 128;    // W2   / dL/dW2
+constexpr uint32_t TM_A = 256;
+constexpr uint32_t TM_B = 384;
+constexpr uint32_t TM_COLS = 512;
+
+struct BwdParams {
+  const __nv_bfloat16* eta;
+  const float* gamma;
+  const float* beta;
+  const float* W1c; const float* b1c; const float* W2c; const float* b2c;
+  // scratch
+  uint8_t* sc_W1; uint8_t* sc_W2;                       // 64 KB per slot, first 32 KB used
+  uint8_t* sc_Z1; uint8_t* sc_X2; uint8_t* sc_gZ1; uint8_t* sc_Z1b; uint8_t* sc_X2b;   // 32 KB per slot
+  uint8_t* sc_xhf; uint8_t* sc_gof; uint8_t* sc_gZ2; uint8_t* sc_xhln;                 // 8 KB per slot
+  float* sc_sigf; float* sc_sigln;                      // 64 floats per slot
+  // upstream
+  const float* gW1_last; const float* gb1_last; const float* gW2_last; const float* gb2_last;
+  // outputs
+  float* d_gamma; float* d_beta;
+  float* gW1; float* gb1; float* gW2; float* gb2;
+  __nv_bfloat16* d_eta;
+  uint8_t* dXQ; uint8_t* dXK; uint8_t* dXV;              // bf16 [rows][64], row-major
+  int H, NC, cgs, nck;
+  uint32_t* status;
+  uint64_t wait_limit_ns;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmGo,
+               const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int quad = warp & 3, wg = warp >> 2;
+  const int hrow = wg * 128 + quad * 32 + lane;
+  const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+  const int tok = quad * 16 + (lane & 15);
+  const bool tok_valid = (wg == 0) && (lane < 16);
+  const long sid = blockIdx.x;
+  const int head = static_cast<int>(sid % p.H);
+  const int NC = p.NC, cgs = p.cgs;
+
+  auto big = [&](int i) -> uint8_t* { return smem + OFF_BIG + i * BIG; };
+  auto tile = [&](int i) -> uint8_t* { return smem + OFF_T + i * TILE; };
+  float* sB2 = reinterpret_cast<float*>(smem + OFF_B2);
+  float* sGb2 = reinterpret_cast<float*>(smem + OFF_GB2);
+  float* sGamma = reinterpret_cast<float*>(smem + OFF_GAMMA);
+  float* sBeta = reinterpret_cast<float*>(smem + OFF_BETA);
+  float* sDG = reinterpret_cast<float*>(smem + OFF_DG);
+  float* sDB = reinterpret_cast<float*>(smem + OFF_DB);
+  float* sSigLn = reinterpret_cast<float*>(smem + OFF_SIGLN);
+  float* sSigF = reinterpret_cast<float*>(smem + OFF_SIGF);
+  float* sGb1 = reinterpret_cast<float*>(smem + OFF_GB1);
+  float* sPart = reinterpret_cast<float*>(smem + OFF_PART);
+  __nv_bfloat16* sEta = reinterpret_cast<__nv_bfloat16*>(smem + OFF_ETA);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_MISC);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + OFF_MISC + 4);
+  const uint64_t limit = p.wait_limit_ns;
+
+  if (tid == 0) {
+    for (int i = 0; i < 15; ++i) mbar_init(&bars[i], 1);
+    fence_mbar_init();
+    *abort_flag = 0;
+    prefetch_tmap(&tmQ);
+    prefetch_tmap(&tmK);
+    prefetch_tmap(&tmV);
+    prefetch_tmap(&tmGo);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, TM_COLS);
+    tmem_relinquish();
+  }
+  if (tid < 64) {
+    sGamma[tid] = p.gamma[head * 64 + tid];
+    sBeta[tid] = p.beta[head * 64 + tid];
+    sGb2[tid] = p.gb2_last[sid * 64 + tid];
+    sDG[tid] = 0.f;
+    sDB[tid] = 0.f;
+  }
+  float Gb1 = p.gb1_last[sid * 256 + hrow];
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+
+  // ---- barrier bookkeeping: every thread waits on every barrier use, in program order
+  uint32_t ph = 0;        // expected parity per barrier
+  uint32_t pending = 0;   // thread 0: loads issued and not yet waited for
+  auto wait_bar = [&](int b) {
+    if (mbar_wait_bounded(&bars[b], (ph >> b) & 1u, abort_flag, limit)) {
+      ph ^= 1u << b;
+      pending &= ~(1u << b);
+    }
+  };
+  auto wait_mma = [&]() {
+    wait_bar(BAR_MMA);
+    __syncwarp();
+    tc_fence_after_sync();
+  };
+  auto publish = [&]() {
+    asm volatile("fence.proxy.async;" ::: "memory");   // generic writes (shared and global) -> async proxy
+    tc_fence_before_sync();
+    __syncthreads();
+  };
+  auto commit = [&]() { umma_commit(&bars[BAR_MMA]); };   // thread 0
+  // thread 0: bulk-load helpers
+  auto load_big = [&](int buf, const uint8_t* src) {
+    mbar_expect_tx(&bars[BAR_BIG + buf], BIG);
+    bulk_load_1d(big(buf), src, BIG, &bars[BAR_BIG + buf]);
+    pending |= 1u << (BAR_BIG + buf);
+  };
+
+  const long tok_rows0 = sid * NC * 64;      // first row of this stream in the [rows][64] token tensors
+
+  // ---- column sum over the 64 tokens of a token tile (threads 128..191, f = tid - 128)
+  auto colsum = [&](const uint8_t* t, int f) {
+    float acc = 0.f;
+#pragma unroll 8
+    for (int r = 0; r < 64; ++r) acc += ld_elem(t, r, f);
+    return acc;
+  };
+
+  // =====================================================================================
+  const float* Gsrc_W1 = p.gW1_last + sid * (64 * 256);
+  const float* Gsrc_W2 = p.gW2_last + sid * (256 * 64);
+  float* Gdst_W1 = p.gW1 + sid * (64 * 256);
+  float* Gdst_W2 = p.gW2 + sid * (256 * 64);
+  bool aborted = false;
+
+  for (int ck = p.nck - 1; ck >= 0 && !aborted; --ck) {
+    const int i0 = ck * cgs;
+    const int gsz = min(cgs, NC - i0);
+    const long slot0 = sid * cgs;           // scratch slot of the group's first mini-batch
+    // buffer roles during recompute: 0 = W1^T bf16, 1 = W2 bf16, 2 = X2^T, 3 = G' / U1^T, 4 = gZ2 tile
+    uint8_t* bW1 = big(0);
+    uint8_t* bW2 = big(1);
+    uint8_t* bX2 = big(2);
+    uint8_t* bGP = big(3);
+    uint8_t* tGZ2 = big(4);
+    uint8_t* tU2 = tile(6);
+
+    auto issue_inputs = [&](int j) {   // thread 0
+      const int s = j & 1;
+      const int row0 = static_cast<int>(tok_rows0 + (long)(i0 + j) * 64);
+      mbar_expect_tx(&bars[BAR_IN + s], 3 * TILE + 128);
+      tma_load_2d(tile(3 * s + 0), &tmK, &bars[BAR_IN + s], 0, row0);
+      tma_load_2d(tile(3 * s + 1), &tmV, &bars[BAR_IN + s], 0, row0);
+      tma_load_2d(tile(3 * s + 2), &tmQ, &bars[BAR_IN + s], 0, row0);
+      bulk_load_1d(sEta + s * 64, p.eta + (sid * NC + i0 + j) * 64, 128, &bars[BAR_IN + s]);
+      pending |= 1u << (BAR_IN + s);
+    };
+    if (tid == 0) {
+      issue_inputs(0);
+      if (gsz > 1) issue_inputs(1);
+    }
+
+    // ---- checkpoint -> tensor memory (fp32) + shared memory (bf16) + scratch slot 0 (bf16)
+    float b1v = p.b1c[(sid * p.nck + ck) * 256 + hrow];
+    if (tid < 64) sB2[tid] = p.b2c[(sid * p.nck + ck) * 64 + tid];
+    {
+      const float* W1g = p.W1c + (sid * p.nck + ck) * (64 * 256);
+      const float* W2g = p.W2c + (sid * p.nck + ck) * (256 * 64) + hrow * 64;
+      uint8_t* g1 = p.sc_W1 + slot0 * 65536;
+      uint8_t* g2 = p.sc_W2 + slot0 * 65536;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t v[32];
+        float f[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          f[j] = W1g[(half * 32 + j) * 256 + hrow];
+          v[j] = __float_as_uint(f[j]);
+        }
+        tmem_st32(tmem + lane_base + TM_S1 + wg * 64 + half * 32, v);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint4 w = pack_chunk(f + c * 8);
+          const uint32_t off = sw128_off(hrow, half * 4 + c);
+          *reinterpret_cast<uint4*>(bW1 + off) = w;
+          *reinterpret_cast<uint4*>(g1 + off) = w;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float4 q4 = reinterpret_cast<const float4*>(W2g)[half * 8 + j];
+          f[j * 4 + 0] = q4.x; f[j * 4 + 1] = q4.y; f[j * 4 + 2] = q4.z; f[j * 4 + 3] = q4.w;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(f[j]);
+        tmem_st32(tmem + lane_base + TM_S2 + wg * 64 + half * 32, v);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint4 w = pack_chunk(f + c * 8);
+          const uint32_t off = sw128_off(hrow, half * 4 + c);
+          *reinterpret_cast<uint4*>(bW2 + off) = w;
+          *reinterpret_cast<uint4*>(g2 + off) = w;
+        }
+      }
+      tmem_wait_st();
+    }
+    publish();
+
+    // ================================================================== recompute the group
+    for (int j = 0; j < gsz; ++j) {
+      const int s = j & 1;
+      const long slot = slot0 + j;
+      const uint8_t* sK = tile(3 * s + 0);
+      const uint8_t* sV = tile(3 * s + 1);
+      const uint8_t* sQ = tile(3 * s + 2);
+      const __nv_bfloat16* eta = sEta + s * 64;
+      wait_bar(BAR_IN + s);
+
+      // MMA1: Z1^T = W1^T K^T
+      if (tid == 0) {
+        tc_fence_after_sync();
+        mma_hidden_major(tmem + TM_A, smem_u32(bW1), smem_u32(sK), false, false);
+        commit();
+      }
+      wait_mma();
+      {
+        uint8_t* gZ1 = p.sc_Z1 + slot * BIG;
+        uint8_t* gX2 = p.sc_X2 + slot * BIG;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t v[32];
+          tmem_ld32(tmem + lane_base + TM_A + wg * 64 + half * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            float z[8], g[8], gp[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              z[k] = __uint_as_float(v[c * 8 + k]) + b1v;
+              gelu_pair(z[k], g[k], gp[k]);
+            }
+            const uint32_t off = sw128_off(hrow, half * 4 + c);
+            const uint4 wg_ = pack_chunk(g);
+            *reinterpret_cast<uint4*>(bX2 + off) = wg_;
+            *reinterpret_cast<uint4*>(gX2 + off) = wg_;
+            *reinterpret_cast<uint4*>(bGP + off) = pack_chunk(gp);
+            *reinterpret_cast<uint4*>(gZ1 + off) = pack_chunk(z);
+          }
+        }
+      }
+      publish();
+
+      // MMA2: Z2 = X2 W2
+      if (tid == 0) {
+        tc_fence_after_sync();
+        mma_token_major(tmem + TM_B, smem_u32(bX2), smem_u32(bW2));
+        commit();
+      }
+      wait_mma();
+      if (wg == 0) {
+        float xh[64];
+        {
+          uint32_t v[32];
+          tmem_ld32(tmem + lane_base + TM_B, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int q = 0; q < 32; ++q) xh[q] = __uint_as_float(v[q]) + sB2[q];
+          tmem_ld32(tmem + lane_base + TM_B + 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int q = 0; q < 32; ++q) xh[32 + q] = __uint_as_float(v[q]) + sB2[32 + q];
+        }
+        float mu = 0.f;
+#pragma unroll
+        for (int q = 0; q < 64; ++q) mu += xh[q];
+        mu *= (1.f / 64.f);
+        float var = 0.f;
+#pragma unroll
+        for (int q = 0; q < 64; ++q) {
+          xh[q] -= mu;
+          var = fmaf(xh[q], xh[q], var);
+        }
+        const float sig = sqrtf(var * (1.f / 64.f) + TTT_LN_EPS);
+        const float rstd = 1.f / sig;
+        float g[64];
+        float s1 = 0.f, s2 = 0.f;
+        uint8_t* g_xhf = p.sc_xhf + slot * TILE;
+        uint8_t* g_gof = p.sc_gof + slot * TILE;
+        uint8_t* g_gz2 = p.sc_gZ2 + slot * TILE;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float kk[8], vv[8], e[8];
+          ld_chunk(sK, tok, c, kk);
+          ld_chunk(sV, tok, c, vv);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int f = c * 8 + k;
+            xh[f] *= rstd;
+            const float gam = sGamma[f];
+            e[k] = fmaf(gam, xh[f], sBeta[f]) - (vv[k] - kk[k]);
+            g[f] = e[k] * gam;
+            s1 += g[f];
+            s2 = fmaf(g[f], xh[f], s2);
+          }
+          if (tok_valid) {
+            const uint32_t off = sw128_off(tok, c);
+            *reinterpret_cast<uint4*>(g_xhf + off) = pack_chunk(xh + c * 8);
+            *reinterpret_cast<uint4*>(g_gof + off) = pack_chunk(e);
+          }
+        }
+        const float sc = rstd * (1.f / 64.f);
+        const float neg_eta = -__bfloat162float(eta[tok]);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float o[8], u[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int f = c * 8 + k;
+            o[k] = (64.f * g[f] - s1 - xh[f] * s2) * sc;
+          }
+          const uint4 w = pack_chunk(o);
+          // the update uses -eta times the bf16-rounded gradient the other products see
+          float ob[8];
+          unpack_chunk(w, ob);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) u[k] = neg_eta * ob[k];
+          if (tok_valid) {
+            const uint32_t off = sw128_off(tok, c);
+            *reinterpret_cast<uint4*>(tGZ2 + off) = w;
+            *reinterpret_cast<uint4*>(g_gz2 + off) = w;
+            *reinterpret_cast<uint4*>(tU2 + off) = pack_chunk(u);
+          }
+        }
+        if (tok_valid) p.sc_sigf[slot * 64 + tok] = sig;
+      }
+      publish();
+
+      // MMA3: R^T = W2 gZ2^T
+      if (tid == 0) {
+        tc_fence_after_sync();
+        mma_hidden_major(tmem + TM_A, smem_u32(bW2), smem_u32(tGZ2), false, false);
+        commit();
+      }
+      if (tid >= 128 && tid < 192) sB2[tid - 128] += colsum(tU2, tid - 128);
+      wait_mma();
+      {
+        uint8_t* gG1 = p.sc_gZ1 + slot * BIG;
+        float bsum = 0.f;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t v[32];
+          tmem_ld32(tmem + lane_base + TM_A + wg * 64 + half * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            float gp[8], u[8];
+            const uint32_t off = sw128_off(hrow, half * 4 + c);
+            unpack_chunk(*reinterpret_cast<const uint4*>(bGP + off), gp);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) gp[k] *= __uint_as_float(v[c * 8 + k]);     // dl/dZ1
+            const uint4 w = pack_chunk(gp);
+            *reinterpret_cast<uint4*>(gG1 + off) = w;
+            float gb[8];
+            unpack_chunk(w, gb);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              u[k] = -__bfloat162float(eta[half * 32 + c * 8 + k]) * gb[k];
+              bsum += u[k];
+            }
+            *reinterpret_cast<uint4*>(bGP + off) = pack_chunk(u);
+          }
+        }
+        b1v += bsum;
+      }
+      publish();
+
+      // MMA4: W1^T += U1^T K ; W2 += X2^T U2
+      if (tid == 0) {
+        tc_fence_after_sync();
+        mma_hidden_major(tmem + TM_S1, smem_u32(bGP), smem_u32(sK), true, true);
+        mma_hidden_major(tmem + TM_S2, smem_u32(bX2), smem_u32(tU2), true, true);
+        commit();
+      }
+      wait_mma();
+      {
+        const bool keep = (j + 1 < gsz);
+        uint8_t* g1 = p.sc_W1 + (slot + 1) * 65536;
+        uint8_t* g2 = p.sc_W2 + (slot + 1) * 65536;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t v[32];
+          float f[32];
+          tmem_ld32(tmem + lane_base + TM_S1 + wg * 64 + half * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int q = 0; q < 32; ++q) f[q] = __uint_as_float(v[q]);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const uint4 w = pack_chunk(f + c * 8);
+            const uint32_t off = sw128_off(hrow, half * 4 + c);
+            *reinterpret_cast<uint4*>(bW1 + off) = w;
+            if (keep) *reinterpret_cast<uint4*>(g1 + off) = w;
+          }
+          tmem_ld32(tmem + lane_base + TM_S2 + wg * 64 + half * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int q = 0; q < 32; ++q) f[q] = __uint_as_float(v[q]);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const uint4 w = pack_chunk(f + c * 8);
+            const uint32_t off = sw128_off(hrow, half * 4 + c);
+            *reinterpret_cast<uint4*>(bW2 + off) = w;
+            if (keep) *reinterpret_cast<uint4*>(g2 + off) = w;
+          }
+        }
+      }
+      publish();
+
+      // MMA5: Z1b^T = W1+^T Q^T
+      if (tid == 0) {
+        tc_fence_after_sync();
+        mma_hidden_major(tmem + TM_A, smem_u32(bW1), smem_u32(sQ), false, false);
+        commit();
+      }
+      wait_mma();
+      {
+        uint8_t* gZ1b = p.sc_Z1b + slot * BIG;
+        uint8_t* gX2b = p.sc_X2b + slot * BIG;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t v[32];
+          tmem_ld32(tmem + lane_base + TM_A + wg * 64 + half * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            float z[8], g[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              z[k] = __uint_as_float(v[c * 8 + k]) + b1v;
+              g[k] = gelu_only(z[k]);
+            }
+            const uint32_t off = sw128_off(hrow, half * 4 + c);
+            const uint4 w = pack_chunk(g);
+            *reinterpret_cast<uint4*>(bX2 + off) = w;
+            *reinterpret_cast<uint4*>(gX2b + off) = w;
+            *reinterpret_cast<uint4*>(gZ1b + off) = pack_chunk(z);
+          }
+        }
+      }
+      publish();
+
+      // MMA6: Z2b = X2b W2+ ; output LayerNorm statistics
+      if (tid == 0) {
+        tc_fence_after_sync();
+        mma_token_major(tmem + TM_B, smem_u32(bX2), smem_u32(bW2));
+        commit();
+      }
+      wait_mma();
+      if (wg == 0) {
+        float z[64];
+        {
+          uint32_t v[32];
+          tmem_ld32(tmem + lane_base + TM_B, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int q = 0; q < 32; ++q) z[q] = __uint_as_float(v[q]) + sB2[q];
+          tmem_ld32(tmem + lane_base + TM_B + 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int q = 0; q < 32; ++q) z[32 + q] = __uint_as_float(v[q]) + sB2[32 + q];
+        }
+        float mu = 0.f;
+#pragma unroll
+        for (int q = 0; q < 64; ++q) mu += z[q];
+        mu *= (1.f / 64.f);
+        float var = 0.f;
+#pragma unroll
+        for (int q = 0; q < 64; ++q) {
+          z[q] -= mu;
+          var = fmaf(z[q], z[q], var);
+        }
+        const float sig = sqrtf(var * (1.f / 64.f) + TTT_LN_EPS);
+        const float rstd = 1.f / sig;
+        uint8_t* g_xhln = p.sc_xhln + slot * TILE;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float o[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) o[k] = z[c * 8 + k] * rstd;
+          if (tok_valid) *reinterpret_cast<uint4*>(g_xhln + sw128_off(tok, c)) = pack_chunk(o);
+        }
+        if (tok_valid) p.sc_sigln[slot * 64 + tok] = sig;
+      }
+      publish();
+      if (tid == 0 && j + 2 < gsz && !*abort_flag) issue_inputs(j + 2);
+      if (*abort_flag) { aborted = true; break; }
+    }
+    if (aborted) break;
+
+    // ================================================================== reverse sweep
+    // dL/dW state: global (fp32) -> tensor memory
+    {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t v[32];
+#pragma unroll
+        for (int q = 0; q < 32; ++q) v[q] = __float_as_uint(Gsrc_W1[(half * 32 + q) * 256 + hrow]);
+        tmem_st32(tmem + lane_base + TM_S1 + wg * 64 + half * 32, v);
+        const float4* src = reinterpret_cast<const float4*>(Gsrc_W2 + hrow * 64 + half * 32);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const float4 q4 = src[q];
+          v[q * 4 + 0] = __float_as_uint(q4.x); v[q * 4 + 1] = __float_as_uint(q4.y);
+          v[q * 4 + 2] = __float_as_uint(q4.z); v[q * 4 + 3] = __float_as_uint(q4.w);
+        }
+        tmem_st32(tmem + lane_base + TM_S2 + wg * 64 + half * 32, v);
+      }
+      tmem_wait_st();
+    }
+    // buffer roles: i0b = W1+ (bf16), i1b = W2+, the other three free
+    int ib0 = 0, ib1 = 1, ib2 = 2, ib3 = 3, ib4 = 4;
+    uint8_t* t_go = tile(0);
+    uint8_t* t_a = tile(1);     // x_hat_ln -> grad_output_fused -> d_gamma addends
+    uint8_t* t_q = tile(2);     // Q -> gZ2in
+    uint8_t* t_g = tile(3);     // gZ2b -> U2 = -eta gZ2
+    uint8_t* t_k = tile(4);
+    uint8_t* t_gz2 = tile(5);
+    uint8_t* t_xf = tile(6);    // x_hat_fused
+    auto issue_step_loads = [&](int j) {   // thread 0: everything step j can ask for up front
+      const long slot = slot0 + j;
+      const int row0 = static_cast<int>(tok_rows0 + (long)(i0 + j) * 64);
+      load_big(ib2, p.sc_Z1b + slot * BIG);
+      load_big(ib3, p.sc_X2b + slot * BIG);
+      load_big(ib4, p.sc_gZ1 + slot * BIG);
+      mbar_expect_tx(&bars[BAR_T + 0], TILE);
+      tma_load_2d(t_go, &tmGo, &bars[BAR_T + 0], 0, row0);
+      mbar_expect_tx(&bars[BAR_T + 1], TILE + 256);
+      bulk_load_1d(t_a, p.sc_xhln + slot * TILE, TILE, &bars[BAR_T + 1]);
+      bulk_load_1d(sSigLn, p.sc_sigln + slot * 64, 256, &bars[BAR_T + 1]);
+      mbar_expect_tx(&bars[BAR_T + 2], TILE);
+      tma_load_2d(t_q, &tmQ, &bars[BAR_T + 2], 0, row0);
+      mbar_expect_tx(&bars[BAR_T + 4], TILE + 128);
+      tma_load_2d(t_k, &tmK, &bars[BAR_T + 4], 0, row0);
+      bulk_load_1d(sEta, p.eta + (sid * NC + i0 + j) * 64, 128, &bars[BAR_T + 4]);
+      mbar_expect_tx(&bars[BAR_T + 5], TILE);
+      bulk_load_1d(t_gz2, p.sc_gZ2 + slot * TILE, TILE, &bars[BAR_T + 5]);
+      mbar_expect_tx(&bars[BAR_T + 6], TILE + 256);
+      bulk_load_1d(t_xf, p.sc_xhf + slot * TILE, TILE, &bars[BAR_T + 6]);
+      bulk_load_1d(sSigF, p.sc_sigf + slot * 64, 256, &bars[BAR_T + 6]);
+      pending |= (1u << (BAR_T + 0)) | (1u << (BAR_T + 1)) | (1u << (BAR_T + 2)) | (1u << (BAR_T + 4)) |
+                 (1u << (BAR_T + 5)) | (1u << (BAR_T + 6));
+    };
+    publish();
+    if (tid == 0) issue_step_loads(gsz - 1);
+
+    for (int j = gsz - 1; j >= 0; --j) {
+      const long slot = slot0 + j;
+      const long grow = tok_rows0 + (long)(i0 + j) * 64 + tok;       // this thread's token row (token epilogues)
+
+      // ---- S4: backward of the output LayerNorm
+      wait_bar(BAR_T + 0);
+      wait_bar(BAR_T + 1);
+      if (wg == 0) {
+        float gx[64];
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float go[8], xl[8];
+          ld_chunk(t_go, tok, c, go);
+          ld_chunk(t_a, tok, c, xl);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            gx[c * 8 + k] = go[k] * sGamma[c * 8 + k];
+            s1 += gx[c * 8 + k];
+            s2 = fmaf(gx[c * 8 + k], xl[k], s2);
+          }
+        }
+        const float rs = 1.f / (64.f * sSigLn[tok]);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float xl[8], o[8];
+          ld_chunk(t_a, tok, c, xl);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) o[k] = (64.f * gx[c * 8 + k] - s1 - xl[k] * s2) * rs;
+          if (tok_valid) st_chunk(t_g, tok, c, o);
+        }
+      } else if (tid < 192) {
+        const int f = tid - 128;
+        float a = 0.f, b = 0.f;
+#pragma unroll 8
+        for (int r = 0; r < 64; ++r) {
+          const float go = ld_elem(t_go, r, f);
+          b += go;
+          a = fmaf(go, ld_elem(t_a, r, f), a);
+        }
+        sDB[f] += b;
+        sDG[f] += a;
+      }
+      publish();
+      if (tid == 0) {   // x_hat_ln is consumed: bring grad_output_fused into its tile
+        mbar_expect_tx(&bars[BAR_T + 1], TILE);
+        bulk_load_1d(t_a, p.sc_gof + slot * TILE, TILE, &bars[BAR_T + 1]);
+        pending |= 1u << (BAR_T + 1);
+        // G1: gX2b^T = W2+ gZ2b^T
+        tc_fence_after_sync();
+        mma_hidden_major(tmem + TM_A, smem_u32(big(ib1)), smem_u32(t_g), false, false);
+        commit();
+      }
+      if (tid >= 128 && tid < 192) sGb2[tid - 128] += colsum(t_g, tid - 128);
+      wait_mma();
+      wait_bar(BAR_BIG + ib2);
+      // ---- E1: gZ1b^T = gX2b^T * gelu'(Z1b^T), in place over Z1b^T
+      {
+        uint8_t* bz = big(ib2);
+        float bsum = 0.f;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t v[32];
+          tmem_ld32(tmem + lane_base + TM_A + wg * 64 + half * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            float z[8];
+            ld_chunk(bz, hrow, half * 4 + c, z);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              z[k] = __uint_as_float(v[c * 8 + k]) * gelu_grad(z[k]);
+              bsum += z[k];
+            }
+            st_chunk(bz, hrow, half * 4 + c, z);
+          }
+        }
+        Gb1 += bsum;
+      }
+      publish();
+      wait_bar(BAR_BIG + ib3);
+      wait_bar(BAR_T + 2);
+      if (tid == 0) {
+        tc_fence_after_sync();
+        mma_hidden_major(tmem + TM_S2, smem_u32(big(ib3)), smem_u32(t_g), true, true);   // G2
+        mma_hidden_major(tmem + TM_S1, smem_u32(big(ib2)), smem_u32(t_q), true, true);   // G3
+        mma_token_major(tmem + TM_B, smem_u32(big(ib2)), smem_u32(big(ib0)));            // G7
+        commit();
+      }
+      wait_mma();
+      // ---- E2: bf16 snapshots of the gradient state; dQ
+      {
+        uint8_t* s1b = big(ib0);
+        uint8_t* s2b = big(ib1);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t v[32];
+          float f[32];
+          tmem_ld32(tmem + lane_base + TM_S1 + wg * 64 + half * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int q = 0; q < 32; ++q) f[q] = __uint_as_float(v[q]);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) st_chunk(s1b, hrow, half * 4 + c, f + c * 8);
+          tmem_ld32(tmem + lane_base + TM_S2 + wg * 64 + half * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int q = 0; q < 32; ++q) f[q] = __uint_as_float(v[q]);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) st_chunk(s2b, hrow, half * 4 + c, f + c * 8);
+        }
+        sGb1[hrow] = Gb1;
+      }
+      if (wg == 0) {
+        uint4* dst = reinterpret_cast<uint4*>(p.dXQ + grow * 128);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t v[32];
+          tmem_ld32(tmem + lane_base + TM_B + half * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            float go[8];
+            ld_chunk(t_go, tok, half * 4 + c, go);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) go[k] += __uint_as_float(v[c * 8 + k]);
+            if (tok_valid) dst[half * 4 + c] = pack_chunk(go);
+          }
+        }
+      }
+      publish();
+      if (tid == 0) {
+        load_big(ib2, p.sc_Z1 + slot * BIG);
+        load_big(ib3, p.sc_X2 + slot * BIG);
+      }
+      wait_bar(BAR_BIG + ib4);
+      // ---- partial sums over the hidden units of gZ1 * G_b1 (fourth term of d_eta)
+      {
+        const int q = tid >> 6, t = tid & 63;
+        const uint8_t* bg = big(ib4);
+        float acc = 0.f;
+#pragma unroll 8
+        for (int h = q * 64; h < q * 64 + 64; ++h) acc = fmaf(ld_elem(bg, h, t), sGb1[h], acc);
+        sPart[q * 64 + t] = acc;
+      }
+      publish();
+      wait_bar(BAR_T + 4);
+      wait_bar(BAR_BIG + ib3);
+      if (tid == 0) {
+        tc_fence_after_sync();
+        mma_hidden_major(tmem + TM_A, smem_u32(big(ib0)), smem_u32(t_k), false, false);   // G4
+        mma_token_major(tmem + TM_B, smem_u32(big(ib4)), smem_u32(big(ib0)));             // G8
+        mma_token_major(tmem + TM_B + 64, smem_u32(big(ib3)), smem_u32(big(ib1)));        // G5
+        commit();
+      }
+      wait_mma();
+      if (tid == 0) load_big(ib3, p.sc_W2 + slot * 65536);
+      wait_bar(BAR_BIG + ib2);
+      // ---- E3: A1, P = A1 gelu'(Z1), S = A1 gelu''(Z1), gelu'(Z1)
+      {
+        uint8_t* bz = big(ib2);
+        uint8_t* bp = big(ib4);
+        uint8_t* bgp = big(ib0);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t v[32];
+          tmem_ld32(tmem + lane_base + TM_A + wg * 64 + half * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            float z[8], pp[8], gp[8];
+            ld_chunk(bz, hrow, half * 4 + c, z);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const float a1 = -__bfloat162float(sEta[half * 32 + c * 8 + k]) * (__uint_as_float(v[c * 8 + k]) + Gb1);
+              float gpp;
+              gelu_grad_pair(z[k], gp[k], gpp);
+              pp[k] = a1 * gp[k];
+              z[k] = a1 * gpp;
+            }
+            st_chunk(bp, hrow, half * 4 + c, pp);
+            st_chunk(bz, hrow, half * 4 + c, z);
+            st_chunk(bgp, hrow, half * 4 + c, gp);
+          }
+        }
+      }
+      publish();
+      wait_bar(BAR_BIG + ib3);
+      wait_bar(BAR_T + 5);
+      if (tid == 0) {
+        tc_fence_after_sync();
+        mma_token_major(tmem + TM_A, smem_u32(big(ib4)), smem_u32(big(ib3)));                 // G6
+        mma_hidden_major(tmem + TM_S2, smem_u32(big(ib4)), smem_u32(t_gz2), true, true);     // G10
+        commit();
+      }
+      wait_mma();
+      if (tid == 0) load_big(ib4, p.sc_W1 + slot * 65536);
+      wait_bar(BAR_T + 6);
+      wait_bar(BAR_T + 1);   // grad_output_fused
+      // ---- E4: second order through the fused LayerNorm + L2 gradient (token-major)
+      if (wg == 0) {
+        float A2[64], t1[64];
+        const float eta_t = __bfloat162float(sEta[tok]);
+        const float rs = 1.f / sSigF[tok];
+        float d12 = 0.f, d3 = 0.f;
+        {
+          uint32_t v[32], w[32];
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            tmem_ld32(tmem + lane_base + TM_B + 64 + half * 32, v);   // acc1 = X2 G_W2
+            tmem_ld32(tmem + lane_base + TM_A + half * 32, w);        // acc2 = P W2
+            tmem_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              float gz[8];
+              ld_chunk(t_gz2, tok, half * 4 + c, gz);
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                const int f = half * 32 + c * 8 + k;
+                const float a1 = __uint_as_float(v[c * 8 + k]) + sGb2[f];
+                d12 = fmaf(gz[k], a1, d12);
+                A2[f] = fmaf(-eta_t, a1, __uint_as_float(w[c * 8 + k]));
+              }
+            }
+          }
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            tmem_ld32(tmem + lane_base + TM_B + half * 32, v);        // T1 = gZ1 G_W1
+            tmem_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              float kk[8];
+              ld_chunk(t_k, tok, half * 4 + c, kk);
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                const int f = half * 32 + c * 8 + k;
+                t1[f] = __uint_as_float(v[c * 8 + k]);
+                d3 = fmaf(t1[f], kk[k], d3);
+              }
+            }
+          }
+        }
+        // pass 1: sums of A2 and A2 * x_hat
+        float s_a = 0.f, s_ax = 0.f, s_gx = 0.f;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float xh[8], go[8];
+          ld_chunk(t_xf, tok, c, xh);
+          ld_chunk(t_a, tok, c, go);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int f = c * 8 + k;
+            s_a += A2[f];
+            s_ax = fmaf(A2[f], xh[k], s_ax);
+            s_gx = fmaf(go[k] * sGamma[f], xh[k], s_gx);
+          }
+        }
+        // pass 2: Bt, outputs that depend on it, gx_hat (kept in A2), sums for gZ2in
+        float s_gs = 0.f, s_gxh = 0.f;
+        uint4* dV = reinterpret_cast<uint4*>(p.dXV + grow * 128);
+        uint4* dKp = reinterpret_cast<uint4*>(p.dXK + grow * 128);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float xh[8], go[8], gz[8], dga[8], dv[8], kp[8];
+          ld_chunk(t_xf, tok, c, xh);
+          ld_chunk(t_a, tok, c, go);
+          ld_chunk(t_gz2, tok, c, gz);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int f = c * 8 + k;
+            const float gam = sGamma[f];
+            const float bt = (A2[f] - (s_a + xh[k] * s_ax) * (1.f / 64.f)) * rs;
+            const float gly = gam * bt;
+            dga[k] = fmaf(go[k], bt, gly * xh[k]);
+            dv[k] = -gly;
+            kp[k] = fmaf(-eta_t, t1[f], gly);
+            const float gxf = go[k] * gam;
+            const float gxh = fmaf(gly, gam, -(gxf * s_ax + A2[f] * s_gx) * rs * (1.f / 64.f));
+            const float gsd = (-gxh * xh[k] - A2[f] * gz[k]) * rs;
+            s_gs += gsd;
+            s_gxh += gxh;
+            A2[f] = gxh;
+          }
+          if (tok_valid) {
+            st_chunk(t_a, tok, c, dga);          // d_gamma addends, in place over grad_output_fused
+            const uint4 wv = pack_chunk(dv);
+            *reinterpret_cast<uint4*>(t_go + sw128_off(tok, c)) = wv;   // dV tile (for d_beta)
+            dV[c] = wv;
+            dKp[c] = pack_chunk(kp);             // partial dK, completed after G13
+          }
+        }
+        // pass 3: gZ2in and U2 = -eta gZ2
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float xh[8], gz[8], o[8];
+          ld_chunk(t_xf, tok, c, xh);
+          ld_chunk(t_gz2, tok, c, gz);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int f = c * 8 + k;
+            o[k] = fmaf(A2[f], rs, (s_gs * xh[k] - s_gxh * rs) * (1.f / 64.f));
+            gz[k] *= -eta_t;
+          }
+          if (tok_valid) {
+            st_chunk(t_q, tok, c, o);
+            st_chunk(t_g, tok, c, gz);
+          }
+        }
+        if (tok_valid) {
+          const float de = -(d12 + d3 + sPart[tok] + sPart[64 + tok] + sPart[128 + tok] + sPart[192 + tok]);
+          p.d_eta[(sid * NC + i0 + j) * 64 + tok] = __float2bfloat16(de);
+        }
+      }
+      publish();
+      if (tid == 0) {
+        tc_fence_after_sync();
+        mma_hidden_major(tmem + TM_B, smem_u32(big(ib3)), smem_u32(t_q), false, false);      // G11
+        mma_hidden_major(tmem + TM_B, smem_u32(big(ib1)), smem_u32(t_g), false, true);       // + G_W2snap U2^T
+        mma_hidden_major(tmem + TM_A, smem_u32(big(ib3)), smem_u32(t_gz2), false, false);    // G12
+        commit();
+      }
+      if (tid >= 128 && tid < 192) {
+        const int f = tid - 128;
+        sGb2[f] += colsum(t_q, f);
+        sDG[f] += colsum(t_a, f);
+        sDB[f] -= colsum(t_go, f);
+      }
+      wait_mma();
+      // ---- E5: gZ1in^T = gX2^T gelu'(Z1^T) + R^T S^T, in place over S^T
+      {
+        uint8_t* bs = big(ib2);
+        const uint8_t* bgp = big(ib0);
+        float bsum = 0.f;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t v[32], w[32];
+          tmem_ld32(tmem + lane_base + TM_B + wg * 64 + half * 32, v);
+          tmem_ld32(tmem + lane_base + TM_A + wg * 64 + half * 32, w);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            float gp[8], sv[8];
+            ld_chunk(bgp, hrow, half * 4 + c, gp);
+            ld_chunk(bs, hrow, half * 4 + c, sv);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              sv[k] = fmaf(__uint_as_float(v[c * 8 + k]), gp[k], __uint_as_float(w[c * 8 + k]) * sv[k]);
+              bsum += sv[k];
+            }
+            st_chunk(bs, hrow, half * 4 + c, sv);
+          }
+        }
+        Gb1 += bsum;
+      }
+      publish();
+      if (tid == 0) load_big(ib0, p.sc_X2 + slot * BIG);
+      wait_bar(BAR_BIG + ib4);
+      wait_bar(BAR_BIG + ib0);
+      if (tid == 0) {
+        tc_fence_after_sync();
+        mma_token_major(tmem + TM_A, smem_u32(big(ib2)), smem_u32(big(ib4)));                 // G13
+        mma_hidden_major(tmem + TM_S1, smem_u32(big(ib2)), smem_u32(t_k), true, true);       // G15
+        mma_hidden_major(tmem + TM_S2, smem_u32(big(ib0)), smem_u32(t_q), true, true);       // G14
+        commit();
+      }
+      wait_mma();
+      // ---- E6: dK = partial + gZ1in W1^T
+      if (wg == 0) {
+        uint4* dKp = reinterpret_cast<uint4*>(p.dXK + grow * 128);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t v[32];
+          tmem_ld32(tmem + lane_base + TM_A + half * 32, v);
+          tmem_wait_ld();
+          if (tok_valid) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              float kp[8];
+              unpack_chunk(dKp[half * 4 + c], kp);
+#pragma unroll
+              for (int k = 0; k < 8; ++k) kp[k] += __uint_as_float(v[c * 8 + k]);
+              dKp[half * 4 + c] = pack_chunk(kp);
+            }
+          }
+        }
+      }
+      publish();
+      // pre-update weights of this mini-batch are the post-update weights of the previous one
+      {
+        const int n0 = ib4, n1 = ib3, n2 = ib2, n3 = ib1, n4 = ib0;
+        ib0 = n0; ib1 = n1; ib2 = n2; ib3 = n3; ib4 = n4;
+      }
+      if (tid == 0 && j > 0 && !*abort_flag) issue_step_loads(j - 1);
+      if (*abort_flag) { aborted = true; break; }
+    }
+    if (aborted) break;
+
+    // ---- park the gradient state (tensor memory -> grad_L_W*_init); the last group leaves the result
+    {
+      __syncwarp();
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t v[32];
+        tmem_ld32(tmem + lane_base + TM_S1 + wg * 64 + half * 32, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int q = 0; q < 32; ++q) Gdst_W1[(half * 32 + q) * 256 + hrow] = __uint_as_float(v[q]);
+        tmem_ld32(tmem + lane_base + TM_S2 + wg * 64 + half * 32, v);
+        tmem_wait_ld();
+        float4* dst = reinterpret_cast<float4*>(Gdst_W2 + hrow * 64 + half * 32);
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          dst[q] = make_float4(__uint_as_float(v[q * 4]), __uint_as_float(v[q * 4 + 1]),
+                               __uint_as_float(v[q * 4 + 2]), __uint_as_float(v[q * 4 + 3]));
+      }
+      Gsrc_W1 = Gdst_W1;
+      Gsrc_W2 = Gdst_W2;
+    }
+    publish();
+  }
+
+  // ---- final vector outputs
+  if (!aborted) {
+    p.gb1[sid * 256 + hrow] = Gb1;
+    if (tid < 64) {
+      p.gb2[sid * 64 + tid] = sGb2[tid];
+      p.d_gamma[sid * 64 + tid] = sDG[tid];
+      p.d_beta[sid * 64 + tid] = sDB[tid];
+    }
+  }
+  if (tid == 0 && (aborted || *abort_flag)) {
+    for (int b = 0; b < 15; ++b)
+      if (pending & (1u << b)) mbar_wait_bounded(&bars[b], (ph >> b) & 1u, abort_flag, limit);
+    atomicExch(p.status, static_cast<uint32_t>(TTT_B200_ERR_TIMEOUT));
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, TM_COLS);
+}
+
+}  // namespace
+
+int ttt_launch_backward(const ttt_b200_bwd_args* a, cudaStream_t stream, uint32_t* status, uint64_t limit_ns) {
+  const uint64_t rows = static_cast<uint64_t>(a->B) * a->H * a->NC * 64;
+  CUtensorMap tmQ, tmK, tmV, tmGo;
+  if (int rc = ttt_make_tile_map(&tmQ, a->XQ, rows)) return rc;
+  if (int rc = ttt_make_tile_map(&tmK, a->XK, rows)) return rc;
+  if (int rc = ttt_make_tile_map(&tmV, a->XV, rows)) return rc;
+  if (int rc = ttt_make_tile_map(&tmGo, a->grad_L_XQW_mini_batch, rows)) return rc;
+  BwdParams p;
+  p.eta = static_cast<const __nv_bfloat16*>(a->last_eta);
+  p.gamma = a->ttt_norm_weight;
+  p.beta = a->ttt_norm_bias;
+  p.W1c = a->W1_checkpoints; p.b1c = a->b1_checkpoints; p.W2c = a->W2_checkpoints; p.b2c = a->b2_checkpoints;
+  p.sc_W1 = reinterpret_cast<uint8_t*>(a->W1_init_group);
+  p.sc_W2 = reinterpret_cast<uint8_t*>(a->W2_init_group);
+  p.sc_Z1 = static_cast<uint8_t*>(a->Z1_group);
+  p.sc_X2 = static_cast<uint8_t*>(a->X2_group);
+  p.sc_gZ1 = static_cast<uint8_t*>(a->grad_l_wrt_Z1_group);
+  p.sc_Z1b = static_cast<uint8_t*>(a->Z1_bar_group);
+  p.sc_X2b = static_cast<uint8_t*>(a->X2_bar_group);
+  p.sc_xhf = static_cast<uint8_t*>(a->x_hat_fused_group);
+  p.sc_gof = static_cast<uint8_t*>(a->grad_output_fused_group);
+  p.sc_gZ2 = static_cast<uint8_t*>(a->grad_l_wrt_Z2_group);
+  p.sc_xhln = static_cast<uint8_t*>(a->x_hat_ln_group);
+  p.sc_sigf = a->std_fused_group;
+  p.sc_sigln = a->std_ln_group;
+  p.gW1_last = a->grad_L_W1_last; p.gb1_last = a->grad_L_b1_last;
+  p.gW2_last = a->grad_L_W2_last; p.gb2_last = a->grad_L_b2_last;
+  p.d_gamma = a->grad_L_ttt_norm_weight; p.d_beta = a->grad_L_ttt_norm_bias;
+  p.gW1 = a->grad_L_W1_init; p.gb1 = a->grad_L_b1_init; p.gW2 = a->grad_L_W2_init; p.gb2 = a->grad_L_b2_init;
+  p.d_eta = static_cast<__nv_bfloat16*>(a->grad_L_last_eta);
+  p.dXQ = static_cast<uint8_t*>(a->grad_L_XQ);
+  p.dXK = static_cast<uint8_t*>(a->grad_L_XK);
+  p.dXV = static_cast<uint8_t*>(a->grad_L_XV);
+  p.H = a->H; p.NC = a->NC; p.cgs = a->checkpoint_group_size; p.nck = a->num_checkpoints;
+  p.status = status;
+  p.wait_limit_ns = limit_ns;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(ttt_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
+    if (dev >= 0 && dev < 64) attr_done[dev] = true;
+  }
+  ttt_bwd_kernel<<<dim3(a->B * a->H), dim3(kThreads), SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmGo, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
+  return TTT_B200_OK;
 }

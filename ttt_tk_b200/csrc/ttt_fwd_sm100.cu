@@ -25,17 +25,15 @@
 //
 // All waits are bounded (see sm100_ptx.cuh); on expiry the CTA reports through the status
 // word, drains its own copies, frees its tensor memory and returns.
-#include "sm100_ptx.cuh"
+#include "ttt_device.cuh"
 #include "ttt_internal.h"
 
-using namespace sm100;
+using namespace tttdev;
 
 namespace {
 
 constexpr int kStages = 3;
 constexpr int kThreads = 256;
-constexpr uint32_t TILE = 8192;    // 64 x 64 bf16
-constexpr uint32_t BIG = 32768;    // 256 x 64 bf16
 
 constexpr uint32_t OFF_K = 0;
 constexpr uint32_t OFF_V = OFF_K + kStages * TILE;
@@ -63,8 +61,6 @@ constexpr uint32_t TM_A = 256;
 constexpr uint32_t TM_Z = 384;
 constexpr uint32_t TM_COLS = 512;
 
-constexpr float kG0 = 0.79788456f, kG1 = 0.044715f, kG2 = 0.1070322243f;
-
 struct FwdParams {
   const __nv_bfloat16* eta;
   const float* gamma;
@@ -85,64 +81,6 @@ struct FwdParams {
   uint32_t* status;
   uint64_t wait_limit_ns;
 };
-
-__device__ __forceinline__ float tanh_fast(float x) {
-  float y;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ void gelu_pair(float x, float& g, float& gp) {
-  const float x2 = x * x;
-  const float t = tanh_fast(kG0 * x * fmaf(kG1, x2, 1.f));
-  const float h = 0.5f * (1.f + t);
-  g = x * h;
-  gp = fmaf(0.5f * x * (1.f - t * t), fmaf(kG2, x2, kG0), h);
-}
-__device__ __forceinline__ float gelu_only(float x) {
-  const float t = tanh_fast(kG0 * x * fmaf(kG1, x * x, 1.f));
-  return 0.5f * x * (1.f + t);
-}
-
-__device__ __forceinline__ void st_chunk(uint8_t* tile, uint32_t row, uint32_t chunk, const float* v) {
-  uint4 w;
-  w.x = pack_bf16(v[0], v[1]);
-  w.y = pack_bf16(v[2], v[3]);
-  w.z = pack_bf16(v[4], v[5]);
-  w.w = pack_bf16(v[6], v[7]);
-  *reinterpret_cast<uint4*>(tile + sw128_off(row, chunk)) = w;
-}
-__device__ __forceinline__ void ld_chunk(const uint8_t* tile, uint32_t row, uint32_t chunk, float* v) {
-  const uint4 w = *reinterpret_cast<const uint4*>(tile + sw128_off(row, chunk));
-  v[0] = bf16_lo(w.x); v[1] = bf16_hi(w.x);
-  v[2] = bf16_lo(w.y); v[3] = bf16_hi(w.y);
-  v[4] = bf16_lo(w.z); v[5] = bf16_hi(w.z);
-  v[6] = bf16_lo(w.w); v[7] = bf16_hi(w.w);
-}
-
-// [256 x 64] = A[256 rows, K-major, two M128 blocks] * B;  B K-major ([64 n][64 k]) or MN-major ([64 k][64 n])
-__device__ __forceinline__ void mma_hidden_major(uint32_t tmem_d, uint32_t a_smem, uint32_t b_smem, bool b_mn,
-                                                 bool accumulate) {
-  const uint32_t idesc = umma_idesc_bf16(128, 64, false, b_mn, false);
-#pragma unroll
-  for (int blk = 0; blk < 2; ++blk) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint64_t ad = umma_desc_sw128(a_smem + blk * 16384 + j * 32, 16);
-      const uint64_t bd = umma_desc_sw128(b_smem + (b_mn ? j * 2048 : j * 32), b_mn ? 8192 : 16);
-      umma_bf16_ss(tmem_d + blk * 64, ad, bd, idesc, (accumulate || j) ? 1u : 0u);
-    }
-  }
-}
-// [64 tok x 64] = X[64 tok x 256] * W[256 x 64], both operands stored [256][64] (MN-major)
-__device__ __forceinline__ void mma_token_major(uint32_t tmem_d, uint32_t x_smem, uint32_t w_smem) {
-  const uint32_t idesc = umma_idesc_bf16(64, 64, true, true, false);
-#pragma unroll
-  for (int j = 0; j < 16; ++j) {
-    const uint64_t ad = umma_desc_sw128(x_smem + j * 2048, BIG);
-    const uint64_t bd = umma_desc_sw128(w_smem + j * 2048, BIG);
-    umma_bf16_ss(tmem_d, ad, bd, idesc, j ? 1u : 0u);
-  }
-}
 
 __global__ void __launch_bounds__(kThreads, 1)
 ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
