@@ -1,0 +1,361 @@
+#!/usr/bin/env python
+"""Benchmark of the TTT-MLP forward + backward path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1|c0|small]
+
+One "step" = one forward + one backward over one batch of synthetic input of the named
+workload (default: the forward+backward configuration, B=4 H=32 seq 8192 cgs 8 per GPU).
+With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank processes its
+own batch shard of that size (weak scaling) and the per-head norm gradients are summed across
+ranks with one NCCL all-reduce, the only exchange the path has.
+
+Prints ONE JSON line (rank 0).  `value` is device-timed with the inputs resident in HBM;
+`e2e` is measured through the public operator API with pinned host buffers, host<->device
+copies inside the timed region.  `--impl reference` times the CPU oracle (the PyTorch-eager
+restatement of the reference's own PyTorch functions; the reference's CUDA kernels are
+sm_90a-only and cannot run on this GPU) on the host cores on a bounded sample of the same
+workload.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (B, H, NC, cgs, description)
+    "c2": (4, 32, 128, 8, "configs[2]: fwd+bwd, B=4 H=32 seq=8192 (NC=128) cgs=8, per GPU"),
+    "c1": (4, 12, 32, 4, "configs[1] shape run fwd+bwd, B=4 H=12 seq=2048 (NC=32) cgs=4, per GPU"),
+    "c0": (1, 4, 32, 4, "configs[0] shape, B=1 H=4 seq=2048 (NC=32) cgs=4"),
+    "small": (1, 8, 16, 4, "small case for profiling, B=1 H=8 seq=1024 cgs=4"),
+}
+U_FLOP = 2 * 64 * 64 * 256            # one GEMM unit per mini-batch per (b,h)
+FWD_U, BWD_U = 7, 22                  # algorithmic GEMM units: forward; backward (7 recompute + 15 sweep)
+STATE_BYTES = 132352                  # fp32 W1 + b1 + W2 + b2 of one (b,h)
+
+
+def algorithmic_bytes(B, H, NC, cgs):
+    """HBM bytes the path must move per step (inputs, outputs, checkpoints), per GPU."""
+    T = NC * 64
+    n = -(-NC // cgs)
+    fwd = 514 * T + STATE_BYTES + 512 + n * STATE_BYTES
+    bwd = 900 * T + n * STATE_BYTES + 2 * STATE_BYTES + 512 + 1024
+    return B * H * fwd, B * H * bwd
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return d, "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.idx}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_host_inputs(B, H, NC, seed):
+    from ttt_tk_b200.synthetic import make_inputs
+    return make_inputs(B, H, NC, seed=seed, eta_scale=0.1, backward=True)
+
+
+class DeviceStep:
+    """Device-resident buffers and the fwd+bwd step through the operator API."""
+
+    def __init__(self, host, cgs, dev):
+        from ttt_tk_b200.buffers import alloc_backward_buffers, GRAD_NAMES
+        self.GRADS = GRAD_NAMES
+        self.cgs = cgs
+        self.dev = dev
+        B, H, NC = host["XQ"].shape[:3]
+        self.B, self.H, self.NC = B, H, NC
+        n = -(-NC // cgs)
+        self.t = {k: v.to(dev) for k, v in host.items()}
+        self.t["last_eta5"] = self.t["last_eta"].unsqueeze(-1).contiguous()
+        self.ck = [torch.empty(B, H, n, *s, device=dev) for s in ((64, 256), (1, 256), (256, 64), (1, 64))]
+        self.out = torch.empty_like(self.t["XQ"])
+        self.scratch, self.outs = alloc_backward_buffers(B, H, NC, cgs, device=dev, fill=0.0)
+        self.norm_grads = torch.zeros(2, H, 64, device=dev)
+        self.ev = None
+
+    def forward(self):
+        from ttt_tk_b200 import ttt_forward
+        t = self.t
+        ttt_forward(t["XQ"], t["XK"], t["XV"], t["last_eta"], t["ttt_norm_weight"], t["ttt_norm_bias"],
+                    t["W1"], t["b1"], t["W2"], t["b2"], *self.ck, self.out, self.cgs)
+
+    def backward(self):
+        from ttt_tk_b200 import ttt_backward
+        t = self.t
+        ttt_backward(t["XQ"], t["XK"], t["XV"], t["last_eta5"], t["ttt_norm_weight"], t["ttt_norm_bias"],
+                     *self.ck, self.out, *self.scratch,
+                     t["grad_L_W1_last"], t["grad_L_b1_last"], t["grad_L_W2_last"], t["grad_L_b2_last"],
+                     t["grad_L_XQW_mini_batch"], *[self.outs[k] for k in self.GRADS], self.cgs)
+
+    def reduce_norm_grads(self, world):
+        # the caller-side batch sum the operator's layout asks for, then the one exchange of the path
+        self.norm_grads[0] = self.outs["grad_L_ttt_norm_weight"].sum(0).squeeze(1)
+        self.norm_grads[1] = self.outs["grad_L_ttt_norm_bias"].sum(0).squeeze(1)
+        if world > 1:
+            torch.distributed.all_reduce(self.norm_grads)
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+    from ttt_tk_b200 import take_status
+    B, H, NC, cgs, desc = WORKLOADS[args.workload]
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    host = make_host_inputs(B, H, NC, seed=rank)
+    step = DeviceStep(host, cgs, dev)
+    K, W = args.steps, args.warmup
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(W):
+        step.forward()
+        step.backward()
+        step.reduce_norm_grads(world)
+    barrier()
+    assert take_status() == 0, "device-side wait ran out during warm-up"
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+    t_end = torch.cuda.Event(enable_timing=True)
+    barrier()
+    for k in range(K):
+        ev[k][0].record()
+        step.forward()
+        ev[k][1].record()
+        step.backward()
+        ev[k][2].record()
+        step.reduce_norm_grads(world)
+    t_end.record()
+    barrier()
+    total_ms = ev[0][0].elapsed_time(t_end)
+    clocks = sampler.stop() if rank == 0 else None
+    assert take_status() == 0, "device-side wait ran out during the timed region"
+    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    tt = torch.tensor([total_ms, fwd_ms, bwd_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    total_ms, fwd_ms, bwd_ms = tt.tolist()
+
+    # ---- end to end through the operator API with pinned host buffers
+    e2e_steps = max(1, min(K, args.e2e_steps))
+    in_keys = ["XQ", "XK", "XV", "last_eta", "ttt_norm_weight", "ttt_norm_bias", "W1", "b1", "W2", "b2",
+               "grad_L_XQW_mini_batch", "grad_L_W1_last", "grad_L_b1_last", "grad_L_W2_last", "grad_L_b2_last"]
+    pin_in = {k: host[k].contiguous().pin_memory() for k in in_keys}
+    out_t = {"Out": step.out, **step.outs}
+    pin_out = {k: torch.empty(v.shape, dtype=v.dtype).pin_memory() for k, v in out_t.items()}
+    h2d = sum(v.numel() * v.element_size() for v in pin_in.values())
+    d2h = sum(v.numel() * v.element_size() for v in pin_out.values())
+
+    def e2e_step():
+        for k, v in pin_in.items():
+            step.t[k].copy_(v, non_blocking=True)
+        step.t["last_eta5"] = step.t["last_eta"].unsqueeze(-1)
+        step.forward()
+        step.backward()
+        step.reduce_norm_grads(world)
+        for k, v in out_t.items():
+            pin_out[k].copy_(v, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    et = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(et, op=dist.ReduceOp.MAX)
+    e2e_ms = et.item() / e2e_steps
+
+    if rank != 0:
+        return None
+    pk, pk_src = peaks()
+    tokens_per_step = world * B * NC * 64
+    ms_per_step = total_ms / K
+    th = B * H * NC * 64                    # token-heads per GPU per step
+    fwd_flop, bwd_flop = th * 32768 * FWD_U, th * 32768 * BWD_U
+    fwd_bytes, bwd_bytes = algorithmic_bytes(B, H, NC, cgs)
+    peak_tf = pk.get("bf16_tflops_sustained", pk["bf16_tflops"])
+    bwd_tf = bwd_flop / (bwd_ms * 1e-3) / 1e12
+    res = {
+        "metric": "ttt_mlp_fwd_bwd_tokens_per_s", "value": tokens_per_step / (ms_per_step * 1e-3),
+        "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": desc, "B_per_gpu": B, "H": H, "seq_len": NC * 64, "checkpoint_group_size": cgs,
+                   "parallelism": f"(batch x head) streams sharded, dp{world}",
+                   "l2": "working set per step (~1.7 GB at c2) exceeds the 126 MB L2; no explicit flush"},
+        "kernels": {"fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+                    "fwd_tflops": fwd_flop / (fwd_ms * 1e-3) / 1e12, "bwd_tflops": bwd_tf,
+                    "fwd_bwd_frac_of_bf16_peak": (fwd_flop + bwd_flop) / ((fwd_ms + bwd_ms) * 1e-3) / 1e12 / peak_tf,
+                    "fwd_algorithmic_gbs": fwd_bytes / (fwd_ms * 1e-3) / 1e9,
+                    "bwd_algorithmic_gbs": bwd_bytes / (bwd_ms * 1e-3) / 1e9,
+                    "streams_per_gpu": B * H},
+        "roofline": {"kernel": "ttt_bwd_kernel", "bound": "tensor", "achieved": bwd_tf, "peak": peak_tf,
+                     "unit": "TFLOP/s", "frac": bwd_tf / peak_tf, "traffic": None,
+                     "peak_source": f"{pk_src} (sustained cuBLAS bf16: kernel timed inside a long step)"},
+        "e2e": {"value": tokens_per_step / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+        "gpu_launches": 2 * K,
+        "clocks": clocks,
+    }
+    return res
+
+
+def cpu_oracle_rate(sample_B, sample_H, NC, cgs, H_full, reps, threads):
+    """tokens/s of the CPU oracle (fwd + hand-derived bwd) on a slice of the workload.
+    A token spans all H_full heads, so a slice with sample_H heads counts sample_H / H_full of it."""
+    from oracle import ttt_mlp as orc
+    torch.set_num_threads(threads)
+    d = orc.make_inputs(sample_B, sample_H, NC, seed=0, backward=True)
+
+    def once():
+        f = orc.ttt_forward(d["XQ"], d["XK"], d["XV"], d["last_eta"], d["ttt_norm_weight"], d["ttt_norm_bias"],
+                            d["W1"], d["b1"], d["W2"], d["b2"], cgs)
+        orc.ttt_backward(d["XQ"], d["XK"], d["XV"], d["last_eta"], d["ttt_norm_weight"], d["ttt_norm_bias"],
+                         f["W1_checkpoints"], f["b1_checkpoints"], f["W2_checkpoints"], f["b2_checkpoints"],
+                         d["grad_L_W1_last"], d["grad_L_b1_last"], d["grad_L_W2_last"], d["grad_L_b2_last"],
+                         d["grad_L_XQW_mini_batch"], cgs)
+
+    with torch.no_grad():
+        once()
+        ts = []
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            once()
+            ts.append(time.perf_counter() - t0)
+    sec = statistics.median(ts)
+    tokens = sample_B * NC * 64 * (sample_H / H_full)
+    return tokens / sec, sec
+
+
+def run_reference(args, rank, world):
+    """The reference arm: its own CPU statement of the path (the oracle), all host threads."""
+    if rank != 0:
+        return None
+    B, H, NC, cgs, desc = WORKLOADS[args.workload]
+    threads = os.cpu_count() or 1
+    sB, sH = 1, min(4, H)
+    K, W = args.steps, args.warmup
+    rate, sec = cpu_oracle_rate(sB, sH, NC, cgs, H, reps=max(1, min(K, 5)), threads=threads)
+    sample = (f"PyTorch-eager fp32 oracle, fwd + hand-derived bwd, slice B={sB} H={sH} of the workload's "
+              f"B={B} H={H} at full sequence (NC={NC}); tokens/s = slice token-heads/s / {H}")
+    return {
+        "impl": "reference", "metric": "ttt_mlp_fwd_bwd_tokens_per_s", "value": rate, "unit": "tokens/s",
+        "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": desc},
+        "cpu_baseline": {"value": rate, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": rate, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        res = run_reference(args, rank, world)
+        if res is not None:
+            print(json.dumps(res), flush=True)
+        return
+
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    res = run_ours(args, rank, world, local_rank)
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            B, H, NC, cgs, _ = WORKLOADS[args.workload]
+            threads = os.cpu_count() or 1
+            sB, sH = 1, min(4, H)
+            rate, sec = cpu_oracle_rate(sB, sH, NC, cgs, H, reps=3, threads=threads)
+            res["cpu_baseline"] = {
+                "value": rate, "unit": "tokens/s", "cores": threads, "kind": "port",
+                "sample": (f"PyTorch-eager fp32 oracle, fwd + hand-derived bwd, slice B={sB} H={sH} at full "
+                           f"sequence (NC={NC}), median of 3 ({sec:.2f} s each); tokens/s = token-heads/s / {H}")}
+        print(json.dumps(res), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -10,34 +10,12 @@ import torch
 
 from oracle import ttt_mlp as orc
 from ttt_tk_b200 import ttt_forward, ttt_backward, take_status
+from ttt_tk_b200.buffers import alloc_backward_buffers, GRAD_NAMES
 
 pytestmark = pytest.mark.gpu
 TOL = 3e-2
-GRADS = ["grad_L_ttt_norm_weight", "grad_L_ttt_norm_bias", "grad_L_W1_init", "grad_L_b1_init",
-         "grad_L_W2_init", "grad_L_b2_init", "grad_L_last_eta", "grad_L_XQ", "grad_L_XK", "grad_L_XV"]
+GRADS = GRAD_NAMES
 CK = ["W1_checkpoints", "b1_checkpoints", "W2_checkpoints", "b2_checkpoints"]
-
-
-def alloc_backward_buffers(B, H, NC, cgs, dev="cuda", fill=float("nan")):
-    """Scratch and output tensors with the reference's shapes (kernels/ttt_backward/matching.py:406-435)."""
-    bf, f32 = torch.bfloat16, torch.float32
-    z = lambda *s, dt=f32: torch.zeros(*s, dtype=dt, device=dev)
-    o = lambda *s, dt=f32: torch.full(s, fill, dtype=dt, device=dev)
-    scratch = [z(B, H, cgs, 64, 256), z(B, H, cgs, 1, 256), z(B, H, cgs, 256, 64), z(B, H, cgs, 1, 64),
-               z(B, H, cgs, 64, 64, dt=bf), z(B, H, cgs, 64, 1),
-               z(B, H, cgs, 64, 256, dt=bf), z(B, H, cgs, 64, 256, dt=bf), z(B, H, cgs, 64, 256, dt=bf),
-               z(B, H, cgs, 64, 256, dt=bf),
-               z(B, H, cgs, 64, 64, dt=bf), z(B, H, cgs, 64, 256, dt=bf), z(B, H, cgs, 64, 64, dt=bf),
-               z(B, H, cgs, 64, 64, dt=bf), z(B, H, cgs, 64, 64, dt=bf), z(B, H, cgs, 64, 1)]
-    outs = {
-        "grad_L_ttt_norm_weight": o(B, H, 1, 64), "grad_L_ttt_norm_bias": o(B, H, 1, 64),
-        "grad_L_W1_init": o(B, H, 64, 256), "grad_L_b1_init": o(B, H, 1, 256),
-        "grad_L_W2_init": o(B, H, 256, 64), "grad_L_b2_init": o(B, H, 1, 64),
-        "grad_L_last_eta": o(B, H, NC, 64, 1, dt=bf),
-        "grad_L_XQ": o(B, H, NC, 64, 64, dt=bf), "grad_L_XK": o(B, H, NC, 64, 64, dt=bf),
-        "grad_L_XV": o(B, H, NC, 64, 64, dt=bf),
-    }
-    return scratch, outs
 
 
 def run_backward(d, ck, cgs):
@@ -45,7 +23,7 @@ def run_backward(d, ck, cgs):
     B, H, NC = d["XQ"].shape[:3]
     t = {k: v.to(dev) for k, v in d.items()}
     ckd = [ck[k].to(dev).float().contiguous() for k in CK]
-    scratch, outs = alloc_backward_buffers(B, H, NC, cgs)
+    scratch, outs = alloc_backward_buffers(B, H, NC, cgs, fill=float("nan"))
     out_fwd = torch.zeros_like(t["XQ"])
     sentinel = out_fwd.clone()
     ret = ttt_backward(t["XQ"], t["XK"], t["XV"], t["last_eta"].unsqueeze(-1).contiguous(),

@@ -88,3 +88,13 @@ def test_forward_rejects_cpu_tensors_and_bad_shapes():
     bad[-1] = 1          # would need 3 checkpoints, tensors hold 2
     with pytest.raises(RuntimeError, match="checkpoint tensors"):
         ops.ttt_forward(*bad)
+
+
+def test_package_input_recipe_equals_the_oracles():
+    from oracle import ttt_mlp as orc
+    from ttt_tk_b200.synthetic import make_inputs
+    a = orc.make_inputs(1, 2, 2, seed=3, eta_scale=0.5, backward=True)
+    b = make_inputs(1, 2, 2, seed=3, eta_scale=0.5, backward=True)
+    assert a.keys() == b.keys()
+    for k in a:
+        assert torch.equal(a[k], b[k]), k
