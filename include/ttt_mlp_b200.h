@@ -140,6 +140,57 @@ int ttt_b200_forward(const ttt_b200_fwd_args* args, void* stream);
 /* Backward: replaces kernels/ttt_backward/ttt.cu:1451-1917 and bwd_ttt_mlp_ker (:179-1443). */
 int ttt_b200_backward(const ttt_b200_bwd_args* args, void* stream);
 
+/* Backward for callers that cannot allocate device memory.  It has no counterpart in the
+ * reference.  Hosts that commit all of HBM to their own pools at start-up (so that a later
+ * cudaMalloc fails or fragments the pool), or that cannot afford the implicit device
+ * synchronisation of an allocation inside a latency-critical loop, cannot provide the sixteen
+ * `*_group` scratch tensors on demand; for them the scratch is a fixed array inside the library
+ * (about 40 MiB, held by every GPU that loads the library's kernels until the process exits).
+ * Inputs, checkpoints, upstream gradients and outputs are passed as for ttt_b200_backward and
+ * the results are the same.
+ *   - Limit: B * H * checkpoint_group_size <= TTT_B200_NOALLOC_MAX_SLOTS; larger problems
+ *     return code 1.
+ *   - The call performs no cudaMalloc / cudaFree / allocating library call.  The first call on
+ *     each device also resolves the array's device address and raises the kernel's
+ *     shared-memory limit: make that first call before any stream capture begins.
+ *   - All calls on a device share the array, which keeps the previous call's contents (nothing
+ *     in it needs to start at zero); calls that overlap on the GPU race on it: serialise them.
+ *   - A device-side wait that ran out (code 3) is reported only by calls with
+ *     TTT_B200_FLAG_SYNC set; without the flag the call returns once the kernel is launched. */
+#define TTT_B200_NOALLOC_MAX_SLOTS 128
+typedef struct ttt_b200_bwd_noalloc_args {
+  const void* XQ;                    /* bf16 [B,H,NC,64,64] */
+  const void* XK;
+  const void* XV;
+  const void* last_eta;              /* bf16 [B,H,NC,64(,1)] */
+  const float* ttt_norm_weight;      /* [H,64] */
+  const float* ttt_norm_bias;        /* [H,64] */
+  const float* W1_checkpoints;       /* [B,H,n,64,256] */
+  const float* b1_checkpoints;       /* [B,H,n,256] */
+  const float* W2_checkpoints;       /* [B,H,n,256,64] */
+  const float* b2_checkpoints;       /* [B,H,n,64] */
+  const float* grad_L_W1_last;       /* [B,H,64,256] */
+  const float* grad_L_b1_last;       /* [B,H,256] */
+  const float* grad_L_W2_last;       /* [B,H,256,64] */
+  const float* grad_L_b2_last;       /* [B,H,64] */
+  const void* grad_L_XQW_mini_batch; /* bf16 [B,H,NC,64,64] */
+  float* grad_L_ttt_norm_weight;     /* [B,H,64] */
+  float* grad_L_ttt_norm_bias;       /* [B,H,64] */
+  float* grad_L_W1_init;             /* [B,H,64,256] */
+  float* grad_L_b1_init;             /* [B,H,256] */
+  float* grad_L_W2_init;             /* [B,H,256,64] */
+  float* grad_L_b2_init;             /* [B,H,64] */
+  void* grad_L_last_eta;             /* bf16 [B,H,NC,64] */
+  void* grad_L_XQ;                   /* bf16 [B,H,NC,64,64] */
+  void* grad_L_XK;
+  void* grad_L_XV;
+  int32_t B, H, NC;
+  int32_t checkpoint_group_size;
+  int32_t num_checkpoints;
+  uint32_t flags;
+} ttt_b200_bwd_noalloc_args;
+int ttt_b200_backward_noalloc(const ttt_b200_bwd_noalloc_args* args, void* stream);
+
 /* Last error text of the calling thread ("" if none). */
 const char* ttt_b200_last_error(void);
 

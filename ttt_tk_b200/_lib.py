@@ -34,7 +34,16 @@ class BwdArgs(ctypes.Structure):
     _fields_ = [(n, c_void_p) for n in BWD_FIELDS] + _DIMS
 
 
-EXPORTS = ["ttt_b200_forward", "ttt_b200_backward", "ttt_b200_last_error", "ttt_b200_take_status",
+# ttt_b200_backward_noalloc: the backward's tensors without `Out` and the sixteen scratch tensors
+BWD_NOALLOC_FIELDS = BWD_FIELDS[:10] + BWD_FIELDS[27:]
+NOALLOC_MAX_SLOTS = 128
+
+
+class BwdNoAllocArgs(ctypes.Structure):
+    _fields_ = [(n, c_void_p) for n in BWD_NOALLOC_FIELDS] + _DIMS
+
+
+EXPORTS = ["ttt_b200_forward", "ttt_b200_backward", "ttt_b200_backward_noalloc", "ttt_b200_last_error", "ttt_b200_take_status",
            "ttt_b200_version", "ttt_b200_umma_selftest"]
 
 FLAG_SYNC = 1
@@ -50,6 +59,8 @@ def load():
     lib.ttt_b200_forward.restype = ctypes.c_int
     lib.ttt_b200_backward.argtypes = [ctypes.POINTER(BwdArgs), c_void_p]
     lib.ttt_b200_backward.restype = ctypes.c_int
+    lib.ttt_b200_backward_noalloc.argtypes = [ctypes.POINTER(BwdNoAllocArgs), c_void_p]
+    lib.ttt_b200_backward_noalloc.restype = ctypes.c_int
     lib.ttt_b200_last_error.argtypes = []
     lib.ttt_b200_last_error.restype = ctypes.c_char_p
     lib.ttt_b200_take_status.argtypes = []

@@ -39,6 +39,8 @@
 //
 // Deviations from the reference kernel (see include/ttt_mlp_b200.h): outputs are overwritten,
 // not accumulated; `Out` is never touched.  Every wait is bounded.
+#include <mutex>
+
 #include "ttt_device.cuh"
 #include "ttt_internal.h"
 
@@ -1115,5 +1117,164 @@ int ttt_launch_backward(const ttt_b200_bwd_args* a, cudaStream_t stream, uint32_
   ttt_bwd_kernel<<<dim3(a->B * a->H), dim3(kThreads), SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmGo, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
+  return TTT_B200_OK;
+}
+
+// =============================================================================================
+// Backward entry point that allocates no device memory.
+//
+// Some hosts of this library cannot let it call cudaMalloc (or hand it freshly allocated
+// scratch): inference servers and training loops that pre-commit all of HBM to their own
+// pools at start-up, so a later allocation fails or fragments the pool; and latency-critical
+// loops for which the implicit device synchronisation of an allocation is not acceptable.
+// For them the per-mini-batch scratch of the backward lives in the fixed array below instead
+// of the caller's sixteen `*_group` tensors.  The array is part of the library image: every
+// GPU on which the library's kernels are loaded holds it until the process exits.
+//
+// Capacity: B * H * checkpoint_group_size <= TTT_B200_NOALLOC_MAX_SLOTS scratch slots of
+// 328 192 bytes (about 40 MiB in total).  Larger problems are rejected with code 1.
+//
+// All calls on a device share the array.  Nothing in it has to start at zero (each slot is
+// written before it is read within one call) and it keeps the previous call's contents; two
+// calls that overlap on the GPU (different streams) race on it and must be serialised by the
+// caller.  The first call on each device looks up the array's device address (the name of a
+// __device__ array is only a host-side handle in host code), raises the kernel's shared-memory
+// limit and resolves the tensor-map encoder; make that first call outside any stream capture.
+namespace {
+
+constexpr size_t NA_SLOTS = TTT_B200_NOALLOC_MAX_SLOTS;
+constexpr size_t NA_OFF_W1 = 0;
+constexpr size_t NA_OFF_W2 = NA_OFF_W1 + NA_SLOTS * 65536;
+constexpr size_t NA_OFF_Z1 = NA_OFF_W2 + NA_SLOTS * 65536;
+constexpr size_t NA_OFF_X2 = NA_OFF_Z1 + NA_SLOTS * BIG;
+constexpr size_t NA_OFF_GZ1 = NA_OFF_X2 + NA_SLOTS * BIG;
+constexpr size_t NA_OFF_Z1B = NA_OFF_GZ1 + NA_SLOTS * BIG;
+constexpr size_t NA_OFF_X2B = NA_OFF_Z1B + NA_SLOTS * BIG;
+constexpr size_t NA_OFF_XHF = NA_OFF_X2B + NA_SLOTS * BIG;
+constexpr size_t NA_OFF_GOF = NA_OFF_XHF + NA_SLOTS * TILE;
+constexpr size_t NA_OFF_GZ2 = NA_OFF_GOF + NA_SLOTS * TILE;
+constexpr size_t NA_OFF_XHLN = NA_OFF_GZ2 + NA_SLOTS * TILE;
+constexpr size_t NA_OFF_SIGF = NA_OFF_XHLN + NA_SLOTS * TILE;
+constexpr size_t NA_OFF_SIGLN = NA_OFF_SIGF + NA_SLOTS * 256;
+constexpr size_t NA_BYTES = NA_OFF_SIGLN + NA_SLOTS * 256;
+static_assert(NA_BYTES == NA_SLOTS * 328192, "scratch slot size changed: update the header comment");
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NA_BYTES];
+static __device__ __align__(16) uint32_t g_noalloc_status;
+
+struct NoAllocDevice {
+  uint8_t* scratch = nullptr;
+  uint32_t* status = nullptr;
+  bool ready = false;
+};
+NoAllocDevice g_noalloc_dev[64];
+
+// Once per device, with that device current: device addresses of the two symbols.
+int noalloc_setup(int dev) {
+  NoAllocDevice& d = g_noalloc_dev[dev];
+  if (d.ready) return TTT_B200_OK;
+  void* ptr = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+  if (e != cudaSuccess || ptr == nullptr)
+    return ttt_set_error(TTT_B200_ERR_LAUNCH, e != cudaSuccess ? cudaGetErrorString(e) : "scratch symbol has no address");
+  d.scratch = static_cast<uint8_t*>(ptr);
+  e = cudaGetSymbolAddress(&ptr, g_noalloc_status);
+  if (e != cudaSuccess || ptr == nullptr)
+    return ttt_set_error(TTT_B200_ERR_LAUNCH, e != cudaSuccess ? cudaGetErrorString(e) : "status symbol has no address");
+  d.status = static_cast<uint32_t*>(ptr);
+  e = cudaFuncSetAttribute(ttt_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
+  d.ready = true;
+  return TTT_B200_OK;
+}
+
+}  // namespace
+
+extern "C" int ttt_b200_backward_noalloc(const ttt_b200_bwd_noalloc_args* a, void* stream_) {
+  if (a == nullptr) return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "args is NULL");
+  if (a->B < 1 || a->H < 1 || a->NC < 1 || a->checkpoint_group_size < 1)
+    return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "B, H, NC and checkpoint_group_size must be >= 1");
+  if (a->num_checkpoints != (a->NC + a->checkpoint_group_size - 1) / a->checkpoint_group_size)
+    return ttt_set_error(TTT_B200_ERR_BAD_ARGS,
+                         "checkpoint tensors must hold ceil(NC / checkpoint_group_size) states");
+  if (static_cast<uint64_t>(a->B) * a->H * a->NC * 64 >= (1ull << 31))
+    return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "B*H*NC*64 must be below 2^31");
+  const uint64_t slots = static_cast<uint64_t>(a->B) * a->H * a->checkpoint_group_size;
+  if (slots > NA_SLOTS)
+    return ttt_set_error(TTT_B200_ERR_BAD_ARGS,
+                         "B*H*checkpoint_group_size exceeds TTT_B200_NOALLOC_MAX_SLOTS (the built-in scratch); "
+                         "use ttt_b200_backward with caller-provided scratch");
+  const void* ptrs[] = {a->XQ, a->XK, a->XV, a->last_eta, a->ttt_norm_weight, a->ttt_norm_bias,
+                        a->W1_checkpoints, a->b1_checkpoints, a->W2_checkpoints, a->b2_checkpoints,
+                        a->grad_L_W1_last, a->grad_L_b1_last, a->grad_L_W2_last, a->grad_L_b2_last,
+                        a->grad_L_XQW_mini_batch, a->grad_L_ttt_norm_weight, a->grad_L_ttt_norm_bias,
+                        a->grad_L_W1_init, a->grad_L_b1_init, a->grad_L_W2_init, a->grad_L_b2_init,
+                        a->grad_L_last_eta, a->grad_L_XQ, a->grad_L_XK, a->grad_L_XV};
+  for (const void* q : ptrs) {
+    if (q == nullptr) return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "a required tensor pointer is NULL");
+    if (reinterpret_cast<uintptr_t>(q) & 15u)
+      return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "tensor pointers must be 16-byte aligned");
+  }
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
+  if (dev < 0 || dev >= 64) return ttt_set_error(TTT_B200_ERR_LAUNCH, "device index out of range");
+  static std::mutex mu;
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    if (int rc = noalloc_setup(dev)) return rc;
+  }
+  const NoAllocDevice& d = g_noalloc_dev[dev];
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+
+  const uint64_t rows = static_cast<uint64_t>(a->B) * a->H * a->NC * 64;
+  CUtensorMap tmQ, tmK, tmV, tmGo;
+  if (int rc = ttt_make_tile_map(&tmQ, a->XQ, rows)) return rc;
+  if (int rc = ttt_make_tile_map(&tmK, a->XK, rows)) return rc;
+  if (int rc = ttt_make_tile_map(&tmV, a->XV, rows)) return rc;
+  if (int rc = ttt_make_tile_map(&tmGo, a->grad_L_XQW_mini_batch, rows)) return rc;
+  BwdParams p;
+  p.eta = static_cast<const __nv_bfloat16*>(a->last_eta);
+  p.gamma = a->ttt_norm_weight;
+  p.beta = a->ttt_norm_bias;
+  p.W1c = a->W1_checkpoints; p.b1c = a->b1_checkpoints; p.W2c = a->W2_checkpoints; p.b2c = a->b2_checkpoints;
+  p.sc_W1 = d.scratch + NA_OFF_W1;
+  p.sc_W2 = d.scratch + NA_OFF_W2;
+  p.sc_Z1 = d.scratch + NA_OFF_Z1;
+  p.sc_X2 = d.scratch + NA_OFF_X2;
+  p.sc_gZ1 = d.scratch + NA_OFF_GZ1;
+  p.sc_Z1b = d.scratch + NA_OFF_Z1B;
+  p.sc_X2b = d.scratch + NA_OFF_X2B;
+  p.sc_xhf = d.scratch + NA_OFF_XHF;
+  p.sc_gof = d.scratch + NA_OFF_GOF;
+  p.sc_gZ2 = d.scratch + NA_OFF_GZ2;
+  p.sc_xhln = d.scratch + NA_OFF_XHLN;
+  p.sc_sigf = reinterpret_cast<float*>(d.scratch + NA_OFF_SIGF);
+  p.sc_sigln = reinterpret_cast<float*>(d.scratch + NA_OFF_SIGLN);
+  p.gW1_last = a->grad_L_W1_last; p.gb1_last = a->grad_L_b1_last;
+  p.gW2_last = a->grad_L_W2_last; p.gb2_last = a->grad_L_b2_last;
+  p.d_gamma = a->grad_L_ttt_norm_weight; p.d_beta = a->grad_L_ttt_norm_bias;
+  p.gW1 = a->grad_L_W1_init; p.gb1 = a->grad_L_b1_init; p.gW2 = a->grad_L_W2_init; p.gb2 = a->grad_L_b2_init;
+  p.d_eta = static_cast<__nv_bfloat16*>(a->grad_L_last_eta);
+  p.dXQ = static_cast<uint8_t*>(a->grad_L_XQ);
+  p.dXK = static_cast<uint8_t*>(a->grad_L_XK);
+  p.dXV = static_cast<uint8_t*>(a->grad_L_XV);
+  p.H = a->H; p.NC = a->NC; p.cgs = a->checkpoint_group_size; p.nck = a->num_checkpoints;
+  p.status = d.status;
+  p.wait_limit_ns = 2000ull * 1000 * 1000;
+  // the status word is shared like the scratch: it must read zero when this launch starts
+  e = cudaMemsetAsync(d.status, 0, sizeof(uint32_t), stream);
+  if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
+  ttt_bwd_kernel<<<dim3(a->B * a->H), dim3(kThreads), SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmGo, p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
+  if (a->flags & TTT_B200_FLAG_SYNC) {
+    uint32_t st = 0;
+    e = cudaMemcpyAsync(&st, d.status, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
+    if (st != 0)
+      return ttt_set_error(TTT_B200_ERR_TIMEOUT, "a device-side bounded wait ran out; results are invalid");
+  }
   return TTT_B200_OK;
 }
