@@ -34,7 +34,8 @@ WORKLOADS = {
     "c2": (4, 32, 128, 8, "configs[2]: fwd+bwd, B=4 H=32 seq=8192 (NC=128) cgs=8, per GPU"),
     "c1": (4, 12, 32, 4, "configs[1] shape run fwd+bwd, B=4 H=12 seq=2048 (NC=32) cgs=4, per GPU"),
     "c0": (1, 4, 32, 4, "configs[0] shape, B=1 H=4 seq=2048 (NC=32) cgs=4"),
-    "small": (1, 8, 16, 4, "small case for profiling, B=1 H=8 seq=1024 cgs=4"),
+    "small": (1, 8, 16, 4, "small case, B=1 H=8 seq=1024 cgs=4"),
+    "prof": (4, 32, 16, 8, "profiling case: configs[2] streams (B=4 H=32) at seq=1024 (NC=16) cgs=8"),
 }
 U_FLOP = 2 * 64 * 64 * 256            # one GEMM unit per mini-batch per (b,h)
 FWD_U, BWD_U = 7, 22                  # algorithmic GEMM units: forward; backward (7 recompute + 15 sweep)
