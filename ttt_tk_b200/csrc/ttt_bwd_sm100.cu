@@ -50,6 +50,25 @@ namespace {
 
 constexpr int kThreads = 256;
 
+// Optional timeline of CTA 0 (compile with -DTTT_STAMPS): thread 0 records the global timer
+// whenever a wait or a publish step returns.  Off in the shipped library.
+#ifdef TTT_STAMPS
+__device__ unsigned long long g_ttt_stamps[16384];
+__device__ unsigned int g_ttt_nstamps;
+#define TTT_STAMP(id)                                                            \
+  do {                                                                           \
+    if (threadIdx.x == 0 && blockIdx.x == 0) {                                   \
+      const unsigned n_ = g_ttt_nstamps;                                         \
+      if (n_ < 16384) {                                                          \
+        g_ttt_stamps[n_] = (globaltimer_ns() << 8) | (unsigned long long)(id);   \
+        g_ttt_nstamps = n_ + 1;                                                  \
+      }                                                                          \
+    }                                                                            \
+  } while (0)
+#else
+#define TTT_STAMP(id)
+#endif
+
 // ---- shared memory map (offsets from a 1024-byte aligned base)
 constexpr uint32_t OFF_BIG = 0;                      // 5 hidden-major buffers of 32 KB
 constexpr uint32_t OFF_T = 5 * BIG;                  // 7 token tiles of 8 KB
@@ -173,6 +192,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       ph ^= 1u << b;
       pending &= ~(1u << b);
     }
+    TTT_STAMP(0x40 + b);
   };
   auto wait_mma = [&]() {
     wait_bar(BAR_MMA);
@@ -180,9 +200,10 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     tc_fence_after_sync();
   };
   auto publish = [&]() {
-    asm volatile("fence.proxy.async;" ::: "memory");   // generic writes (shared and global) -> async proxy
+    fence_proxy_async_smem();   // generic-proxy writes to shared memory -> async proxy (MMA, bulk copies)
     tc_fence_before_sync();
     __syncthreads();
+    TTT_STAMP(0x10);
   };
   auto commit = [&]() { umma_commit(&bars[BAR_MMA]); };   // thread 0
   // thread 0: bulk-load helpers
@@ -244,7 +265,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       const float* W2g = p.W2c + (sid * p.nck + ck) * (256 * 64) + hrow * 64;
       uint8_t* g1 = p.sc_W1 + slot0 * 65536;
       uint8_t* g2 = p.sc_W2 + slot0 * 65536;
-#pragma unroll
+#pragma unroll 1
       for (int half = 0; half < 2; ++half) {
         uint32_t v[32];
         float f[32];
@@ -301,7 +322,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       {
         uint8_t* gZ1 = p.sc_Z1 + slot * BIG;
         uint8_t* gX2 = p.sc_X2 + slot * BIG;
-#pragma unroll
+#pragma unroll 1
         for (int half = 0; half < 2; ++half) {
           uint32_t v[32];
           tmem_ld32(tmem + lane_base + TM_A + wg * 64 + half * 32, v);
@@ -421,7 +442,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       {
         uint8_t* gG1 = p.sc_gZ1 + slot * BIG;
         float bsum = 0.f;
-#pragma unroll
+#pragma unroll 1
         for (int half = 0; half < 2; ++half) {
           uint32_t v[32];
           tmem_ld32(tmem + lane_base + TM_A + wg * 64 + half * 32, v);
@@ -461,7 +482,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const bool keep = (j + 1 < gsz);
         uint8_t* g1 = p.sc_W1 + (slot + 1) * 65536;
         uint8_t* g2 = p.sc_W2 + (slot + 1) * 65536;
-#pragma unroll
+#pragma unroll 1
         for (int half = 0; half < 2; ++half) {
           uint32_t v[32];
           float f[32];
@@ -501,7 +522,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       {
         uint8_t* gZ1b = p.sc_Z1b + slot * BIG;
         uint8_t* gX2b = p.sc_X2b + slot * BIG;
-#pragma unroll
+#pragma unroll 1
         for (int half = 0; half < 2; ++half) {
           uint32_t v[32];
           tmem_ld32(tmem + lane_base + TM_A + wg * 64 + half * 32, v);
@@ -575,7 +596,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // ================================================================== reverse sweep
     // dL/dW state: global (fp32) -> tensor memory
     {
-#pragma unroll
+#pragma unroll 1
       for (int half = 0; half < 2; ++half) {
         uint32_t v[32];
 #pragma unroll
@@ -601,32 +622,44 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     uint8_t* t_k = tile(4);
     uint8_t* t_gz2 = tile(5);
     uint8_t* t_xf = tile(6);    // x_hat_fused
-    auto issue_step_loads = [&](int j) {   // thread 0: everything step j can ask for up front
+    // thread 0: loads of sweep step j, in three parts so that each can go out as early as its
+    // destination is free (token tiles first: the step starts with them)
+    auto issue_tiles_a = [&](int j) {          // dL/dOut, x_hat_ln + std_ln, x_hat_fused + std_fused
       const long slot = slot0 + j;
       const int row0 = static_cast<int>(tok_rows0 + (long)(i0 + j) * 64);
-      load_big(ib2, p.sc_Z1b + slot * BIG);
-      load_big(ib3, p.sc_X2b + slot * BIG);
-      load_big(ib4, p.sc_gZ1 + slot * BIG);
       mbar_expect_tx(&bars[BAR_T + 0], TILE);
       tma_load_2d(t_go, &tmGo, &bars[BAR_T + 0], 0, row0);
       mbar_expect_tx(&bars[BAR_T + 1], TILE + 256);
       bulk_load_1d(t_a, p.sc_xhln + slot * TILE, TILE, &bars[BAR_T + 1]);
       bulk_load_1d(sSigLn, p.sc_sigln + slot * 64, 256, &bars[BAR_T + 1]);
-      mbar_expect_tx(&bars[BAR_T + 2], TILE);
-      tma_load_2d(t_q, &tmQ, &bars[BAR_T + 2], 0, row0);
-      mbar_expect_tx(&bars[BAR_T + 4], TILE + 128);
-      tma_load_2d(t_k, &tmK, &bars[BAR_T + 4], 0, row0);
-      bulk_load_1d(sEta, p.eta + (sid * NC + i0 + j) * 64, 128, &bars[BAR_T + 4]);
-      mbar_expect_tx(&bars[BAR_T + 5], TILE);
-      bulk_load_1d(t_gz2, p.sc_gZ2 + slot * TILE, TILE, &bars[BAR_T + 5]);
       mbar_expect_tx(&bars[BAR_T + 6], TILE + 256);
       bulk_load_1d(t_xf, p.sc_xhf + slot * TILE, TILE, &bars[BAR_T + 6]);
       bulk_load_1d(sSigF, p.sc_sigf + slot * 64, 256, &bars[BAR_T + 6]);
-      pending |= (1u << (BAR_T + 0)) | (1u << (BAR_T + 1)) | (1u << (BAR_T + 2)) | (1u << (BAR_T + 4)) |
-                 (1u << (BAR_T + 5)) | (1u << (BAR_T + 6));
+      pending |= (1u << (BAR_T + 0)) | (1u << (BAR_T + 1)) | (1u << (BAR_T + 6));
     };
+    auto issue_rest = [&](int j) {             // Q, K + eta, dl/dZ2 tiles; X2_bar and dl/dZ1
+      const long slot = slot0 + j;
+      const int row0 = static_cast<int>(tok_rows0 + (long)(i0 + j) * 64);
+      mbar_expect_tx(&bars[BAR_T + 2], TILE);
+      tma_load_2d(t_q, &tmQ, &bars[BAR_T + 2], 0, row0);
+      load_big(ib3, p.sc_X2b + slot * BIG);
+      mbar_expect_tx(&bars[BAR_T + 4], TILE + 128);
+      tma_load_2d(t_k, &tmK, &bars[BAR_T + 4], 0, row0);
+      bulk_load_1d(sEta, p.eta + (sid * NC + i0 + j) * 64, 128, &bars[BAR_T + 4]);
+      load_big(ib4, p.sc_gZ1 + slot * BIG);
+      mbar_expect_tx(&bars[BAR_T + 5], TILE);
+      bulk_load_1d(t_gz2, p.sc_gZ2 + slot * TILE, TILE, &bars[BAR_T + 5]);
+      pending |= (1u << (BAR_T + 2)) | (1u << (BAR_T + 4)) | (1u << (BAR_T + 5));
+    };
+    // scratch was written with generic-proxy stores by all threads: order them before the
+    // bulk (async-proxy) copies that read it back
+    asm volatile("fence.proxy.async;" ::: "memory");
     publish();
-    if (tid == 0) issue_step_loads(gsz - 1);
+    if (tid == 0) {
+      issue_tiles_a(gsz - 1);
+      load_big(ib2, p.sc_Z1b + (slot0 + gsz - 1) * BIG);
+      issue_rest(gsz - 1);
+    }
 
     for (int j = gsz - 1; j >= 0; --j) {
       const long slot = slot0 + j;
@@ -688,7 +721,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       {
         uint8_t* bz = big(ib2);
         float bsum = 0.f;
-#pragma unroll
+#pragma unroll 1
         for (int half = 0; half < 2; ++half) {
           uint32_t v[32];
           tmem_ld32(tmem + lane_base + TM_A + wg * 64 + half * 32, v);
@@ -722,7 +755,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       {
         uint8_t* s1b = big(ib0);
         uint8_t* s2b = big(ib1);
-#pragma unroll
+#pragma unroll 1
         for (int half = 0; half < 2; ++half) {
           uint32_t v[32];
           float f[32];
@@ -743,7 +776,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       if (wg == 0) {
         uint4* dst = reinterpret_cast<uint4*>(p.dXQ + grow * 128);
-#pragma unroll
+#pragma unroll 1
         for (int half = 0; half < 2; ++half) {
           uint32_t v[32];
           tmem_ld32(tmem + lane_base + TM_B + half * 32, v);
@@ -791,7 +824,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         uint8_t* bz = big(ib2);
         uint8_t* bp = big(ib4);
         uint8_t* bgp = big(ib0);
-#pragma unroll
+#pragma unroll 1
         for (int half = 0; half < 2; ++half) {
           uint32_t v[32];
           tmem_ld32(tmem + lane_base + TM_A + wg * 64 + half * 32, v);
@@ -956,12 +989,14 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         sDB[f] -= colsum(t_go, f);
       }
       wait_mma();
+      // the state-gradient snapshot buffer is free: bring the next step's Z1_bar into it
+      if (tid == 0 && j > 0) load_big(ib1, p.sc_Z1b + (slot - 1) * BIG);
       // ---- E5: gZ1in^T = gX2^T gelu'(Z1^T) + R^T S^T, in place over S^T
       {
         uint8_t* bs = big(ib2);
         const uint8_t* bgp = big(ib0);
         float bsum = 0.f;
-#pragma unroll
+#pragma unroll 1
         for (int half = 0; half < 2; ++half) {
           uint32_t v[32], w[32];
           tmem_ld32(tmem + lane_base + TM_B + wg * 64 + half * 32, v);
@@ -983,7 +1018,10 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         Gb1 += bsum;
       }
       publish();
-      if (tid == 0) load_big(ib0, p.sc_X2 + slot * BIG);
+      if (tid == 0) {
+        load_big(ib0, p.sc_X2 + slot * BIG);
+        if (j > 0) issue_tiles_a(j - 1);
+      }
       wait_bar(BAR_BIG + ib4);
       wait_bar(BAR_BIG + ib0);
       if (tid == 0) {
@@ -997,7 +1035,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       // ---- E6: dK = partial + gZ1in W1^T
       if (wg == 0) {
         uint4* dKp = reinterpret_cast<uint4*>(p.dXK + grow * 128);
-#pragma unroll
+#pragma unroll 1
         for (int half = 0; half < 2; ++half) {
           uint32_t v[32];
           tmem_ld32(tmem + lane_base + TM_A + half * 32, v);
@@ -1017,10 +1055,10 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
       // pre-update weights of this mini-batch are the post-update weights of the previous one
       {
-        const int n0 = ib4, n1 = ib3, n2 = ib2, n3 = ib1, n4 = ib0;
+        const int n0 = ib4, n1 = ib3, n2 = ib1, n3 = ib2, n4 = ib0;
         ib0 = n0; ib1 = n1; ib2 = n2; ib3 = n3; ib4 = n4;
       }
-      if (tid == 0 && j > 0 && !*abort_flag) issue_step_loads(j - 1);
+      if (tid == 0 && j > 0 && !*abort_flag) issue_rest(j - 1);
       if (*abort_flag) { aborted = true; break; }
     }
     if (aborted) break;
@@ -1028,7 +1066,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // ---- park the gradient state (tensor memory -> grad_L_W*_init); the last group leaves the result
     {
       __syncwarp();
-#pragma unroll
+#pragma unroll 1
       for (int half = 0; half < 2; ++half) {
         uint32_t v[32];
         tmem_ld32(tmem + lane_base + TM_S1 + wg * 64 + half * 32, v);
@@ -1278,3 +1316,18 @@ extern "C" int ttt_b200_backward_noalloc(const ttt_b200_bwd_noalloc_args* a, voi
   }
   return TTT_B200_OK;
 }
+
+#ifdef TTT_STAMPS
+// Debug builds only: copy out and reset the timeline of CTA 0 (entries: time_ns << 8 | id).
+extern "C" int ttt_b200_debug_stamps(unsigned long long* out, int max_entries) {
+  unsigned int n = 0;
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(&n, g_ttt_nstamps, sizeof(n));
+  if (n > 16384) n = 16384;
+  if ((int)n > max_entries) n = max_entries;
+  cudaMemcpyFromSymbol(out, g_ttt_stamps, n * sizeof(unsigned long long));
+  const unsigned int zero = 0;
+  cudaMemcpyToSymbol(g_ttt_nstamps, &zero, sizeof(zero));
+  return (int)n;
+}
+#endif

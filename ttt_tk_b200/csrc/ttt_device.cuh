@@ -73,32 +73,63 @@ __device__ __forceinline__ float ld_elem(const uint8_t* tile, uint32_t row, uint
       *reinterpret_cast<const __nv_bfloat16*>(tile + sw128_off(row, col >> 3) + (col & 7) * 2));
 }
 
+// ---- MMA issue.  One thread issues every MMA of the kernels, so the instruction stream
+// around each tcgen05.mma is kept to two integer adds: the descriptors' high words are the
+// same constant for every operand (stride byte offset 1024, version 1, 128-byte swizzle) and
+// the low words (start address | leading byte offset) advance by a constant per K step.
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return ((smem_addr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16);
+}
+template <bool kAccumulate>
+__device__ __forceinline__ void mma_issue(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %4};\n\t"
+      "mov.b64 db, {%2, %4};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}" ::"r"(tmem_d),
+      "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(kDescHi), "n"(kAccumulate ? 1 : 0)
+      : "memory");
+}
+
 // "Hidden-major" product: D[256 x 64] (two M=128 blocks, 64 fp32 columns each, at tmem_d and
 // tmem_d + 64) (+)= A * B with A a [256][64] bf16 tile read K-major (row = hidden unit) and B a
 // [64][64] tile read K-major (row = N index) or MN-major (row = K index).
-__device__ __forceinline__ void mma_hidden_major(uint32_t tmem_d, uint32_t a_smem, uint32_t b_smem, bool b_mn,
-                                                 bool accumulate) {
-  const uint32_t idesc = umma_idesc_bf16(128, 64, false, b_mn, false);
+template <bool kBMn, bool kAccumulate>
+__device__ __forceinline__ void mma_hidden_major_t(uint32_t tmem_d, uint32_t a_smem, uint32_t b_smem) {
+  constexpr uint32_t idesc = umma_idesc_bf16(128, 64, false, kBMn, false);
+  const uint32_t a0 = desc_lo(a_smem, 16);
+  const uint32_t b0 = desc_lo(b_smem, kBMn ? 8192 : 16);
+  constexpr uint32_t bstep = kBMn ? (2048u >> 4) : (32u >> 4);
 #pragma unroll
   for (int blk = 0; blk < 2; ++blk) {
+    if (kAccumulate) mma_issue<true>(tmem_d + blk * 64, a0 + blk * (16384u >> 4), b0, idesc);
+    else             mma_issue<false>(tmem_d + blk * 64, a0 + blk * (16384u >> 4), b0, idesc);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint64_t ad = umma_desc_sw128(a_smem + blk * 16384 + j * 32, 16);
-      const uint64_t bd = umma_desc_sw128(b_smem + (b_mn ? j * 2048 : j * 32), b_mn ? 8192 : 16);
-      umma_bf16_ss(tmem_d + blk * 64, ad, bd, idesc, (accumulate || j) ? 1u : 0u);
-    }
+    for (int j = 1; j < 4; ++j)
+      mma_issue<true>(tmem_d + blk * 64, a0 + blk * (16384u >> 4) + j * 2, b0 + j * bstep, idesc);
+  }
+}
+__device__ __forceinline__ void mma_hidden_major(uint32_t tmem_d, uint32_t a_smem, uint32_t b_smem, bool b_mn,
+                                                 bool accumulate) {
+  if (b_mn) {
+    if (accumulate) mma_hidden_major_t<true, true>(tmem_d, a_smem, b_smem);
+    else            mma_hidden_major_t<true, false>(tmem_d, a_smem, b_smem);
+  } else {
+    if (accumulate) mma_hidden_major_t<false, true>(tmem_d, a_smem, b_smem);
+    else            mma_hidden_major_t<false, false>(tmem_d, a_smem, b_smem);
   }
 }
 // "Token-major" product: D[64 tok x 64] (M = 64: row r in TMEM lane (r % 16) + 32 * (r / 16))
 // = X[64 x 256] * W[256 x 64], both operands [256][64] tiles read MN-major (row = hidden unit).
 __device__ __forceinline__ void mma_token_major(uint32_t tmem_d, uint32_t x_smem, uint32_t w_smem) {
-  const uint32_t idesc = umma_idesc_bf16(64, 64, true, true, false);
+  constexpr uint32_t idesc = umma_idesc_bf16(64, 64, true, true, false);
+  const uint32_t a0 = desc_lo(x_smem, BIG);
+  const uint32_t b0 = desc_lo(w_smem, BIG);
+  mma_issue<false>(tmem_d, a0, b0, idesc);
 #pragma unroll
-  for (int j = 0; j < 16; ++j) {
-    const uint64_t ad = umma_desc_sw128(x_smem + j * 2048, BIG);
-    const uint64_t bd = umma_desc_sw128(w_smem + j * 2048, BIG);
-    umma_bf16_ss(tmem_d, ad, bd, idesc, j ? 1u : 0u);
-  }
+  for (int j = 1; j < 16; ++j) mma_issue<true>(tmem_d, a0 + j * (2048u >> 4), b0 + j * (2048u >> 4), idesc);
 }
 
 }  // namespace tttdev

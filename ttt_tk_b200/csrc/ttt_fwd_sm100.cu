@@ -158,7 +158,7 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   {
     const float* W1g = p.W1 + stream_id * (64 * 256);
     const float* W2g = p.W2 + stream_id * (256 * 64) + hrow * 64;
-#pragma unroll
+#pragma unroll 1
     for (int half = 0; half < 2; ++half) {
       uint32_t v[32];
       float f[32];
@@ -191,7 +191,7 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   // fp32 state (tensor memory, registers, shared memory) -> global, reference layouts
   auto store_state = [&](float* W1o, float* b1o, float* W2o, float* b2o) {
     __syncwarp();
-#pragma unroll
+#pragma unroll 1
     for (int half = 0; half < 2; ++half) {
       uint32_t v[32];
       tmem_ld32(tmem + lane_base + TM_W1 + wg * 64 + half * 32, v);
@@ -249,7 +249,7 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
     wait_mma();
     // ---- EPI1: X2^T = gelu(Z1^T + b1), G' = gelu'(Z1^T + b1)
-#pragma unroll
+#pragma unroll 1
     for (int half = 0; half < 2; ++half) {
       uint32_t v[32];
       tmem_ld32(tmem + lane_base + TM_A + wg * 64 + half * 32, v);
@@ -349,7 +349,7 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // ---- EPI3: U1^T = R^T * G' (= -eta dl/dZ1), b1 += row sum
     {
       float bsum = 0.f;
-#pragma unroll
+#pragma unroll 1
       for (int half = 0; half < 2; ++half) {
         uint32_t v[32];
         tmem_ld32(tmem + lane_base + TM_A + wg * 64 + half * 32, v);
@@ -379,7 +379,7 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
     wait_mma();
     // ---- EPI4: refresh the bf16 operand copies of the state
-#pragma unroll
+#pragma unroll 1
     for (int half = 0; half < 2; ++half) {
       uint32_t v[32];
       float f[32];
@@ -406,7 +406,7 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
     wait_mma();
     // ---- EPI5: X2b^T = gelu(Z1b^T + b1)
-#pragma unroll
+#pragma unroll 1
     for (int half = 0; half < 2; ++half) {
       uint32_t v[32];
       tmem_ld32(tmem + lane_base + TM_A + wg * 64 + half * 32, v);
