@@ -204,9 +204,10 @@ int ttt_b200_version(void);
 /* Diagnostics (no counterpart in the reference): one CTA computes
  * D[M,N] = (+/-)A[M,K] * B[N,K]^T, `repeat` times accumulated, through the same shared-memory
  * descriptors, instruction descriptors and tensor-memory mapping as the operator kernels.
- * A, B, D are fp32 device arrays (operands are rounded to bf16).  Synchronises. */
+ * A, B, D are fp32 device arrays (operands are rounded to bf16).  repeat_and_mode: bits 0..7 the
+ * repeat count, bit 8 = read the M = 64 result back with the 16x256b fragment loads.  Synchronises. */
 int ttt_b200_umma_selftest(const float* A, const float* B, float* D, int M, int N, int K, int a_mn, int b_mn,
-                           int neg_a, int repeat, void* stream);
+                           int neg_a, int repeat_and_mode, void* stream);
 
 #ifdef __cplusplus
 }

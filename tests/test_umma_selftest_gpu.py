@@ -17,6 +17,8 @@ CASES = [
     (64, 64, 64, 0, 0, 0, 1),    # M = 64 tensor-memory lane mapping, K-major
     (128, 64, 256, 1, 1, 0, 1),  # MN-major A spanning two 64-blocks (leading byte offset)
     (128, 128, 128, 0, 0, 0, 1),
+    (64, 64, 256, 1, 1, 0, 1 | 256),   # same product, result read back as 16x256b fragments
+    (64, 64, 64, 0, 0, 1, 2 | 256),
 ]
 
 
@@ -31,6 +33,6 @@ def test_umma_forms(M, N, K, a_mn, b_mn, neg, rep):
                                     ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     assert rc == 0, lib.ttt_b200_last_error()
     torch.cuda.synchronize()
-    want = (A.double() @ B.double().T) * rep * (-1 if neg else 1)
+    want = (A.double() @ B.double().T) * (rep & 0xff) * (-1 if neg else 1)
     err = (D.double() - want).abs().max().item()
     assert err < 1e-3 * K ** 0.5, f"max abs err {err}"

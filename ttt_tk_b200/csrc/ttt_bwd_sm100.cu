@@ -85,7 +85,8 @@ constexpr uint32_t OFF_PART = OFF_GB1 + 1024;        // fp32[4][64] partial sums
 constexpr uint32_t OFF_ETA = OFF_PART + 1024;        // bf16[2][64]
 constexpr uint32_t OFF_BAR = OFF_ETA + 256;          // 16 mbarriers
 constexpr uint32_t OFF_MISC = OFF_BAR + 128;
-constexpr uint32_t SMEM_USED = OFF_MISC + 64;
+constexpr uint32_t OFF_XCH = OFF_MISC + 64;        // fp32[2][64][8] row-sum exchange between warp pairs
+constexpr uint32_t SMEM_USED = OFF_XCH + 4096;
 constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;
 static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB per-CTA shared memory of sm_100");
 
@@ -126,7 +127,8 @@ struct BwdParams {
 __global__ void __launch_bounds__(kThreads, 1)
 ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmGo,
-               const BwdParams p) {
+               const __grid_constant__ CUtensorMap tmDQ, const __grid_constant__ CUtensorMap tmDK,
+               const __grid_constant__ CUtensorMap tmDV, const BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -134,8 +136,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const int quad = warp & 3, wg = warp >> 2;
   const int hrow = wg * 128 + quad * 32 + lane;
   const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
-  const int tok = quad * 16 + (lane & 15);
-  const bool tok_valid = (wg == 0) && (lane < 16);
+  const TokMap tm(warp, lane);          // this thread's fragment of the 64 x 64 token-major tiles
   const long sid = blockIdx.x;
   const int head = static_cast<int>(sid % p.H);
   const int NC = p.NC, cgs = p.cgs;
@@ -154,6 +155,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   float* sPart = reinterpret_cast<float*>(smem + OFF_PART);
   __nv_bfloat16* sEta = reinterpret_cast<__nv_bfloat16*>(smem + OFF_ETA);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+  float* sXch = reinterpret_cast<float*>(smem + OFF_XCH);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_MISC);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + OFF_MISC + 4);
   const uint64_t limit = p.wait_limit_ns;
@@ -166,6 +168,9 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     prefetch_tmap(&tmK);
     prefetch_tmap(&tmV);
     prefetch_tmap(&tmGo);
+    prefetch_tmap(&tmDQ);
+    prefetch_tmap(&tmDK);
+    prefetch_tmap(&tmDV);
   }
   if (warp == 0) {
     tmem_alloc(tmem_slot, TM_COLS);
@@ -221,6 +226,15 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 #pragma unroll 8
     for (int r = 0; r < 64; ++r) acc += ld_elem(t, r, f);
     return acc;
+  };
+
+  // the thread's fragment of a token tile -> the same swizzled image in global scratch
+  auto tok_st_global = [&](uint8_t* g, const float (&v)[16]) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      *reinterpret_cast<uint32_t*>(g + tm.off(tm.r0, q)) = pack_bf16(v[4 * q], v[4 * q + 1]);
+      *reinterpret_cast<uint32_t*>(g + tm.off(tm.r1, q)) = pack_bf16(v[4 * q + 2], v[4 * q + 3]);
+    }
   };
 
   // =====================================================================================
@@ -353,81 +367,65 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         commit();
       }
       wait_mma();
-      if (wg == 0) {
-        float xh[64];
-        {
-          uint32_t v[32];
-          tmem_ld32(tmem + lane_base + TM_B, v);
-          tmem_wait_ld();
+      {
+        float xh[16], b2c[8], gam[8], bet[8];
+        tok_ld(tm, tmem + TM_B, xh);
+        tok_ld_cols(tm, sB2, b2c);
+        tok_ld_cols(tm, sGamma, gam);
+        tok_ld_cols(tm, sBeta, bet);
 #pragma unroll
-          for (int q = 0; q < 32; ++q) xh[q] = __uint_as_float(v[q]) + sB2[q];
-          tmem_ld32(tmem + lane_base + TM_B + 32, v);
-          tmem_wait_ld();
-#pragma unroll
-          for (int q = 0; q < 32; ++q) xh[32 + q] = __uint_as_float(v[q]) + sB2[32 + q];
+        for (int q = 0; q < 4; ++q) {
+          xh[4 * q] += b2c[2 * q]; xh[4 * q + 1] += b2c[2 * q + 1];
+          xh[4 * q + 2] += b2c[2 * q]; xh[4 * q + 3] += b2c[2 * q + 1];
         }
-        float mu = 0.f;
+        float rs0, rs1;
+        tok_layernorm(tm, xh, TTT_LN_EPS, sXch, rs0, rs1);
+        float kk[16], vv[16], g[16], e[16];
+        tok_ld_tile(tm, sK, kk);
+        tok_ld_tile(tm, sV, vv);
+        float a[2] = {0.f, 0.f}, b[2] = {0.f, 0.f};
 #pragma unroll
-        for (int q = 0; q < 64; ++q) mu += xh[q];
-        mu *= (1.f / 64.f);
-        float var = 0.f;
+        for (int q = 0; q < 4; ++q) {
 #pragma unroll
-        for (int q = 0; q < 64; ++q) {
-          xh[q] -= mu;
-          var = fmaf(xh[q], xh[q], var);
-        }
-        const float sig = sqrtf(var * (1.f / 64.f) + TTT_LN_EPS);
-        const float rstd = 1.f / sig;
-        float g[64];
-        float s1 = 0.f, s2 = 0.f;
-        uint8_t* g_xhf = p.sc_xhf + slot * TILE;
-        uint8_t* g_gof = p.sc_gof + slot * TILE;
-        uint8_t* g_gz2 = p.sc_gZ2 + slot * TILE;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          float kk[8], vv[8], e[8];
-          ld_chunk(sK, tok, c, kk);
-          ld_chunk(sV, tok, c, vv);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const int f = c * 8 + k;
-            xh[f] *= rstd;
-            const float gam = sGamma[f];
-            e[k] = fmaf(gam, xh[f], sBeta[f]) - (vv[k] - kk[k]);
-            g[f] = e[k] * gam;
-            s1 += g[f];
-            s2 = fmaf(g[f], xh[f], s2);
-          }
-          if (tok_valid) {
-            const uint32_t off = sw128_off(tok, c);
-            *reinterpret_cast<uint4*>(g_xhf + off) = pack_chunk(xh + c * 8);
-            *reinterpret_cast<uint4*>(g_gof + off) = pack_chunk(e);
+          for (int h = 0; h < 2; ++h) {
+            const int x0 = 4 * q + h, x1 = 4 * q + 2 + h, c = 2 * q + h;
+            xh[x0] *= rs0;
+            xh[x1] *= rs1;
+            e[x0] = fmaf(gam[c], xh[x0], bet[c]) - (vv[x0] - kk[x0]);
+            e[x1] = fmaf(gam[c], xh[x1], bet[c]) - (vv[x1] - kk[x1]);
+            g[x0] = e[x0] * gam[c];
+            g[x1] = e[x1] * gam[c];
+            a[0] += g[x0]; a[1] = fmaf(g[x0], xh[x0], a[1]);
+            b[0] += g[x1]; b[1] = fmaf(g[x1], xh[x1], b[1]);
           }
         }
-        const float sc = rstd * (1.f / 64.f);
-        const float neg_eta = -__bfloat162float(eta[tok]);
+        tok_st_global(p.sc_xhf + slot * TILE, xh);
+        tok_st_global(p.sc_gof + slot * TILE, e);
+        tok_row_allreduce<2>(tm, a, b, sXch);
+        const float sc0 = rs0 * (1.f / 64.f), sc1 = rs1 * (1.f / 64.f);
+        const float ne0 = -__bfloat162float(eta[tm.r0]), ne1 = -__bfloat162float(eta[tm.r1]);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          float o[8], u[8];
+        for (int q = 0; q < 4; ++q) {
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const int f = c * 8 + k;
-            o[k] = (64.f * g[f] - s1 - xh[f] * s2) * sc;
-          }
-          const uint4 w = pack_chunk(o);
-          // the update uses -eta times the bf16-rounded gradient the other products see
-          float ob[8];
-          unpack_chunk(w, ob);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) u[k] = neg_eta * ob[k];
-          if (tok_valid) {
-            const uint32_t off = sw128_off(tok, c);
-            *reinterpret_cast<uint4*>(tGZ2 + off) = w;
-            *reinterpret_cast<uint4*>(g_gz2 + off) = w;
-            *reinterpret_cast<uint4*>(tU2 + off) = pack_chunk(u);
+          for (int h = 0; h < 2; ++h) {
+            const int x0 = 4 * q + h, x1 = 4 * q + 2 + h;
+            // dl/dZ2, rounded to bf16 once: the update below uses -eta times the rounded value
+            g[x0] = __bfloat162float(__float2bfloat16((64.f * g[x0] - a[0] - xh[x0] * a[1]) * sc0));
+            g[x1] = __bfloat162float(__float2bfloat16((64.f * g[x1] - b[0] - xh[x1] * b[1]) * sc1));
           }
         }
-        if (tok_valid) p.sc_sigf[slot * 64 + tok] = sig;
+        tok_st_tile(tm, tGZ2, g);
+        tok_st_global(p.sc_gZ2 + slot * TILE, g);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          g[4 * q] *= ne0; g[4 * q + 1] *= ne0;
+          g[4 * q + 2] *= ne1; g[4 * q + 3] *= ne1;
+        }
+        tok_st_tile(tm, tU2, g);
+        if (tm.colhalf == 0 && tm.l3 == 0) {
+          p.sc_sigf[slot * 64 + tm.r0] = 1.f / rs0;
+          p.sc_sigf[slot * 64 + tm.r1] = 1.f / rs1;
+        }
       }
       publish();
 
@@ -552,40 +550,27 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         commit();
       }
       wait_mma();
-      if (wg == 0) {
-        float z[64];
-        {
-          uint32_t v[32];
-          tmem_ld32(tmem + lane_base + TM_B, v);
-          tmem_wait_ld();
+      {
+        float z[16], b2c[8];
+        tok_ld(tm, tmem + TM_B, z);
+        tok_ld_cols(tm, sB2, b2c);
 #pragma unroll
-          for (int q = 0; q < 32; ++q) z[q] = __uint_as_float(v[q]) + sB2[q];
-          tmem_ld32(tmem + lane_base + TM_B + 32, v);
-          tmem_wait_ld();
-#pragma unroll
-          for (int q = 0; q < 32; ++q) z[32 + q] = __uint_as_float(v[q]) + sB2[32 + q];
+        for (int q = 0; q < 4; ++q) {
+          z[4 * q] += b2c[2 * q]; z[4 * q + 1] += b2c[2 * q + 1];
+          z[4 * q + 2] += b2c[2 * q]; z[4 * q + 3] += b2c[2 * q + 1];
         }
-        float mu = 0.f;
+        float rs0, rs1;
+        tok_layernorm(tm, z, TTT_LN_EPS, sXch, rs0, rs1);
 #pragma unroll
-        for (int q = 0; q < 64; ++q) mu += z[q];
-        mu *= (1.f / 64.f);
-        float var = 0.f;
-#pragma unroll
-        for (int q = 0; q < 64; ++q) {
-          z[q] -= mu;
-          var = fmaf(z[q], z[q], var);
+        for (int q = 0; q < 4; ++q) {
+          z[4 * q] *= rs0; z[4 * q + 1] *= rs0;
+          z[4 * q + 2] *= rs1; z[4 * q + 3] *= rs1;
         }
-        const float sig = sqrtf(var * (1.f / 64.f) + TTT_LN_EPS);
-        const float rstd = 1.f / sig;
-        uint8_t* g_xhln = p.sc_xhln + slot * TILE;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          float o[8];
-#pragma unroll
-          for (int k = 0; k < 8; ++k) o[k] = z[c * 8 + k] * rstd;
-          if (tok_valid) *reinterpret_cast<uint4*>(g_xhln + sw128_off(tok, c)) = pack_chunk(o);
+        tok_st_global(p.sc_xhln + slot * TILE, z);
+        if (tm.colhalf == 0 && tm.l3 == 0) {
+          p.sc_sigln[slot * 64 + tm.r0] = 1.f / rs0;
+          p.sc_sigln[slot * 64 + tm.r1] = 1.f / rs1;
         }
-        if (tok_valid) p.sc_sigln[slot * 64 + tok] = sig;
       }
       publish();
       if (tid == 0 && j + 2 < gsz && !*abort_flag) issue_inputs(j + 2);
@@ -663,36 +648,51 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
     for (int j = gsz - 1; j >= 0; --j) {
       const long slot = slot0 + j;
-      const long grow = tok_rows0 + (long)(i0 + j) * 64 + tok;       // this thread's token row (token epilogues)
+      const int row0 = static_cast<int>(tok_rows0 + (long)(i0 + j) * 64);   // first token row of this mini-batch
+      float kp[16];                                                          // partial dK, completed in E6
 
       // ---- S4: backward of the output LayerNorm
       wait_bar(BAR_T + 0);
       wait_bar(BAR_T + 1);
-      if (wg == 0) {
-        float gx[64];
-        float s1 = 0.f, s2 = 0.f;
+      {
+        float go[16], xl[16], gam[8];
+        tok_ld_tile(tm, t_go, go);
+        tok_ld_tile(tm, t_a, xl);
+        tok_ld_cols(tm, sGamma, gam);
+        float a[2] = {0.f, 0.f}, b[2] = {0.f, 0.f};
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          float go[8], xl[8];
-          ld_chunk(t_go, tok, c, go);
-          ld_chunk(t_a, tok, c, xl);
+        for (int q = 0; q < 4; ++q) {
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            gx[c * 8 + k] = go[k] * sGamma[c * 8 + k];
-            s1 += gx[c * 8 + k];
-            s2 = fmaf(gx[c * 8 + k], xl[k], s2);
+          for (int h = 0; h < 2; ++h) {
+            const int x0 = 4 * q + h, x1 = 4 * q + 2 + h;
+            go[x0] *= gam[2 * q + h];
+            go[x1] *= gam[2 * q + h];
+            a[0] += go[x0]; a[1] = fmaf(go[x0], xl[x0], a[1]);
+            b[0] += go[x1]; b[1] = fmaf(go[x1], xl[x1], b[1]);
           }
         }
-        const float rs = 1.f / (64.f * sSigLn[tok]);
+        tok_row_allreduce<2>(tm, a, b, sXch);
+        const float q0 = 1.f / (64.f * sSigLn[tm.r0]), q1 = 1.f / (64.f * sSigLn[tm.r1]);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          float xl[8], o[8];
-          ld_chunk(t_a, tok, c, xl);
+        for (int q = 0; q < 4; ++q) {
 #pragma unroll
-          for (int k = 0; k < 8; ++k) o[k] = (64.f * gx[c * 8 + k] - s1 - xl[k] * s2) * rs;
-          if (tok_valid) st_chunk(t_g, tok, c, o);
+          for (int h = 0; h < 2; ++h) {
+            const int x0 = 4 * q + h, x1 = 4 * q + 2 + h;
+            go[x0] = (64.f * go[x0] - a[0] - xl[x0] * a[1]) * q0;
+            go[x1] = (64.f * go[x1] - b[0] - xl[x1] * b[1]) * q1;
+          }
         }
-      } else if (tid < 192) {
+        tok_st_tile(tm, t_g, go);
+      }
+      publish();
+      if (tid == 0) {
+        // G1: gX2b^T = W2+ gZ2b^T
+        tc_fence_after_sync();
+        mma_hidden_major(tmem + TM_A, smem_u32(big(ib1)), smem_u32(t_g), false, false);
+        commit();
+      }
+      if (tid >= 128 && tid < 192) {
+        // column sums over the tokens: d_beta += sum go, d_gamma += sum go * x_hat_ln, G_b2 += sum gZ2b
         const int f = tid - 128;
         float a = 0.f, b = 0.f;
 #pragma unroll 8
@@ -703,18 +703,8 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         sDB[f] += b;
         sDG[f] += a;
+        sGb2[f] += colsum(t_g, f);
       }
-      publish();
-      if (tid == 0) {   // x_hat_ln is consumed: bring grad_output_fused into its tile
-        mbar_expect_tx(&bars[BAR_T + 1], TILE);
-        bulk_load_1d(t_a, p.sc_gof + slot * TILE, TILE, &bars[BAR_T + 1]);
-        pending |= 1u << (BAR_T + 1);
-        // G1: gX2b^T = W2+ gZ2b^T
-        tc_fence_after_sync();
-        mma_hidden_major(tmem + TM_A, smem_u32(big(ib1)), smem_u32(t_g), false, false);
-        commit();
-      }
-      if (tid >= 128 && tid < 192) sGb2[tid - 128] += colsum(t_g, tid - 128);
       wait_mma();
       wait_bar(BAR_BIG + ib2);
       // ---- E1: gZ1b^T = gX2b^T * gelu'(Z1b^T), in place over Z1b^T
@@ -741,6 +731,11 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         Gb1 += bsum;
       }
       publish();
+      if (tid == 0) {   // x_hat_ln and its column sums are consumed: bring grad_output_fused into that tile
+        mbar_expect_tx(&bars[BAR_T + 1], TILE);
+        bulk_load_1d(t_a, p.sc_gof + slot * TILE, TILE, &bars[BAR_T + 1]);
+        pending |= 1u << (BAR_T + 1);
+      }
       wait_bar(BAR_BIG + ib3);
       wait_bar(BAR_T + 2);
       if (tid == 0) {
@@ -774,25 +769,18 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         sGb1[hrow] = Gb1;
       }
-      if (wg == 0) {
-        uint4* dst = reinterpret_cast<uint4*>(p.dXQ + grow * 128);
-#pragma unroll 1
-        for (int half = 0; half < 2; ++half) {
-          uint32_t v[32];
-          tmem_ld32(tmem + lane_base + TM_B + half * 32, v);
-          tmem_wait_ld();
+      {   // dQ = go + gZ1b W1+^T, staged over the dL/dOut tile and stored by TMA
+        float acc[16], go[16];
+        tok_ld(tm, tmem + TM_B, acc);
+        tok_ld_tile(tm, t_go, go);
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            float go[8];
-            ld_chunk(t_go, tok, half * 4 + c, go);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) go[k] += __uint_as_float(v[c * 8 + k]);
-            if (tok_valid) dst[half * 4 + c] = pack_chunk(go);
-          }
-        }
+        for (int q = 0; q < 16; ++q) go[q] += acc[q];
+        tok_st_tile(tm, t_go, go);
       }
       publish();
       if (tid == 0) {
+        tma_store_2d(&tmDQ, t_go, 0, row0);
+        tma_commit_group();
         load_big(ib2, p.sc_Z1 + slot * BIG);
         load_big(ib3, p.sc_X2 + slot * BIG);
       }
@@ -817,7 +805,10 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         commit();
       }
       wait_mma();
-      if (tid == 0) load_big(ib3, p.sc_W2 + slot * 65536);
+      if (tid == 0) {
+        load_big(ib3, p.sc_W2 + slot * 65536);
+        tma_wait_group_read<0>();     // dQ has left the dL/dOut tile (E4 reuses it for dV)
+      }
       wait_bar(BAR_BIG + ib2);
       // ---- E3: A1, P = A1 gelu'(Z1), S = A1 gelu''(Z1), gelu'(Z1)
       {
@@ -860,122 +851,108 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       if (tid == 0) load_big(ib4, p.sc_W1 + slot * 65536);
       wait_bar(BAR_T + 6);
       wait_bar(BAR_T + 1);   // grad_output_fused
-      // ---- E4: second order through the fused LayerNorm + L2 gradient (token-major)
-      if (wg == 0) {
-        float A2[64], t1[64];
-        const float eta_t = __bfloat162float(sEta[tok]);
-        const float rs = 1.f / sSigF[tok];
-        float d12 = 0.f, d3 = 0.f;
+      // ---- E4: second order through the fused LayerNorm + L2 gradient (token-major, all 8 warps)
+      {
+        float A2[16], t1[16], gz[16], xh[16], go[16];
+        float gam[8];
+        tok_ld_cols(tm, sGamma, gam);
+        const float eta0 = __bfloat162float(sEta[tm.r0]), eta1 = __bfloat162float(sEta[tm.r1]);
+        const float rs0 = 1.f / sSigF[tm.r0], rs1 = 1.f / sSigF[tm.r1];
+        tok_ld_tile(tm, t_gz2, gz);
+        tok_ld_tile(tm, t_xf, xh);
+        tok_ld_tile(tm, t_a, go);
+        float ra[5] = {0.f, 0.f, 0.f, 0.f, 0.f}, rb[5] = {0.f, 0.f, 0.f, 0.f, 0.f};   // d12, d3, sum A2, sum A2 xh, sum gxf xh
         {
-          uint32_t v[32], w[32];
+          float acc1[16], acc2[16], kk[16], gb2[8];
+          tok_ld(tm, tmem + TM_B + 64, acc1);     // X2 G_W2
+          tok_ld(tm, tmem + TM_A, acc2);          // P W2
+          tok_ld(tm, tmem + TM_B, t1);            // gZ1 G_W1
+          tok_ld_tile(tm, t_k, kk);
+          tok_ld_cols(tm, sGb2, gb2);
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            tmem_ld32(tmem + lane_base + TM_B + 64 + half * 32, v);   // acc1 = X2 G_W2
-            tmem_ld32(tmem + lane_base + TM_A + half * 32, w);        // acc2 = P W2
-            tmem_wait_ld();
+          for (int q = 0; q < 4; ++q) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              float gz[8];
-              ld_chunk(t_gz2, tok, half * 4 + c, gz);
-#pragma unroll
-              for (int k = 0; k < 8; ++k) {
-                const int f = half * 32 + c * 8 + k;
-                const float a1 = __uint_as_float(v[c * 8 + k]) + sGb2[f];
-                d12 = fmaf(gz[k], a1, d12);
-                A2[f] = fmaf(-eta_t, a1, __uint_as_float(w[c * 8 + k]));
-              }
-            }
-          }
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            tmem_ld32(tmem + lane_base + TM_B + half * 32, v);        // T1 = gZ1 G_W1
-            tmem_wait_ld();
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              float kk[8];
-              ld_chunk(t_k, tok, half * 4 + c, kk);
-#pragma unroll
-              for (int k = 0; k < 8; ++k) {
-                const int f = half * 32 + c * 8 + k;
-                t1[f] = __uint_as_float(v[c * 8 + k]);
-                d3 = fmaf(t1[f], kk[k], d3);
-              }
+            for (int h = 0; h < 2; ++h) {
+              const int x0 = 4 * q + h, x1 = 4 * q + 2 + h, c = 2 * q + h;
+              const float u0 = acc1[x0] + gb2[c], u1 = acc1[x1] + gb2[c];
+              ra[0] = fmaf(gz[x0], u0, ra[0]);
+              rb[0] = fmaf(gz[x1], u1, rb[0]);
+              ra[1] = fmaf(t1[x0], kk[x0], ra[1]);
+              rb[1] = fmaf(t1[x1], kk[x1], rb[1]);
+              A2[x0] = fmaf(-eta0, u0, acc2[x0]);
+              A2[x1] = fmaf(-eta1, u1, acc2[x1]);
+              ra[2] += A2[x0];
+              rb[2] += A2[x1];
+              ra[3] = fmaf(A2[x0], xh[x0], ra[3]);
+              rb[3] = fmaf(A2[x1], xh[x1], rb[3]);
+              ra[4] = fmaf(go[x0] * gam[c], xh[x0], ra[4]);
+              rb[4] = fmaf(go[x1] * gam[c], xh[x1], rb[4]);
             }
           }
         }
-        // pass 1: sums of A2 and A2 * x_hat
-        float s_a = 0.f, s_ax = 0.f, s_gx = 0.f;
+        tok_row_allreduce<5>(tm, ra, rb, sXch);
+        float sa[2] = {0.f, 0.f}, sb[2] = {0.f, 0.f};      // sum g_std, sum g_xhat
+        float dga[16], dv[16];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          float xh[8], go[8];
-          ld_chunk(t_xf, tok, c, xh);
-          ld_chunk(t_a, tok, c, go);
+        for (int q = 0; q < 4; ++q) {
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const int f = c * 8 + k;
-            s_a += A2[f];
-            s_ax = fmaf(A2[f], xh[k], s_ax);
-            s_gx = fmaf(go[k] * sGamma[f], xh[k], s_gx);
+          for (int h = 0; h < 2; ++h) {
+            const int c = 2 * q + h;
+            const float gm = gam[c];
+            {
+              const int x = 4 * q + h;
+              const float bt = (A2[x] - (ra[2] + xh[x] * ra[3]) * (1.f / 64.f)) * rs0;
+              const float gly = gm * bt;
+              dga[x] = fmaf(go[x], bt, gly * xh[x]);
+              dv[x] = -gly;
+              kp[x] = fmaf(-eta0, t1[x], gly);
+              const float gxh = fmaf(gly, gm, -(go[x] * gm * ra[3] + A2[x] * ra[4]) * rs0 * (1.f / 64.f));
+              sa[0] += (-gxh * xh[x] - A2[x] * gz[x]) * rs0;
+              sa[1] += gxh;
+              A2[x] = gxh;
+            }
+            {
+              const int x = 4 * q + 2 + h;
+              const float bt = (A2[x] - (rb[2] + xh[x] * rb[3]) * (1.f / 64.f)) * rs1;
+              const float gly = gm * bt;
+              dga[x] = fmaf(go[x], bt, gly * xh[x]);
+              dv[x] = -gly;
+              kp[x] = fmaf(-eta1, t1[x], gly);
+              const float gxh = fmaf(gly, gm, -(go[x] * gm * rb[3] + A2[x] * rb[4]) * rs1 * (1.f / 64.f));
+              sb[0] += (-gxh * xh[x] - A2[x] * gz[x]) * rs1;
+              sb[1] += gxh;
+              A2[x] = gxh;
+            }
           }
         }
-        // pass 2: Bt, outputs that depend on it, gx_hat (kept in A2), sums for gZ2in
-        float s_gs = 0.f, s_gxh = 0.f;
-        uint4* dV = reinterpret_cast<uint4*>(p.dXV + grow * 128);
-        uint4* dKp = reinterpret_cast<uint4*>(p.dXK + grow * 128);
+        tok_st_tile(tm, t_a, dga);       // d_gamma addends, over grad_output_fused
+        tok_st_tile(tm, t_go, dv);       // dV: stored by TMA, and column-summed for d_beta
+        tok_row_allreduce<2>(tm, sa, sb, sXch);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          float xh[8], go[8], gz[8], dga[8], dv[8], kp[8];
-          ld_chunk(t_xf, tok, c, xh);
-          ld_chunk(t_a, tok, c, go);
-          ld_chunk(t_gz2, tok, c, gz);
+        for (int q = 0; q < 4; ++q) {
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const int f = c * 8 + k;
-            const float gam = sGamma[f];
-            const float bt = (A2[f] - (s_a + xh[k] * s_ax) * (1.f / 64.f)) * rs;
-            const float gly = gam * bt;
-            dga[k] = fmaf(go[k], bt, gly * xh[k]);
-            dv[k] = -gly;
-            kp[k] = fmaf(-eta_t, t1[f], gly);
-            const float gxf = go[k] * gam;
-            const float gxh = fmaf(gly, gam, -(gxf * s_ax + A2[f] * s_gx) * rs * (1.f / 64.f));
-            const float gsd = (-gxh * xh[k] - A2[f] * gz[k]) * rs;
-            s_gs += gsd;
-            s_gxh += gxh;
-            A2[f] = gxh;
-          }
-          if (tok_valid) {
-            st_chunk(t_a, tok, c, dga);          // d_gamma addends, in place over grad_output_fused
-            const uint4 wv = pack_chunk(dv);
-            *reinterpret_cast<uint4*>(t_go + sw128_off(tok, c)) = wv;   // dV tile (for d_beta)
-            dV[c] = wv;
-            dKp[c] = pack_chunk(kp);             // partial dK, completed after G13
+          for (int h = 0; h < 2; ++h) {
+            const int x0 = 4 * q + h, x1 = 4 * q + 2 + h;
+            A2[x0] = fmaf(A2[x0], rs0, (sa[0] * xh[x0] - sa[1] * rs0) * (1.f / 64.f));   // gZ2in
+            A2[x1] = fmaf(A2[x1], rs1, (sb[0] * xh[x1] - sb[1] * rs1) * (1.f / 64.f));
+            gz[x0] *= -eta0;                                                            // U2 = -eta gZ2
+            gz[x1] *= -eta1;
           }
         }
-        // pass 3: gZ2in and U2 = -eta gZ2
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          float xh[8], gz[8], o[8];
-          ld_chunk(t_xf, tok, c, xh);
-          ld_chunk(t_gz2, tok, c, gz);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const int f = c * 8 + k;
-            o[k] = fmaf(A2[f], rs, (s_gs * xh[k] - s_gxh * rs) * (1.f / 64.f));
-            gz[k] *= -eta_t;
-          }
-          if (tok_valid) {
-            st_chunk(t_q, tok, c, o);
-            st_chunk(t_g, tok, c, gz);
-          }
-        }
-        if (tok_valid) {
-          const float de = -(d12 + d3 + sPart[tok] + sPart[64 + tok] + sPart[128 + tok] + sPart[192 + tok]);
-          p.d_eta[(sid * NC + i0 + j) * 64 + tok] = __float2bfloat16(de);
+        tok_st_tile(tm, t_q, A2);
+        tok_st_tile(tm, t_g, gz);
+        if (tm.colhalf == 0 && tm.l3 == 0) {
+          const int r0 = tm.r0, r1 = tm.r1;
+          const float de0 = -(ra[0] + ra[1] + sPart[r0] + sPart[64 + r0] + sPart[128 + r0] + sPart[192 + r0]);
+          const float de1 = -(rb[0] + rb[1] + sPart[r1] + sPart[64 + r1] + sPart[128 + r1] + sPart[192 + r1]);
+          p.d_eta[(sid * NC + i0 + j) * 64 + r0] = __float2bfloat16(de0);
+          p.d_eta[(sid * NC + i0 + j) * 64 + r1] = __float2bfloat16(de1);
         }
       }
       publish();
       if (tid == 0) {
+        tma_store_2d(&tmDV, t_go, 0, row0);
+        tma_commit_group();
         tc_fence_after_sync();
         mma_hidden_major(tmem + TM_B, smem_u32(big(ib3)), smem_u32(t_q), false, false);      // G11
         mma_hidden_major(tmem + TM_B, smem_u32(big(ib1)), smem_u32(t_g), false, true);       // + G_W2snap U2^T
@@ -1020,6 +997,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
       if (tid == 0) {
         load_big(ib0, p.sc_X2 + slot * BIG);
+        tma_wait_group_read<0>();     // dV has left its tile
         if (j > 0) issue_tiles_a(j - 1);
       }
       wait_bar(BAR_BIG + ib4);
@@ -1032,27 +1010,20 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         commit();
       }
       wait_mma();
-      // ---- E6: dK = partial + gZ1in W1^T
-      if (wg == 0) {
-        uint4* dKp = reinterpret_cast<uint4*>(p.dXK + grow * 128);
-#pragma unroll 1
-        for (int half = 0; half < 2; ++half) {
-          uint32_t v[32];
-          tmem_ld32(tmem + lane_base + TM_A + half * 32, v);
-          tmem_wait_ld();
-          if (tok_valid) {
+      // ---- E6: dK = partial + gZ1in W1^T, staged over the gZ2in tile and stored by TMA
+      {
+        float acc[16];
+        tok_ld(tm, tmem + TM_A, acc);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              float kp[8];
-              unpack_chunk(dKp[half * 4 + c], kp);
-#pragma unroll
-              for (int k = 0; k < 8; ++k) kp[k] += __uint_as_float(v[c * 8 + k]);
-              dKp[half * 4 + c] = pack_chunk(kp);
-            }
-          }
-        }
+        for (int q = 0; q < 16; ++q) kp[q] += acc[q];
+        tok_st_tile(tm, t_q, kp);
       }
       publish();
+      if (tid == 0) {
+        tma_store_2d(&tmDK, t_q, 0, row0);
+        tma_commit_group();
+        tma_wait_group_read<0>();     // the next step's Q lands in the same tile
+      }
       // pre-update weights of this mini-batch are the post-update weights of the previous one
       {
         const int n0 = ib4, n1 = ib3, n2 = ib1, n3 = ib2, n4 = ib0;
@@ -1096,6 +1067,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       p.d_beta[sid * 64 + tid] = sDB[tid];
     }
   }
+  if (tid == 0) tma_wait_group<0>();
   if (tid == 0 && (aborted || *abort_flag)) {
     for (int b = 0; b < 15; ++b)
       if (pending & (1u << b)) mbar_wait_bounded(&bars[b], (ph >> b) & 1u, abort_flag, limit);
@@ -1110,11 +1082,14 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
 int ttt_launch_backward(const ttt_b200_bwd_args* a, cudaStream_t stream, uint32_t* status, uint64_t limit_ns) {
   const uint64_t rows = static_cast<uint64_t>(a->B) * a->H * a->NC * 64;
-  CUtensorMap tmQ, tmK, tmV, tmGo;
+  CUtensorMap tmQ, tmK, tmV, tmGo, tmDQ, tmDK, tmDV;
   if (int rc = ttt_make_tile_map(&tmQ, a->XQ, rows)) return rc;
   if (int rc = ttt_make_tile_map(&tmK, a->XK, rows)) return rc;
   if (int rc = ttt_make_tile_map(&tmV, a->XV, rows)) return rc;
   if (int rc = ttt_make_tile_map(&tmGo, a->grad_L_XQW_mini_batch, rows)) return rc;
+  if (int rc = ttt_make_tile_map(&tmDQ, a->grad_L_XQ, rows)) return rc;
+  if (int rc = ttt_make_tile_map(&tmDK, a->grad_L_XK, rows)) return rc;
+  if (int rc = ttt_make_tile_map(&tmDV, a->grad_L_XV, rows)) return rc;
   BwdParams p;
   p.eta = static_cast<const __nv_bfloat16*>(a->last_eta);
   p.gamma = a->ttt_norm_weight;
@@ -1152,7 +1127,7 @@ int ttt_launch_backward(const ttt_b200_bwd_args* a, cudaStream_t stream, uint32_
     if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
     if (dev >= 0 && dev < 64) attr_done[dev] = true;
   }
-  ttt_bwd_kernel<<<dim3(a->B * a->H), dim3(kThreads), SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmGo, p);
+  ttt_bwd_kernel<<<dim3(a->B * a->H), dim3(kThreads), SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmGo, tmDQ, tmDK, tmDV, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
   return TTT_B200_OK;
@@ -1266,11 +1241,14 @@ extern "C" int ttt_b200_backward_noalloc(const ttt_b200_bwd_noalloc_args* a, voi
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
 
   const uint64_t rows = static_cast<uint64_t>(a->B) * a->H * a->NC * 64;
-  CUtensorMap tmQ, tmK, tmV, tmGo;
+  CUtensorMap tmQ, tmK, tmV, tmGo, tmDQ, tmDK, tmDV;
   if (int rc = ttt_make_tile_map(&tmQ, a->XQ, rows)) return rc;
   if (int rc = ttt_make_tile_map(&tmK, a->XK, rows)) return rc;
   if (int rc = ttt_make_tile_map(&tmV, a->XV, rows)) return rc;
   if (int rc = ttt_make_tile_map(&tmGo, a->grad_L_XQW_mini_batch, rows)) return rc;
+  if (int rc = ttt_make_tile_map(&tmDQ, a->grad_L_XQ, rows)) return rc;
+  if (int rc = ttt_make_tile_map(&tmDK, a->grad_L_XK, rows)) return rc;
+  if (int rc = ttt_make_tile_map(&tmDV, a->grad_L_XV, rows)) return rc;
   BwdParams p;
   p.eta = static_cast<const __nv_bfloat16*>(a->last_eta);
   p.gamma = a->ttt_norm_weight;
@@ -1303,7 +1281,7 @@ extern "C" int ttt_b200_backward_noalloc(const ttt_b200_bwd_noalloc_args* a, voi
   // the status word is shared like the scratch: it must read zero when this launch starts
   e = cudaMemsetAsync(d.status, 0, sizeof(uint32_t), stream);
   if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
-  ttt_bwd_kernel<<<dim3(a->B * a->H), dim3(kThreads), SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmGo, p);
+  ttt_bwd_kernel<<<dim3(a->B * a->H), dim3(kThreads), SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmGo, tmDQ, tmDK, tmDV, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
   if (a->flags & TTT_B200_FLAG_SYNC) {

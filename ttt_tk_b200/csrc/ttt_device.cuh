@@ -132,4 +132,106 @@ __device__ __forceinline__ void mma_token_major(uint32_t tmem_d, uint32_t x_smem
   for (int j = 1; j < 16; ++j) mma_issue<true>(tmem_d, a0 + j * (2048u >> 4), b0 + j * (2048u >> 4), idesc);
 }
 
+// ---- Token-major 64 x 64 accumulators spread over 8 warps (256 threads).
+// A token-major accumulator (M = 64) keeps row r in TMEM lane (r % 16) + 32 * (r / 16): quadrant q
+// holds rows 16q .. 16q+15 in its first 16 lanes.  The two warps that may touch quadrant q (q and
+// q + 4) each take 32 of the 64 columns with one 16x256b.x4 load, so every thread owns 16 values:
+//   rows r0 = 16q + lane/4 and r1 = r0 + 8;  for j = 0..3 the column pair c = 32*colhalf + 8j + 2(lane%4):
+//   v[4j], v[4j+1] = (r0, c), (r0, c+1);   v[4j+2], v[4j+3] = (r1, c), (r1, c+1).
+// A row is shared by 8 threads: the 4 lanes of a quad in each of the two warps; row sums go through
+// two shuffles and one exchange in shared memory between the warp pair (named barrier 1 + q).
+struct TokMap {
+  int quad, colhalf, l3;
+  int r0, r1;
+  uint32_t taddr;      // lane/column offset to add to the accumulator's TMEM address
+  __device__ __forceinline__ TokMap(int warp, int lane)
+      : quad(warp & 3), colhalf(warp >> 2), l3(lane & 3), r0((warp & 3) * 16 + (lane >> 2)),
+        r1((warp & 3) * 16 + (lane >> 2) + 8),
+        taddr((static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>((warp >> 2) * 32)) {}
+  __device__ __forceinline__ int col(int j) const { return colhalf * 32 + j * 8 + l3 * 2; }
+  // byte offset of the column pair j of row r inside a swizzled [64][64] bf16 tile
+  __device__ __forceinline__ uint32_t off(int r, int j) const { return sw128_off(r, colhalf * 4 + j) + l3 * 4; }
+};
+__device__ __forceinline__ void tok_ld(const TokMap& m, uint32_t tmem_acc, float (&v)[16]) {
+  uint32_t u[16];
+  tmem_ld_16x256b_x4(tmem_acc + m.taddr, u);
+  tmem_wait_ld();
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(u[i]);
+}
+// the thread's 16 values of a swizzled bf16 tile, same order as the accumulator fragment
+__device__ __forceinline__ void tok_ld_tile(const TokMap& m, const uint8_t* tile, float (&v)[16]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t w0 = *reinterpret_cast<const uint32_t*>(tile + m.off(m.r0, j));
+    const uint32_t w1 = *reinterpret_cast<const uint32_t*>(tile + m.off(m.r1, j));
+    v[4 * j] = bf16_lo(w0); v[4 * j + 1] = bf16_hi(w0);
+    v[4 * j + 2] = bf16_lo(w1); v[4 * j + 3] = bf16_hi(w1);
+  }
+}
+__device__ __forceinline__ void tok_st_tile(const TokMap& m, uint8_t* tile, const float (&v)[16]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    *reinterpret_cast<uint32_t*>(tile + m.off(m.r0, j)) = pack_bf16(v[4 * j], v[4 * j + 1]);
+    *reinterpret_cast<uint32_t*>(tile + m.off(m.r1, j)) = pack_bf16(v[4 * j + 2], v[4 * j + 3]);
+  }
+}
+// per-column vector (fp32[64] in shared memory) -> the thread's 8 columns: c[2j], c[2j+1]
+__device__ __forceinline__ void tok_ld_cols(const TokMap& m, const float* vec, float (&c)[8]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = *reinterpret_cast<const float2*>(vec + m.col(j));
+    c[2 * j] = f.x; c[2 * j + 1] = f.y;
+  }
+}
+// All-reduce N per-row partial sums over the 8 threads that share each row.  a[] belongs to row
+// r0, b[] to row r1.  xch: fp32[2][64][8] in shared memory.
+template <int N>
+__device__ __forceinline__ void tok_row_allreduce(const TokMap& m, float (&a)[N], float (&b)[N], float* xch) {
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    a[i] += __shfl_xor_sync(0xffffffffu, a[i], 1);
+    b[i] += __shfl_xor_sync(0xffffffffu, b[i], 1);
+    a[i] += __shfl_xor_sync(0xffffffffu, a[i], 2);
+    b[i] += __shfl_xor_sync(0xffffffffu, b[i], 2);
+  }
+  if (m.l3 == 0) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      xch[(m.colhalf * 64 + m.r0) * 8 + i] = a[i];
+      xch[(m.colhalf * 64 + m.r1) * 8 + i] = b[i];
+    }
+  }
+  named_bar_sync(1 + m.quad, 64);
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    a[i] += xch[((m.colhalf ^ 1) * 64 + m.r0) * 8 + i];
+    b[i] += xch[((m.colhalf ^ 1) * 64 + m.r1) * 8 + i];
+  }
+  named_bar_sync(1 + m.quad, 64);
+}
+// LayerNorm statistics of the thread's two rows: centres z in place, returns 1/std per row
+__device__ __forceinline__ void tok_layernorm(const TokMap& m, float (&z)[16], float eps, float* xch, float& rstd0,
+                                              float& rstd1) {
+  float s0[1] = {0.f}, s1[1] = {0.f};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    s0[0] += z[4 * j] + z[4 * j + 1];
+    s1[0] += z[4 * j + 2] + z[4 * j + 3];
+  }
+  tok_row_allreduce<1>(m, s0, s1, xch);
+  const float mu0 = s0[0] * (1.f / 64.f), mu1 = s1[0] * (1.f / 64.f);
+  s0[0] = 0.f; s1[0] = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    z[4 * j] -= mu0; z[4 * j + 1] -= mu0;
+    z[4 * j + 2] -= mu1; z[4 * j + 3] -= mu1;
+    s0[0] = fmaf(z[4 * j], z[4 * j], fmaf(z[4 * j + 1], z[4 * j + 1], s0[0]));
+    s1[0] = fmaf(z[4 * j + 2], z[4 * j + 2], fmaf(z[4 * j + 3], z[4 * j + 3], s1[0]));
+  }
+  tok_row_allreduce<1>(m, s0, s1, xch);
+  rstd0 = rsqrtf(s0[0] * (1.f / 64.f) + eps);
+  rstd1 = rsqrtf(s1[0] * (1.f / 64.f) + eps);
+}
+
 }  // namespace tttdev

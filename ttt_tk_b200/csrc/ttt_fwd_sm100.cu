@@ -50,7 +50,8 @@ constexpr uint32_t OFF_GAMMA = OFF_B2 + 256;
 constexpr uint32_t OFF_BETA = OFF_GAMMA + 256;
 constexpr uint32_t OFF_BAR = OFF_BETA + 256;
 constexpr uint32_t OFF_MISC = OFF_BAR + 64;
-constexpr uint32_t SMEM_USED = OFF_MISC + 64;
+constexpr uint32_t OFF_XCH = OFF_MISC + 64;       // fp32[2][64][8] row-sum exchange between warp pairs
+constexpr uint32_t SMEM_USED = OFF_XCH + 4096;
 constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;  // slack for the 1024-byte alignment
 static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB per-CTA shared memory of sm_100");
 
@@ -93,8 +94,7 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const int quad = warp & 3, wg = warp >> 2;
   const int hrow = wg * 128 + quad * 32 + lane;          // hidden unit owned in the 256-row epilogues
   const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
-  const int tok = quad * 16 + (lane & 15);               // token owned in the 64-row epilogues (wg 0)
-  const bool tok_valid = lane < 16;
+  const TokMap tm(warp, lane);                           // fragment of the 64 x 64 token-major tiles
   const long stream_id = blockIdx.x;
   const int head = static_cast<int>(stream_id % p.H);
 
@@ -109,6 +109,7 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   float* sBeta = reinterpret_cast<float*>(smem + OFF_BETA);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + OFF_BAR);   // [kStages]
   uint64_t* mma_bar = full + kStages;
+  float* sXch = reinterpret_cast<float*>(smem + OFF_XCH);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_MISC);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + OFF_MISC + 4);
 
@@ -272,60 +273,50 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       umma_commit(mma_bar);
     }
     wait_mma();
-    // ---- LN: fused LayerNorm + L2 gradient, U2 = -eta * dl/dZ2
-    if (wg == 0) {
-      float xh[64];
-      {
-        uint32_t v[32];
-        tmem_ld32(tmem + lane_base + TM_Z, v);
-        tmem_wait_ld();
+    // ---- LN: fused LayerNorm + L2 gradient, U2 = -eta * dl/dZ2 (all 8 warps, 16 values each)
+    {
+      float xh[16], b2c[8], gam[8], bet[8];
+      tok_ld(tm, tmem + TM_Z, xh);
+      tok_ld_cols(tm, sB2, b2c);
+      tok_ld_cols(tm, sGamma, gam);
+      tok_ld_cols(tm, sBeta, bet);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) xh[j] = __uint_as_float(v[j]) + sB2[j];
-        tmem_ld32(tmem + lane_base + TM_Z + 32, v);
-        tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) xh[32 + j] = __uint_as_float(v[j]) + sB2[32 + j];
+      for (int j = 0; j < 4; ++j) {
+        xh[4 * j] += b2c[2 * j]; xh[4 * j + 1] += b2c[2 * j + 1];
+        xh[4 * j + 2] += b2c[2 * j]; xh[4 * j + 3] += b2c[2 * j + 1];
       }
-      float mu = 0.f;
+      float rs0, rs1;
+      tok_layernorm(tm, xh, TTT_LN_EPS, sXch, rs0, rs1);
+      float kk[16], vv[16], g[16];
+      tok_ld_tile(tm, sK, kk);
+      tok_ld_tile(tm, sV, vv);
+      float a[2] = {0.f, 0.f}, b[2] = {0.f, 0.f};
 #pragma unroll
-      for (int j = 0; j < 64; ++j) mu += xh[j];
-      mu *= (1.f / 64.f);
-      float var = 0.f;
+      for (int j = 0; j < 4; ++j) {
 #pragma unroll
-      for (int j = 0; j < 64; ++j) {
-        xh[j] -= mu;
-        var = fmaf(xh[j], xh[j], var);
-      }
-      const float rstd = rsqrtf(var * (1.f / 64.f) + TTT_LN_EPS);
-      float g[64];
-      float s1 = 0.f, s2 = 0.f;
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        float kk[8], vv[8];
-        ld_chunk(sK, tok, c, kk);
-        ld_chunk(sV, tok, c, vv);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const int f = c * 8 + k;
-          xh[f] *= rstd;
-          const float gam = sGamma[f];
-          const float e = fmaf(gam, xh[f], sBeta[f]) - (vv[k] - kk[k]);
-          g[f] = e * gam;
-          s1 += g[f];
-          s2 = fmaf(g[f], xh[f], s2);
+        for (int e = 0; e < 2; ++e) {
+          const int i0 = 4 * j + e, i1 = 4 * j + 2 + e, c = 2 * j + e;
+          xh[i0] *= rs0;
+          xh[i1] *= rs1;
+          g[i0] = (fmaf(gam[c], xh[i0], bet[c]) - (vv[i0] - kk[i0])) * gam[c];
+          g[i1] = (fmaf(gam[c], xh[i1], bet[c]) - (vv[i1] - kk[i1])) * gam[c];
+          a[0] += g[i0]; a[1] = fmaf(g[i0], xh[i0], a[1]);
+          b[0] += g[i1]; b[1] = fmaf(g[i1], xh[i1], b[1]);
         }
       }
-      const float scale = -__bfloat162float(sEta[tok]) * rstd * (1.f / 64.f);
+      tok_row_allreduce<2>(tm, a, b, sXch);
+      const float sc0 = -__bfloat162float(sEta[tm.r0]) * rs0 * (1.f / 64.f);
+      const float sc1 = -__bfloat162float(sEta[tm.r1]) * rs1 * (1.f / 64.f);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        float o[8];
+      for (int j = 0; j < 4; ++j) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const int f = c * 8 + k;
-          o[k] = (64.f * g[f] - s1 - xh[f] * s2) * scale;
+        for (int e = 0; e < 2; ++e) {
+          const int i0 = 4 * j + e, i1 = 4 * j + 2 + e;
+          g[i0] = (64.f * g[i0] - a[0] - xh[i0] * a[1]) * sc0;
+          g[i1] = (64.f * g[i1] - b[0] - xh[i1] * b[1]) * sc1;
         }
-        if (tok_valid) st_chunk(sU2, tok, c, o);
       }
+      tok_st_tile(tm, sU2, g);
     }
     publish();
 
@@ -429,41 +420,30 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
     wait_mma();
     // ---- OUT: Q + gamma * LN(Z2b + b2) + beta
-    if (wg == 0) {
-      float z[64];
-      {
-        uint32_t v[32];
-        tmem_ld32(tmem + lane_base + TM_Z, v);
-        tmem_wait_ld();
+    {
+      float z[16], b2c[8], gam[8], bet[8], q[16];
+      tok_ld(tm, tmem + TM_Z, z);
+      tok_ld_cols(tm, sB2, b2c);
+      tok_ld_cols(tm, sGamma, gam);
+      tok_ld_cols(tm, sBeta, bet);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) z[j] = __uint_as_float(v[j]) + sB2[j];
-        tmem_ld32(tmem + lane_base + TM_Z + 32, v);
-        tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) z[32 + j] = __uint_as_float(v[j]) + sB2[32 + j];
+      for (int j = 0; j < 4; ++j) {
+        z[4 * j] += b2c[2 * j]; z[4 * j + 1] += b2c[2 * j + 1];
+        z[4 * j + 2] += b2c[2 * j]; z[4 * j + 3] += b2c[2 * j + 1];
       }
-      float mu = 0.f;
+      float rs0, rs1;
+      tok_layernorm(tm, z, TTT_LN_EPS, sXch, rs0, rs1);
+      tok_ld_tile(tm, sQ, q);
 #pragma unroll
-      for (int j = 0; j < 64; ++j) mu += z[j];
-      mu *= (1.f / 64.f);
-      float var = 0.f;
+      for (int j = 0; j < 4; ++j) {
 #pragma unroll
-      for (int j = 0; j < 64; ++j) {
-        z[j] -= mu;
-        var = fmaf(z[j], z[j], var);
-      }
-      const float rstd = rsqrtf(var * (1.f / 64.f) + TTT_LN_EPS);
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        float q[8];
-        ld_chunk(sQ, tok, c, q);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const int f = c * 8 + k;
-          q[k] += fmaf(sGamma[f], z[f] * rstd, sBeta[f]);
+        for (int e = 0; e < 2; ++e) {
+          const int i0 = 4 * j + e, i1 = 4 * j + 2 + e, c = 2 * j + e;
+          q[i0] += fmaf(gam[c], z[i0] * rs0, bet[c]);
+          q[i1] += fmaf(gam[c], z[i1] * rs1, bet[c]);
         }
-        if (tok_valid) st_chunk(sOut, tok, c, q);
       }
+      tok_st_tile(tm, sOut, q);
     }
     publish();
     if (tid == 0) {

@@ -19,6 +19,7 @@ struct ProbeParams {
   int a_mn, b_mn;   // operand stored MN-major (else K-major)
   int neg_a;        // use -A
   int repeat;       // run the product `repeat` times, accumulating
+  int frag_ld;      // read the result back with the 16x256b fragment loads (M = 64 only)
   uint32_t* status;
 };
 
@@ -82,7 +83,24 @@ __global__ void __launch_bounds__(128, 1) umma_probe_kernel(ProbeParams p) {
   }
   const bool ok = mbar_wait_bounded(&bar, 0, &abort_flag, 200ull * 1000 * 1000);
   tc_fence_after_sync();
-  if (ok) {
+  if (ok && p.frag_ld) {
+    // 16x256b fragments of the M = 64 layout: rows 16*warp + lane/4 (+8), column pairs 8j + 2(lane%4)
+    for (int c0 = 0; c0 < N; c0 += 32) {
+      uint32_t v[16];
+      tmem_ld_16x256b_x4(tmem + (static_cast<uint32_t>(warp * 32) << 16) + c0, v);
+      tmem_wait_ld();
+      const int r0 = warp * 16 + (lane >> 2);
+      for (int j = 0; j < 4; ++j) {
+        const int c = c0 + 8 * j + 2 * (lane & 3);
+        if (c + 1 < N) {
+          p.D[r0 * N + c] = __uint_as_float(v[4 * j]);
+          p.D[r0 * N + c + 1] = __uint_as_float(v[4 * j + 1]);
+          p.D[(r0 + 8) * N + c] = __uint_as_float(v[4 * j + 2]);
+          p.D[(r0 + 8) * N + c + 1] = __uint_as_float(v[4 * j + 3]);
+        }
+      }
+    }
+  } else if (ok) {
     // M = 128: row = TMEM lane.  M = 64: row r sits in lane (r % 16) + 32 * (r / 16).
     const int row = (M == 128) ? tid : (lane < 16 ? warp * 16 + lane : -1);
     for (int c0 = 0; c0 < N; c0 += 32) {
@@ -103,7 +121,12 @@ __global__ void __launch_bounds__(128, 1) umma_probe_kernel(ProbeParams p) {
 }  // namespace
 
 extern "C" int ttt_b200_umma_selftest(const float* A, const float* B, float* D, int M, int N, int K, int a_mn,
-                                      int b_mn, int neg_a, int repeat, void* stream_) {
+                                      int b_mn, int neg_a, int repeat_and_mode, void* stream_) {
+  // bits 0..7: repeat count; bit 8: read back through the 16x256b fragment loads (M = 64, N % 32 == 0)
+  const int repeat = repeat_and_mode & 0xff;
+  const int frag_ld = (repeat_and_mode >> 8) & 1;
+  if (frag_ld && (M != 64 || (N % 32) != 0))
+    return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "umma_selftest: fragment read-back needs M = 64 and N % 32 == 0");
   if (!(M == 64 || M == 128) || N < 16 || N > 256 || (N % 16) || K < 64 || K > 256 || (K % 64) || repeat < 1)
     return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "umma_selftest: unsupported shape");
   if ((a_mn && M > 128) || N * K * 2 > 131072)
@@ -111,7 +134,7 @@ extern "C" int ttt_b200_umma_selftest(const float* A, const float* B, float* D, 
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   uint32_t* status = nullptr;
   if (int rc = ttt_status_word(&status)) return rc;
-  ProbeParams p{A, B, D, M, N, K, a_mn, b_mn, neg_a, repeat, status};
+  ProbeParams p{A, B, D, M, N, K, a_mn, b_mn, neg_a, repeat, frag_ld, status};
   const int smem = 65536 + 131072 + 1024;
   cudaError_t e = cudaFuncSetAttribute(umma_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
