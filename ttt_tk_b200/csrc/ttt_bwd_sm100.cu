@@ -95,6 +95,7 @@ constexpr int BAR_BIG = 0;     // +buffer index (0..4)
 constexpr int BAR_T = 5;       // +tile index (0..6)
 constexpr int BAR_IN = 12;     // +stage (0..1), recompute inputs
 constexpr int BAR_MMA = 14;
+constexpr int BAR_V = 15;      // recompute: the single V tile
 
 constexpr uint32_t TM_S1 = 0;      // W1^T / dL/dW1^T
 constexpr uint32_t TM_S2 = 128;    // W2   / dL/dW2
@@ -161,7 +162,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const uint64_t limit = p.wait_limit_ns;
 
   if (tid == 0) {
-    for (int i = 0; i < 15; ++i) mbar_init(&bars[i], 1);
+    for (int i = 0; i < 16; ++i) mbar_init(&bars[i], 1);
     fence_mbar_init();
     *abort_flag = 0;
     prefetch_tmap(&tmQ);
@@ -248,26 +249,35 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const int i0 = ck * cgs;
     const int gsz = min(cgs, NC - i0);
     const long slot0 = sid * cgs;           // scratch slot of the group's first mini-batch
-    // buffer roles during recompute: 0 = W1^T bf16, 1 = W2 bf16, 2 = X2^T, 3 = G' / U1^T, 4 = gZ2 tile
+    // buffer roles during recompute: 0 = W1^T bf16, 1 = W2 bf16, 2 = X2^T / X2_bar^T,
+    // 3 = Z1^T -> U1^T -> Z1_bar^T, 4 = G' -> dl/dZ1^T; every one of them also leaves for the
+    // scratch slot as a bulk copy.  Token tiles: 0..3 = K, Q of two stages, 4 = V, 5 = gZ2, 6 = U2.
     uint8_t* bW1 = big(0);
     uint8_t* bW2 = big(1);
     uint8_t* bX2 = big(2);
-    uint8_t* bGP = big(3);
-    uint8_t* tGZ2 = big(4);
+    uint8_t* bZ1 = big(3);
+    uint8_t* bGP = big(4);
+    uint8_t* tV = tile(4);
+    uint8_t* tGZ2 = tile(5);
     uint8_t* tU2 = tile(6);
 
     auto issue_inputs = [&](int j) {   // thread 0
       const int s = j & 1;
       const int row0 = static_cast<int>(tok_rows0 + (long)(i0 + j) * 64);
-      mbar_expect_tx(&bars[BAR_IN + s], 3 * TILE + 128);
-      tma_load_2d(tile(3 * s + 0), &tmK, &bars[BAR_IN + s], 0, row0);
-      tma_load_2d(tile(3 * s + 1), &tmV, &bars[BAR_IN + s], 0, row0);
-      tma_load_2d(tile(3 * s + 2), &tmQ, &bars[BAR_IN + s], 0, row0);
+      mbar_expect_tx(&bars[BAR_IN + s], 2 * TILE + 128);
+      tma_load_2d(tile(2 * s + 0), &tmK, &bars[BAR_IN + s], 0, row0);
+      tma_load_2d(tile(2 * s + 1), &tmQ, &bars[BAR_IN + s], 0, row0);
       bulk_load_1d(sEta + s * 64, p.eta + (sid * NC + i0 + j) * 64, 128, &bars[BAR_IN + s]);
       pending |= 1u << (BAR_IN + s);
     };
+    auto issue_v = [&](int j) {        // thread 0
+      mbar_expect_tx(&bars[BAR_V], TILE);
+      tma_load_2d(tV, &tmV, &bars[BAR_V], 0, static_cast<int>(tok_rows0 + (long)(i0 + j) * 64));
+      pending |= 1u << BAR_V;
+    };
     if (tid == 0) {
       issue_inputs(0);
+      issue_v(0);
       if (gsz > 1) issue_inputs(1);
     }
 
@@ -277,8 +287,6 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     {
       const float* W1g = p.W1c + (sid * p.nck + ck) * (64 * 256);
       const float* W2g = p.W2c + (sid * p.nck + ck) * (256 * 64) + hrow * 64;
-      uint8_t* g1 = p.sc_W1 + slot0 * 65536;
-      uint8_t* g2 = p.sc_W2 + slot0 * 65536;
 #pragma unroll 1
       for (int half = 0; half < 2; ++half) {
         uint32_t v[32];
@@ -294,7 +302,6 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           const uint4 w = pack_chunk(f + c * 8);
           const uint32_t off = sw128_off(hrow, half * 4 + c);
           *reinterpret_cast<uint4*>(bW1 + off) = w;
-          *reinterpret_cast<uint4*>(g1 + off) = w;
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -309,20 +316,24 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           const uint4 w = pack_chunk(f + c * 8);
           const uint32_t off = sw128_off(hrow, half * 4 + c);
           *reinterpret_cast<uint4*>(bW2 + off) = w;
-          *reinterpret_cast<uint4*>(g2 + off) = w;
         }
       }
       tmem_wait_st();
     }
     publish();
+    if (tid == 0) {   // bf16 images of the checkpoint = pre-update weights of the group's first mini-batch
+      bulk_store_1d(p.sc_W1 + slot0 * 65536, bW1, BIG);
+      bulk_store_1d(p.sc_W2 + slot0 * 65536, bW2, BIG);
+      tma_commit_group();
+    }
 
     // ================================================================== recompute the group
     for (int j = 0; j < gsz; ++j) {
       const int s = j & 1;
       const long slot = slot0 + j;
-      const uint8_t* sK = tile(3 * s + 0);
-      const uint8_t* sV = tile(3 * s + 1);
-      const uint8_t* sQ = tile(3 * s + 2);
+      const uint8_t* sK = tile(2 * s + 0);
+      const uint8_t* sQ = tile(2 * s + 1);
+      const uint8_t* sV = tV;
       const __nv_bfloat16* eta = sEta + s * 64;
       wait_bar(BAR_IN + s);
 
@@ -334,8 +345,6 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       wait_mma();
       {
-        uint8_t* gZ1 = p.sc_Z1 + slot * BIG;
-        uint8_t* gX2 = p.sc_X2 + slot * BIG;
 #pragma unroll 1
         for (int half = 0; half < 2; ++half) {
           uint32_t v[32];
@@ -350,15 +359,18 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               gelu_pair(z[k], g[k], gp[k]);
             }
             const uint32_t off = sw128_off(hrow, half * 4 + c);
-            const uint4 wg_ = pack_chunk(g);
-            *reinterpret_cast<uint4*>(bX2 + off) = wg_;
-            *reinterpret_cast<uint4*>(gX2 + off) = wg_;
+            *reinterpret_cast<uint4*>(bX2 + off) = pack_chunk(g);
             *reinterpret_cast<uint4*>(bGP + off) = pack_chunk(gp);
-            *reinterpret_cast<uint4*>(gZ1 + off) = pack_chunk(z);
+            *reinterpret_cast<uint4*>(bZ1 + off) = pack_chunk(z);
           }
         }
       }
       publish();
+      if (tid == 0) {
+        bulk_store_1d(p.sc_X2 + slot * BIG, bX2, BIG);
+        bulk_store_1d(p.sc_Z1 + slot * BIG, bZ1, BIG);
+        tma_commit_group();
+      }
 
       // MMA2: Z2 = X2 W2
       if (tid == 0) {
@@ -367,6 +379,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         commit();
       }
       wait_mma();
+      wait_bar(BAR_V);
       {
         float xh[16], b2c[8], gam[8], bet[8];
         tok_ld(tm, tmem + TM_B, xh);
@@ -427,10 +440,12 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           p.sc_sigf[slot * 64 + tm.r1] = 1.f / rs1;
         }
       }
+      if (tid == 0) tma_wait_group_read<0>();   // Z1 / X2 images have left shared memory
       publish();
 
       // MMA3: R^T = W2 gZ2^T
       if (tid == 0) {
+        if (j + 1 < gsz) issue_v(j + 1);        // V is consumed
         tc_fence_after_sync();
         mma_hidden_major(tmem + TM_A, smem_u32(bW2), smem_u32(tGZ2), false, false);
         commit();
@@ -438,7 +453,6 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       if (tid >= 128 && tid < 192) sB2[tid - 128] += colsum(tU2, tid - 128);
       wait_mma();
       {
-        uint8_t* gG1 = p.sc_gZ1 + slot * BIG;
         float bsum = 0.f;
 #pragma unroll 1
         for (int half = 0; half < 2; ++half) {
@@ -453,7 +467,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 #pragma unroll
             for (int k = 0; k < 8; ++k) gp[k] *= __uint_as_float(v[c * 8 + k]);     // dl/dZ1
             const uint4 w = pack_chunk(gp);
-            *reinterpret_cast<uint4*>(gG1 + off) = w;
+            *reinterpret_cast<uint4*>(bGP + off) = w;             // dl/dZ1 (bf16), in place over G'
             float gb[8];
             unpack_chunk(w, gb);
 #pragma unroll
@@ -461,7 +475,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               u[k] = -__bfloat162float(eta[half * 32 + c * 8 + k]) * gb[k];
               bsum += u[k];
             }
-            *reinterpret_cast<uint4*>(bGP + off) = pack_chunk(u);
+            *reinterpret_cast<uint4*>(bZ1 + off) = pack_chunk(u);  // U1 = -eta dl/dZ1, over Z1
           }
         }
         b1v += bsum;
@@ -470,16 +484,15 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
       // MMA4: W1^T += U1^T K ; W2 += X2^T U2
       if (tid == 0) {
+        bulk_store_1d(p.sc_gZ1 + slot * BIG, bGP, BIG);
+        tma_commit_group();
         tc_fence_after_sync();
-        mma_hidden_major(tmem + TM_S1, smem_u32(bGP), smem_u32(sK), true, true);
+        mma_hidden_major(tmem + TM_S1, smem_u32(bZ1), smem_u32(sK), true, true);
         mma_hidden_major(tmem + TM_S2, smem_u32(bX2), smem_u32(tU2), true, true);
         commit();
       }
       wait_mma();
       {
-        const bool keep = (j + 1 < gsz);
-        uint8_t* g1 = p.sc_W1 + (slot + 1) * 65536;
-        uint8_t* g2 = p.sc_W2 + (slot + 1) * 65536;
 #pragma unroll 1
         for (int half = 0; half < 2; ++half) {
           uint32_t v[32];
@@ -493,7 +506,6 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             const uint4 w = pack_chunk(f + c * 8);
             const uint32_t off = sw128_off(hrow, half * 4 + c);
             *reinterpret_cast<uint4*>(bW1 + off) = w;
-            if (keep) *reinterpret_cast<uint4*>(g1 + off) = w;
           }
           tmem_ld32(tmem + lane_base + TM_S2 + wg * 64 + half * 32, v);
           tmem_wait_ld();
@@ -504,7 +516,6 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             const uint4 w = pack_chunk(f + c * 8);
             const uint32_t off = sw128_off(hrow, half * 4 + c);
             *reinterpret_cast<uint4*>(bW2 + off) = w;
-            if (keep) *reinterpret_cast<uint4*>(g2 + off) = w;
           }
         }
       }
@@ -512,14 +523,17 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
       // MMA5: Z1b^T = W1+^T Q^T
       if (tid == 0) {
+        if (j + 1 < gsz) {   // the new weights are the next mini-batch's pre-update weights
+          bulk_store_1d(p.sc_W1 + (slot + 1) * 65536, bW1, BIG);
+          bulk_store_1d(p.sc_W2 + (slot + 1) * 65536, bW2, BIG);
+          tma_commit_group();
+        }
         tc_fence_after_sync();
         mma_hidden_major(tmem + TM_A, smem_u32(bW1), smem_u32(sQ), false, false);
         commit();
       }
       wait_mma();
       {
-        uint8_t* gZ1b = p.sc_Z1b + slot * BIG;
-        uint8_t* gX2b = p.sc_X2b + slot * BIG;
 #pragma unroll 1
         for (int half = 0; half < 2; ++half) {
           uint32_t v[32];
@@ -534,10 +548,8 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               g[k] = gelu_only(z[k]);
             }
             const uint32_t off = sw128_off(hrow, half * 4 + c);
-            const uint4 w = pack_chunk(g);
-            *reinterpret_cast<uint4*>(bX2 + off) = w;
-            *reinterpret_cast<uint4*>(gX2b + off) = w;
-            *reinterpret_cast<uint4*>(gZ1b + off) = pack_chunk(z);
+            *reinterpret_cast<uint4*>(bX2 + off) = pack_chunk(g);
+            *reinterpret_cast<uint4*>(bZ1 + off) = pack_chunk(z);
           }
         }
       }
@@ -545,6 +557,9 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
       // MMA6: Z2b = X2b W2+ ; output LayerNorm statistics
       if (tid == 0) {
+        bulk_store_1d(p.sc_X2b + slot * BIG, bX2, BIG);
+        bulk_store_1d(p.sc_Z1b + slot * BIG, bZ1, BIG);
+        tma_commit_group();
         tc_fence_after_sync();
         mma_token_major(tmem + TM_B, smem_u32(bX2), smem_u32(bW2));
         commit();
@@ -572,6 +587,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           p.sc_sigln[slot * 64 + tm.r1] = 1.f / rs1;
         }
       }
+      if (tid == 0) tma_wait_group_read<0>();   // every image of this mini-batch has left shared memory
       publish();
       if (tid == 0 && j + 2 < gsz && !*abort_flag) issue_inputs(j + 2);
       if (*abort_flag) { aborted = true; break; }
@@ -636,9 +652,10 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       bulk_load_1d(t_gz2, p.sc_gZ2 + slot * TILE, TILE, &bars[BAR_T + 5]);
       pending |= (1u << (BAR_T + 2)) | (1u << (BAR_T + 4)) | (1u << (BAR_T + 5));
     };
-    // scratch was written with generic-proxy stores by all threads: order them before the
-    // bulk (async-proxy) copies that read it back
+    // scratch was written partly with generic-proxy stores by all threads, partly with bulk
+    // stores by thread 0: order both before the bulk (async-proxy) copies that read it back
     asm volatile("fence.proxy.async;" ::: "memory");
+    if (tid == 0) tma_wait_group<0>();
     publish();
     if (tid == 0) {
       issue_tiles_a(gsz - 1);
@@ -1069,7 +1086,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   }
   if (tid == 0) tma_wait_group<0>();
   if (tid == 0 && (aborted || *abort_flag)) {
-    for (int b = 0; b < 15; ++b)
+    for (int b = 0; b < 16; ++b)
       if (pending & (1u << b)) mbar_wait_bounded(&bars[b], (ph >> b) & 1u, abort_flag, limit);
     atomicExch(p.status, static_cast<uint32_t>(TTT_B200_ERR_TIMEOUT));
   }
