@@ -145,10 +145,8 @@ class DeviceStep:
 
     def reduce_norm_grads(self, world):
         # the caller-side batch sum the operator's layout asks for, then the one exchange of the path
-        self.norm_grads[0] = self.outs["grad_L_ttt_norm_weight"].sum(0).squeeze(1)
-        self.norm_grads[1] = self.outs["grad_L_ttt_norm_bias"].sum(0).squeeze(1)
-        if world > 1:
-            torch.distributed.all_reduce(self.norm_grads)
+        from ttt_tk_b200.dist import reduce_norm_grads
+        self.norm_grads = reduce_norm_grads(self.outs["grad_L_ttt_norm_weight"], self.outs["grad_L_ttt_norm_bias"])
 
 
 def run_ours(args, rank, world, local_rank):

@@ -209,6 +209,13 @@ int ttt_b200_version(void);
 int ttt_b200_umma_selftest(const float* A, const float* B, float* D, int M, int N, int K, int a_mn, int b_mn,
                            int neg_a, int repeat_and_mode, void* stream);
 
+/* Diagnostics (no counterpart in the reference): exercise the failure path.  One CTA waits, with
+ * the operator kernels' bounded wait, on a barrier nothing arrives on; after `limit_us` it gives
+ * up, reports through the status word and exits normally.  Returns code 3 (the expected outcome)
+ * and stores the time the kernel waited in *waited_ns (host pointer, may be NULL).  The context
+ * stays usable.  Synchronises. */
+int ttt_b200_wait_selftest(int limit_us, unsigned long long* waited_ns, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -44,7 +44,7 @@ class BwdNoAllocArgs(ctypes.Structure):
 
 
 EXPORTS = ["ttt_b200_forward", "ttt_b200_backward", "ttt_b200_backward_noalloc", "ttt_b200_last_error", "ttt_b200_take_status",
-           "ttt_b200_version", "ttt_b200_umma_selftest"]
+           "ttt_b200_version", "ttt_b200_umma_selftest", "ttt_b200_wait_selftest"]
 
 FLAG_SYNC = 1
 
@@ -69,6 +69,8 @@ def load():
     lib.ttt_b200_version.restype = ctypes.c_int
     lib.ttt_b200_umma_selftest.argtypes = [c_void_p, c_void_p, c_void_p] + [ctypes.c_int] * 7 + [c_void_p]
     lib.ttt_b200_umma_selftest.restype = ctypes.c_int
+    lib.ttt_b200_wait_selftest.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_ulonglong), c_void_p]
+    lib.ttt_b200_wait_selftest.restype = ctypes.c_int
     return lib
 
 

@@ -338,10 +338,13 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       wait_bar(BAR_IN + s);
 
       // MMA1: Z1^T = W1^T K^T
-      if (tid == 0) {
+      if (warp == 0) {
+        if (lane == 0) {
         tc_fence_after_sync();
         mma_hidden_major(tmem + TM_A, smem_u32(bW1), smem_u32(sK), false, false);
         commit();
+      }
+        __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
       {
@@ -373,10 +376,13 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
 
       // MMA2: Z2 = X2 W2
-      if (tid == 0) {
+      if (warp == 0) {
+        if (lane == 0) {
         tc_fence_after_sync();
         mma_token_major(tmem + TM_B, smem_u32(bX2), smem_u32(bW2));
         commit();
+      }
+        __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
       wait_bar(BAR_V);
@@ -444,11 +450,14 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
 
       // MMA3: R^T = W2 gZ2^T
-      if (tid == 0) {
+      if (warp == 0) {
+        if (lane == 0) {
         if (j + 1 < gsz) issue_v(j + 1);        // V is consumed
         tc_fence_after_sync();
         mma_hidden_major(tmem + TM_A, smem_u32(bW2), smem_u32(tGZ2), false, false);
         commit();
+      }
+        __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       if (tid >= 128 && tid < 192) sB2[tid - 128] += colsum(tU2, tid - 128);
       wait_mma();
@@ -483,13 +492,16 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
 
       // MMA4: W1^T += U1^T K ; W2 += X2^T U2
-      if (tid == 0) {
+      if (warp == 0) {
+        if (lane == 0) {
         bulk_store_1d(p.sc_gZ1 + slot * BIG, bGP, BIG);
         tma_commit_group();
         tc_fence_after_sync();
         mma_hidden_major(tmem + TM_S1, smem_u32(bZ1), smem_u32(sK), true, true);
         mma_hidden_major(tmem + TM_S2, smem_u32(bX2), smem_u32(tU2), true, true);
         commit();
+      }
+        __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
       {
@@ -522,7 +534,8 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
 
       // MMA5: Z1b^T = W1+^T Q^T
-      if (tid == 0) {
+      if (warp == 0) {
+        if (lane == 0) {
         if (j + 1 < gsz) {   // the new weights are the next mini-batch's pre-update weights
           bulk_store_1d(p.sc_W1 + (slot + 1) * 65536, bW1, BIG);
           bulk_store_1d(p.sc_W2 + (slot + 1) * 65536, bW2, BIG);
@@ -531,6 +544,8 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tc_fence_after_sync();
         mma_hidden_major(tmem + TM_A, smem_u32(bW1), smem_u32(sQ), false, false);
         commit();
+      }
+        __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
       {
@@ -556,13 +571,16 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
 
       // MMA6: Z2b = X2b W2+ ; output LayerNorm statistics
-      if (tid == 0) {
+      if (warp == 0) {
+        if (lane == 0) {
         bulk_store_1d(p.sc_X2b + slot * BIG, bX2, BIG);
         bulk_store_1d(p.sc_Z1b + slot * BIG, bZ1, BIG);
         tma_commit_group();
         tc_fence_after_sync();
         mma_token_major(tmem + TM_B, smem_u32(bX2), smem_u32(bW2));
         commit();
+      }
+        __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
       {
@@ -702,11 +720,14 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tok_st_tile(tm, t_g, go);
       }
       publish();
-      if (tid == 0) {
+      if (warp == 0) {
+        if (lane == 0) {
         // G1: gX2b^T = W2+ gZ2b^T
         tc_fence_after_sync();
         mma_hidden_major(tmem + TM_A, smem_u32(big(ib1)), smem_u32(t_g), false, false);
         commit();
+      }
+        __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       if (tid >= 128 && tid < 192) {
         // column sums over the tokens: d_beta += sum go, d_gamma += sum go * x_hat_ln, G_b2 += sum gZ2b
@@ -755,12 +776,15 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       wait_bar(BAR_BIG + ib3);
       wait_bar(BAR_T + 2);
-      if (tid == 0) {
+      if (warp == 0) {
+        if (lane == 0) {
         tc_fence_after_sync();
         mma_hidden_major(tmem + TM_S2, smem_u32(big(ib3)), smem_u32(t_g), true, true);   // G2
         mma_hidden_major(tmem + TM_S1, smem_u32(big(ib2)), smem_u32(t_q), true, true);   // G3
         mma_token_major(tmem + TM_B, smem_u32(big(ib2)), smem_u32(big(ib0)));            // G7
         commit();
+      }
+        __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
       // ---- E2: bf16 snapshots of the gradient state; dQ
@@ -814,12 +838,15 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
       wait_bar(BAR_T + 4);
       wait_bar(BAR_BIG + ib3);
-      if (tid == 0) {
+      if (warp == 0) {
+        if (lane == 0) {
         tc_fence_after_sync();
         mma_hidden_major(tmem + TM_A, smem_u32(big(ib0)), smem_u32(t_k), false, false);   // G4
         mma_token_major(tmem + TM_B, smem_u32(big(ib4)), smem_u32(big(ib0)));             // G8
         mma_token_major(tmem + TM_B + 64, smem_u32(big(ib3)), smem_u32(big(ib1)));        // G5
         commit();
+      }
+        __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
       if (tid == 0) {
@@ -858,11 +885,14 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
       wait_bar(BAR_BIG + ib3);
       wait_bar(BAR_T + 5);
-      if (tid == 0) {
+      if (warp == 0) {
+        if (lane == 0) {
         tc_fence_after_sync();
         mma_token_major(tmem + TM_A, smem_u32(big(ib4)), smem_u32(big(ib3)));                 // G6
         mma_hidden_major(tmem + TM_S2, smem_u32(big(ib4)), smem_u32(t_gz2), true, true);     // G10
         commit();
+      }
+        __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
       if (tid == 0) load_big(ib4, p.sc_W1 + slot * 65536);
@@ -967,7 +997,8 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
       publish();
-      if (tid == 0) {
+      if (warp == 0) {
+        if (lane == 0) {
         tma_store_2d(&tmDV, t_go, 0, row0);
         tma_commit_group();
         tc_fence_after_sync();
@@ -975,6 +1006,8 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         mma_hidden_major(tmem + TM_B, smem_u32(big(ib1)), smem_u32(t_g), false, true);       // + G_W2snap U2^T
         mma_hidden_major(tmem + TM_A, smem_u32(big(ib3)), smem_u32(t_gz2), false, false);    // G12
         commit();
+      }
+        __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       if (tid >= 128 && tid < 192) {
         const int f = tid - 128;
@@ -1019,12 +1052,15 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       wait_bar(BAR_BIG + ib4);
       wait_bar(BAR_BIG + ib0);
-      if (tid == 0) {
+      if (warp == 0) {
+        if (lane == 0) {
         tc_fence_after_sync();
         mma_token_major(tmem + TM_A, smem_u32(big(ib2)), smem_u32(big(ib4)));                 // G13
         mma_hidden_major(tmem + TM_S1, smem_u32(big(ib2)), smem_u32(t_k), true, true);       // G15
         mma_hidden_major(tmem + TM_S2, smem_u32(big(ib0)), smem_u32(t_q), true, true);       // G14
         commit();
+      }
+        __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
       // ---- E6: dK = partial + gZ1in W1^T, staged over the gZ2in tile and stored by TMA

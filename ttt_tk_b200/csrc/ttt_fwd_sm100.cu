@@ -243,11 +243,14 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     mbar_wait_bounded(&full[s], (it / kStages) & 1, abort_flag, limit);
 
     // ---- MMA1: Z1^T = W1^T K^T
-    if (tid == 0) {
+    if (warp == 0) {
+        if (lane == 0) {
       tc_fence_after_sync();
       mma_hidden_major(tmem + TM_A, smem_u32(sW1), smem_u32(sK), false, false);
       umma_commit(mma_bar);
     }
+        __syncwarp();   // the other lanes do not spin while lane 0 issues
+      }
     wait_mma();
     // ---- EPI1: X2^T = gelu(Z1^T + b1), G' = gelu'(Z1^T + b1)
 #pragma unroll 1
@@ -267,11 +270,14 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     publish();
 
     // ---- MMA2: Z2 = X2 W2
-    if (tid == 0) {
+    if (warp == 0) {
+        if (lane == 0) {
       tc_fence_after_sync();
       mma_token_major(tmem + TM_Z, smem_u32(sX2), smem_u32(sW2));
       umma_commit(mma_bar);
     }
+        __syncwarp();   // the other lanes do not spin while lane 0 issues
+      }
     wait_mma();
     // ---- LN: fused LayerNorm + L2 gradient, U2 = -eta * dl/dZ2 (all 8 warps, 16 values each)
     {
@@ -321,11 +327,14 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     publish();
 
     // ---- MMA3: R^T = W2 U2^T
-    if (tid == 0) {
+    if (warp == 0) {
+        if (lane == 0) {
       tc_fence_after_sync();
       mma_hidden_major(tmem + TM_A, smem_u32(sW2), smem_u32(sU2), false, false);
       umma_commit(mma_bar);
     }
+        __syncwarp();   // the other lanes do not spin while lane 0 issues
+      }
     // b2 += column sums of U2 (bf16 values, the operand the W2 update sees), fp32 accumulate
     if (tid >= 128 && tid < 192) {
       const int f = tid - 128;
@@ -362,12 +371,15 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     publish();
 
     // ---- MMA4: W1^T += U1^T K ;  W2 += X2^T U2
-    if (tid == 0) {
+    if (warp == 0) {
+        if (lane == 0) {
       tc_fence_after_sync();
       mma_hidden_major(tmem + TM_W1, smem_u32(sGP), smem_u32(sK), true, true);
       mma_hidden_major(tmem + TM_W2, smem_u32(sX2), smem_u32(sU2), true, true);
       umma_commit(mma_bar);
     }
+        __syncwarp();   // the other lanes do not spin while lane 0 issues
+      }
     wait_mma();
     // ---- EPI4: refresh the bf16 operand copies of the state
 #pragma unroll 1
@@ -390,11 +402,14 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     publish();
 
     // ---- MMA5: Z1b^T = W1^T Q^T
-    if (tid == 0) {
+    if (warp == 0) {
+        if (lane == 0) {
       tc_fence_after_sync();
       mma_hidden_major(tmem + TM_A, smem_u32(sW1), smem_u32(sQ), false, false);
       umma_commit(mma_bar);
     }
+        __syncwarp();   // the other lanes do not spin while lane 0 issues
+      }
     wait_mma();
     // ---- EPI5: X2b^T = gelu(Z1b^T + b1)
 #pragma unroll 1
@@ -413,11 +428,14 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     publish();
 
     // ---- MMA6: Z2b = X2b W2
-    if (tid == 0) {
+    if (warp == 0) {
+        if (lane == 0) {
       tc_fence_after_sync();
       mma_token_major(tmem + TM_Z, smem_u32(sX2), smem_u32(sW2));
       umma_commit(mma_bar);
     }
+        __syncwarp();   // the other lanes do not spin while lane 0 issues
+      }
     wait_mma();
     // ---- OUT: Q + gamma * LN(Z2b + b2) + beta
     {

@@ -143,3 +143,49 @@ extern "C" int ttt_b200_umma_selftest(const float* A, const float* B, float* D, 
   if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
   return ttt_check_status(stream);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Self-test of the failure path: one CTA waits, with the kernels' own bounded wait, on a barrier
+// that nothing ever arrives on.  The wait must run out after `limit_us`, the CTA must report
+// through the status word and exit normally, and the context must stay usable.
+namespace {
+__global__ void wait_probe_kernel(uint32_t* status, uint64_t limit_ns, unsigned long long* waited_ns) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+    abort_flag = 0;
+  }
+  __syncthreads();
+  const uint64_t t0 = globaltimer_ns();
+  const bool ok = mbar_wait_bounded(&bar, 0, &abort_flag, limit_ns);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    *waited_ns = globaltimer_ns() - t0;
+    if (!ok) atomicExch(status, TTT_B200_ERR_TIMEOUT);
+  }
+}
+}  // namespace
+
+extern "C" int ttt_b200_wait_selftest(int limit_us, unsigned long long* waited_ns_host, void* stream_) {
+  if (limit_us < 1 || limit_us > 1000000)
+    return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "wait_selftest: limit must be 1 us .. 1 s");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  uint32_t* status = nullptr;
+  if (int rc = ttt_status_word(&status)) return rc;
+  unsigned long long* d_waited = nullptr;
+  cudaError_t e = cudaMalloc(&d_waited, sizeof(unsigned long long));
+  if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
+  wait_probe_kernel<<<1, 64, 0, stream>>>(status, static_cast<uint64_t>(limit_us) * 1000ull, d_waited);
+  e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  unsigned long long waited = 0;
+  if (e == cudaSuccess) e = cudaMemcpy(&waited, d_waited, sizeof(waited), cudaMemcpyDeviceToHost);
+  cudaFree(d_waited);
+  if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
+  if (waited_ns_host) *waited_ns_host = waited;
+  if (ttt_take_status() != 0)
+    return ttt_set_error(TTT_B200_ERR_TIMEOUT, "a device-side bounded wait ran out; results are invalid");
+  return TTT_B200_OK;
+}
