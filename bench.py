@@ -71,10 +71,13 @@ class ClockSampler:
         self.proc = None
 
     def start(self):
+        """Start sampling and return once the first sample has arrived (nvidia-smi needs a moment
+        to come up; the timed region is only tens of milliseconds long)."""
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.idx}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "10"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.first = self.proc.stdout.readline()
         except Exception:
             self.proc = None
 
@@ -89,7 +92,7 @@ class ClockSampler:
             out = ""
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.strip().splitlines():
+        for line in out.strip().splitlines():   # the sample taken before the GPU was under load is left out
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue

@@ -1,0 +1,144 @@
+"""Parity at the benchmark configurations' sizes, long sequences, and the autograd wrapper."""
+import pytest
+import torch
+
+from oracle import ttt_mlp as orc
+from ttt_tk_b200 import ttt_forward, ttt_backward, take_status
+from ttt_tk_b200.autograd import ttt_mlp
+from ttt_tk_b200.buffers import alloc_backward_buffers, alloc_checkpoints, GRAD_NAMES, CHECKPOINT_NAMES
+from ttt_tk_b200.synthetic import make_inputs
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(d, cgs):
+    dev = "cuda"
+    B, H, NC = d["XQ"].shape[:3]
+    t = {k: v.to(dev) for k, v in d.items()}
+    ck = alloc_checkpoints(B, H, NC, cgs, dev)
+    out = torch.empty_like(t["XQ"])
+    ttt_forward(t["XQ"], t["XK"], t["XV"], t["last_eta"], t["ttt_norm_weight"], t["ttt_norm_bias"],
+                t["W1"], t["b1"], t["W2"], t["b2"], *ck, out, cgs)
+    scratch, outs = alloc_backward_buffers(B, H, NC, cgs, dev, fill=float("nan"))
+    ttt_backward(t["XQ"], t["XK"], t["XV"], t["last_eta"].unsqueeze(-1).contiguous(), t["ttt_norm_weight"],
+                 t["ttt_norm_bias"], *ck, out, *scratch, t["grad_L_W1_last"], t["grad_L_b1_last"],
+                 t["grad_L_W2_last"], t["grad_L_b2_last"], t["grad_L_XQW_mini_batch"],
+                 *[outs[k] for k in GRAD_NAMES], cgs)
+    torch.cuda.synchronize()
+    assert take_status() == 0
+    return out, ck, outs
+
+
+def _oracle(d, cgs, ck=None):
+    f = orc.ttt_forward(d["XQ"], d["XK"], d["XV"], d["last_eta"], d["ttt_norm_weight"], d["ttt_norm_bias"],
+                        d["W1"], d["b1"], d["W2"], d["b2"], cgs)
+    c = f if ck is None else ck
+    g = orc.ttt_backward(d["XQ"], d["XK"], d["XV"], d["last_eta"], d["ttt_norm_weight"], d["ttt_norm_bias"],
+                         c["W1_checkpoints"], c["b1_checkpoints"], c["W2_checkpoints"], c["b2_checkpoints"],
+                         d["grad_L_W1_last"], d["grad_L_b1_last"], d["grad_L_W2_last"], d["grad_L_b2_last"],
+                         d["grad_L_XQW_mini_batch"], cgs)
+    return f, g
+
+
+def test_config1_full_size_forward_and_backward():
+    """configs[1] shape (B=4, H=12, seq 2048, cgs 4), every stream against the oracle."""
+    B, H, NC, cgs = 4, 12, 32, 4
+    d = make_inputs(B, H, NC, seed=0, backward=True)
+    out, ck, outs = _run(d, cgs)
+    f, g = _oracle(d, cgs, {k: c.cpu() for k, c in zip(CHECKPOINT_NAMES, ck)})
+    assert orc.rel_l2(out.float().cpu(), f["Out"]) <= 1e-2
+    for k, c in zip(CHECKPOINT_NAMES, ck):
+        if k[0] == "W":
+            assert orc.rel_l2(c.cpu(), f[k]) <= 1e-2, k
+    for k in GRAD_NAMES:
+        assert orc.rel_l2(outs[k].float().cpu(), g[k]) <= 3e-2, k
+
+
+def test_config2_full_size_streams_are_independent_and_correct():
+    """configs[2] (B=4, H=32, seq 8192, cgs 8) at full size.  The oracle would need minutes for all 128
+    streams, so: (a) two streams taken out and run alone must give bit-identical results (streams are
+    independent and the kernels deterministic), (b) those two streams are checked against the oracle."""
+    B, H, NC, cgs = 4, 32, 128, 8
+    d = make_inputs(B, H, NC, seed=0, backward=True)
+    out, ck, outs = _run(d, cgs)
+    picks = [(0, 0), (3, 31)]
+    for (b, h) in picks:
+        sub = {}
+        for k, v in d.items():
+            if v.shape[0] == 1:
+                sub[k] = v[:, h:h + 1].contiguous()
+            else:
+                sub[k] = v[b:b + 1, h:h + 1].contiguous()
+        out1, ck1, outs1 = _run(sub, cgs)
+        assert torch.equal(out1[0, 0], out[b, h])
+        for c1, c in zip(ck1, ck):
+            assert torch.equal(c1[0, 0], c[b, h])
+        for k in GRAD_NAMES:
+            assert torch.equal(outs1[k][0, 0], outs[k][b, h]), k
+        f, g = _oracle(sub, cgs, {k: c.cpu() for k, c in zip(CHECKPOINT_NAMES, ck1)})
+        assert orc.rel_l2(out1.float().cpu(), f["Out"]) <= 1e-2
+        for k in GRAD_NAMES:
+            assert orc.rel_l2(outs1[k].float().cpu(), g[k]) <= 3e-2, k
+
+
+def test_long_sequence_error_stays_inside_the_gate():
+    """Long-context shape of configs[3] (seq 65536, NC = 1024, cgs 32) on two heads: the error of the
+    bf16-operand recurrence grows with the mini-batch index and must still meet the gates at the end."""
+    B, H, NC, cgs = 1, 2, 1024, 32
+    d = make_inputs(B, H, NC, seed=0, backward=True)
+    out, ck, outs = _run(d, cgs)
+    f, g = _oracle(d, cgs, {k: c.cpu() for k, c in zip(CHECKPOINT_NAMES, ck)})
+    o = out.float().cpu()
+    assert orc.rel_l2(o, f["Out"]) <= 1e-2
+    tail = orc.rel_l2(o[:, :, -64:], f["Out"][:, :, -64:])
+    assert tail <= 1.5e-2, f"last 64 mini-batches: rel-L2 {tail:.3e}"
+    assert orc.rel_l2(ck[0].cpu()[:, :, -1], f["W1_checkpoints"][:, :, -1]) <= 1e-2
+    for k in GRAD_NAMES:
+        assert orc.rel_l2(outs[k].float().cpu(), g[k]) <= 3e-2, k
+
+
+@pytest.mark.parametrize("eta_scale", [0.01, 1.0])
+def test_eta_scale_sweep_forward(eta_scale):
+    """The eta scales of configs[4] (0.01, 0.1, 1.0) x sigmoid(N(0,1)) / 64 on a slice of its shape."""
+    B, H, NC, cgs = 2, 4, 64, 16
+    d = make_inputs(B, H, NC, seed=1, eta_scale=eta_scale)
+    dev = "cuda"
+    t = {k: v.to(dev) for k, v in d.items()}
+    ck = alloc_checkpoints(B, H, NC, cgs, dev)
+    out = torch.empty_like(t["XQ"])
+    ttt_forward(t["XQ"], t["XK"], t["XV"], t["last_eta"], t["ttt_norm_weight"], t["ttt_norm_bias"],
+                t["W1"], t["b1"], t["W2"], t["b2"], *ck, out, cgs, sync=True)
+    f = orc.ttt_forward(d["XQ"], d["XK"], d["XV"], d["last_eta"], d["ttt_norm_weight"], d["ttt_norm_bias"],
+                        d["W1"], d["b1"], d["W2"], d["b2"], cgs)
+    assert orc.rel_l2(out.float().cpu(), f["Out"]) <= 1e-2
+
+
+def test_autograd_function_matches_oracle_autograd():
+    B, H, NC, cgs = 2, 2, 6, 4
+    d = make_inputs(B, H, NC, seed=9, backward=True)
+    dev = "cuda"
+    names = ["XQ", "XK", "XV", "last_eta", "ttt_norm_weight", "ttt_norm_bias", "W1", "b1", "W2", "b2"]
+    leaves = [d[k].to(dev).requires_grad_(True) for k in names]
+    out, state = ttt_mlp(*leaves, checkpoint_group_size=cgs)
+    loss = (out.float() * d["grad_L_XQW_mini_batch"].to(dev).float()).sum()
+    for s, k in zip(state, ["grad_L_W1_last", "grad_L_b1_last", "grad_L_W2_last", "grad_L_b2_last"]):
+        loss = loss + (s * d[k].to(dev)).sum()
+    loss.backward()
+    ref = orc.ttt_backward_autograd(d["XQ"], d["XK"], d["XV"], d["last_eta"], d["ttt_norm_weight"],
+                                    d["ttt_norm_bias"], d["W1"], d["b1"], d["W2"], d["b2"],
+                                    d["grad_L_W1_last"], d["grad_L_b1_last"], d["grad_L_W2_last"],
+                                    d["grad_L_b2_last"], d["grad_L_XQW_mini_batch"])
+    want = {"XQ": ref["grad_L_XQ"], "XK": ref["grad_L_XK"], "XV": ref["grad_L_XV"],
+            "last_eta": ref["grad_L_last_eta"].squeeze(-1),
+            "ttt_norm_weight": ref["grad_L_ttt_norm_weight"].sum(0, keepdim=True),
+            "ttt_norm_bias": ref["grad_L_ttt_norm_bias"].sum(0, keepdim=True),
+            "W1": ref["grad_L_W1_init"], "b1": ref["grad_L_b1_init"],
+            "W2": ref["grad_L_W2_init"], "b2": ref["grad_L_b2_init"]}
+    for leaf, k in zip(leaves, names):
+        assert leaf.grad is not None, k
+        assert orc.rel_l2(leaf.grad.float().cpu(), want[k].float()) <= 3e-2, k
+    # final state against the oracle forward
+    f = orc.ttt_forward(d["XQ"], d["XK"], d["XV"], d["last_eta"], d["ttt_norm_weight"], d["ttt_norm_bias"],
+                        d["W1"], d["b1"], d["W2"], d["b2"], cgs)
+    assert orc.rel_l2(state[0].detach().cpu(), f["W1_final"]) <= 1e-2
+    assert orc.rel_l2(state[2].detach().cpu(), f["W2_final"]) <= 1e-2
