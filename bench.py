@@ -132,19 +132,26 @@ class DeviceStep:
         self.norm_grads = torch.zeros(2, H, 64, device=dev)
         self.ev = None
 
-    def forward(self):
+    def forward(self, sl=(slice(None), slice(None))):
+        """Forward over the streams `sl` = (batch element b:b+1 or all, head range): such a slice of a
+        contiguous [B, H, ...] tensor is contiguous."""
         from ttt_tk_b200 import ttt_forward
         t = self.t
-        ttt_forward(t["XQ"], t["XK"], t["XV"], t["last_eta"], t["ttt_norm_weight"], t["ttt_norm_bias"],
-                    t["W1"], t["b1"], t["W2"], t["b2"], *self.ck, self.out, self.cgs)
+        hs = (slice(None), sl[1])
+        ttt_forward(t["XQ"][sl], t["XK"][sl], t["XV"][sl], t["last_eta"][sl], t["ttt_norm_weight"][hs],
+                    t["ttt_norm_bias"][hs], t["W1"][sl], t["b1"][sl], t["W2"][sl], t["b2"][sl],
+                    *[c[sl] for c in self.ck], self.out[sl], self.cgs)
 
-    def backward(self):
+    def backward(self, sl=(slice(None), slice(None))):
         from ttt_tk_b200 import ttt_backward
         t = self.t
-        ttt_backward(t["XQ"], t["XK"], t["XV"], t["last_eta5"], t["ttt_norm_weight"], t["ttt_norm_bias"],
-                     *self.ck, self.out, *self.scratch,
-                     t["grad_L_W1_last"], t["grad_L_b1_last"], t["grad_L_W2_last"], t["grad_L_b2_last"],
-                     t["grad_L_XQW_mini_batch"], *[self.outs[k] for k in self.GRADS], self.cgs)
+        hs = (slice(None), sl[1])
+        ttt_backward(t["XQ"][sl], t["XK"][sl], t["XV"][sl], t["last_eta5"][sl], t["ttt_norm_weight"][hs],
+                     t["ttt_norm_bias"][hs], *[c[sl] for c in self.ck], self.out[sl],
+                     *[x[sl] for x in self.scratch],
+                     t["grad_L_W1_last"][sl], t["grad_L_b1_last"][sl], t["grad_L_W2_last"][sl],
+                     t["grad_L_b2_last"][sl], t["grad_L_XQW_mini_batch"][sl],
+                     *[self.outs[k][sl] for k in self.GRADS], self.cgs)
 
     def reduce_norm_grads(self, world):
         # the caller-side batch sum the operator's layout asks for, then the one exchange of the path
@@ -209,15 +216,37 @@ def run_ours(args, rank, world, local_rank):
     h2d = sum(v.numel() * v.element_size() for v in pin_in.values())
     d2h = sum(v.numel() * v.element_size() for v in pin_out.values())
 
+    # The batch elements are independent, so the step is pipelined over them: each batch element's
+    # host->device copies, forward, backward and device->host copies go to their own CUDA stream; the
+    # two copy directions and the kernels of different batch elements then overlap.
+    hsplit = max(1, min(args.e2e_head_chunks, H))
+    hb = [(i * H // hsplit, (i + 1) * H // hsplit) for i in range(hsplit)]
+    chunks = [(slice(b, b + 1), slice(h0, h1)) for b in range(B) for (h0, h1) in hb]
+    streams = [torch.cuda.Stream(device=dev) for _ in range(min(len(chunks), 8))]
+    shared_keys = ["ttt_norm_weight", "ttt_norm_bias"]
+    step.t["last_eta5"] = step.t["last_eta"].unsqueeze(-1)     # a view: follows the copies into last_eta
+
     def e2e_step():
-        for k, v in pin_in.items():
-            step.t[k].copy_(v, non_blocking=True)
-        step.t["last_eta5"] = step.t["last_eta"].unsqueeze(-1)
-        step.forward()
-        step.backward()
+        main = torch.cuda.current_stream(dev)
+        for k in shared_keys:
+            step.t[k].copy_(pin_in[k], non_blocking=True)
+        ready = torch.cuda.Event()
+        ready.record(main)
+        for st in streams:
+            st.wait_event(ready)
+        for i, sl in enumerate(chunks):
+            st = streams[i % len(streams)]
+            with torch.cuda.stream(st):
+                for k, v in pin_in.items():
+                    if k not in shared_keys:
+                        step.t[k][sl].copy_(v[sl], non_blocking=True)
+                step.forward(sl)
+                step.backward(sl)
+                for k, v in out_t.items():
+                    pin_out[k][sl].copy_(v[sl], non_blocking=True)
+        for st in streams:
+            main.wait_stream(st)
         step.reduce_norm_grads(world)
-        for k, v in out_t.items():
-            pin_out[k].copy_(v, non_blocking=True)
 
     e2e_step()
     barrier()
@@ -260,7 +289,9 @@ def run_ours(args, rank, world, local_rank):
                      "unit": "TFLOP/s", "frac": bwd_tf / peak_tf, "traffic": None,
                      "peak_source": f"{pk_src} (sustained cuBLAS bf16: kernel timed inside a long step)"},
         "e2e": {"value": tokens_per_step / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                "pipelining": f"{len(chunks)} (batch element, head range) chunks on {len(streams)} CUDA streams "
+                              "(copies and kernels overlap)"},
         "gpu_launches": 2 * K,
         "clocks": clocks,
     }
@@ -324,6 +355,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--e2e-head-chunks", type=int, default=2,
+                    help="end-to-end step: split every batch element's heads into this many chunks")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
