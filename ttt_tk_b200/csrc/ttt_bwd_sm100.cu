@@ -39,6 +39,7 @@
 //
 // Deviations from the reference kernel (see include/ttt_mlp_b200.h): outputs are overwritten,
 // not accumulated; `Out` is never touched.  Every wait is bounded.
+#include <cstdio>
 #include <mutex>
 
 #include "ttt_device.cuh"
@@ -48,7 +49,8 @@ using namespace tttdev;
 
 namespace {
 
-constexpr int kThreads = 256;
+constexpr int kComputeThreads = 256;   // 8 compute warps: epilogues
+constexpr int kThreads = 288;          // + 1 producer warp: MMA issue, bulk loads and stores
 
 // Optional timeline of CTA 0 (compile with -DTTT_STAMPS): thread 0 records the global timer
 // whenever a wait or a publish step returns.  Off in the shipped library.
@@ -134,7 +136,9 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int quad = warp & 3, wg = warp >> 2;
+  const bool is_comp = warp < 8;              // compute warps run the epilogues
+  const bool is_prod0 = (tid == kComputeThreads);   // lane 0 of the producer warp issues every MMA and copy
+  const int quad = warp & 3, wg = (warp >> 2) & 1;
   const int hrow = wg * 128 + quad * 32 + lane;
   const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
   const TokMap tm(warp, lane);          // this thread's fragment of the 64 x 64 token-major tiles
@@ -198,6 +202,9 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       ph ^= 1u << b;
       pending &= ~(1u << b);
     }
+#ifdef TTT_DEBUG_WAIT
+    else if ((tid & 31) == 0) printf("wait gave up: bar %d warp %d blk %d\n", b, warp, (int)blockIdx.x);
+#endif
     TTT_STAMP(0x40 + b);
   };
   auto wait_mma = [&]() {
@@ -275,7 +282,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       tma_load_2d(tV, &tmV, &bars[BAR_V], 0, static_cast<int>(tok_rows0 + (long)(i0 + j) * 64));
       pending |= 1u << BAR_V;
     };
-    if (tid == 0) {
+    if (is_prod0) {
       issue_inputs(0);
       issue_v(0);
       if (gsz > 1) issue_inputs(1);
@@ -284,7 +291,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // ---- checkpoint -> tensor memory (fp32) + shared memory (bf16) + scratch slot 0 (bf16)
     float b1v = p.b1c[(sid * p.nck + ck) * 256 + hrow];
     if (tid < 64) sB2[tid] = p.b2c[(sid * p.nck + ck) * 64 + tid];
-    {
+    if (is_comp) {
       const float* W1g = p.W1c + (sid * p.nck + ck) * (64 * 256);
       const float* W2g = p.W2c + (sid * p.nck + ck) * (256 * 64) + hrow * 64;
 #pragma unroll 1
@@ -321,7 +328,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       tmem_wait_st();
     }
     publish();
-    if (tid == 0) {   // bf16 images of the checkpoint = pre-update weights of the group's first mini-batch
+    if (is_prod0) {   // bf16 images of the checkpoint = pre-update weights of the group's first mini-batch
       bulk_store_1d(p.sc_W1 + slot0 * 65536, bW1, BIG);
       bulk_store_1d(p.sc_W2 + slot0 * 65536, bW2, BIG);
       tma_commit_group();
@@ -338,7 +345,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       wait_bar(BAR_IN + s);
 
       // MMA1: Z1^T = W1^T K^T
-      if (warp == 0) {
+      if (warp == 8) {
         if (lane == 0) {
         tc_fence_after_sync();
         mma_hidden_major(tmem + TM_A, smem_u32(bW1), smem_u32(sK), false, false);
@@ -347,7 +354,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
-      {
+      if (is_comp) {
 #pragma unroll 1
         for (int half = 0; half < 2; ++half) {
           uint32_t v[32];
@@ -369,14 +376,14 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
       publish();
-      if (tid == 0) {
+      if (is_prod0) {
         bulk_store_1d(p.sc_X2 + slot * BIG, bX2, BIG);
         bulk_store_1d(p.sc_Z1 + slot * BIG, bZ1, BIG);
         tma_commit_group();
       }
 
       // MMA2: Z2 = X2 W2
-      if (warp == 0) {
+      if (warp == 8) {
         if (lane == 0) {
         tc_fence_after_sync();
         mma_token_major(tmem + TM_B, smem_u32(bX2), smem_u32(bW2));
@@ -386,7 +393,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       wait_mma();
       wait_bar(BAR_V);
-      {
+      if (is_comp) {
         float xh[16], b2c[8], gam[8], bet[8];
         tok_ld(tm, tmem + TM_B, xh);
         tok_ld_cols(tm, sB2, b2c);
@@ -446,11 +453,11 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           p.sc_sigf[slot * 64 + tm.r1] = 1.f / rs1;
         }
       }
-      if (tid == 0) tma_wait_group_read<0>();   // Z1 / X2 images have left shared memory
+      if (is_prod0) tma_wait_group_read<0>();   // Z1 / X2 images have left shared memory
       publish();
 
       // MMA3: R^T = W2 gZ2^T
-      if (warp == 0) {
+      if (warp == 8) {
         if (lane == 0) {
         if (j + 1 < gsz) issue_v(j + 1);        // V is consumed
         tc_fence_after_sync();
@@ -461,7 +468,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       if (tid >= 128 && tid < 192) sB2[tid - 128] += colsum(tU2, tid - 128);
       wait_mma();
-      {
+      if (is_comp) {
         float bsum = 0.f;
 #pragma unroll 1
         for (int half = 0; half < 2; ++half) {
@@ -492,7 +499,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
 
       // MMA4: W1^T += U1^T K ; W2 += X2^T U2
-      if (warp == 0) {
+      if (warp == 8) {
         if (lane == 0) {
         bulk_store_1d(p.sc_gZ1 + slot * BIG, bGP, BIG);
         tma_commit_group();
@@ -504,7 +511,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
-      {
+      if (is_comp) {
 #pragma unroll 1
         for (int half = 0; half < 2; ++half) {
           uint32_t v[32];
@@ -534,7 +541,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
 
       // MMA5: Z1b^T = W1+^T Q^T
-      if (warp == 0) {
+      if (warp == 8) {
         if (lane == 0) {
         if (j + 1 < gsz) {   // the new weights are the next mini-batch's pre-update weights
           bulk_store_1d(p.sc_W1 + (slot + 1) * 65536, bW1, BIG);
@@ -548,7 +555,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
-      {
+      if (is_comp) {
 #pragma unroll 1
         for (int half = 0; half < 2; ++half) {
           uint32_t v[32];
@@ -571,7 +578,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
 
       // MMA6: Z2b = X2b W2+ ; output LayerNorm statistics
-      if (warp == 0) {
+      if (warp == 8) {
         if (lane == 0) {
         bulk_store_1d(p.sc_X2b + slot * BIG, bX2, BIG);
         bulk_store_1d(p.sc_Z1b + slot * BIG, bZ1, BIG);
@@ -583,7 +590,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
-      {
+      if (is_comp) {
         float z[16], b2c[8];
         tok_ld(tm, tmem + TM_B, z);
         tok_ld_cols(tm, sB2, b2c);
@@ -605,16 +612,16 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           p.sc_sigln[slot * 64 + tm.r1] = 1.f / rs1;
         }
       }
-      if (tid == 0) tma_wait_group_read<0>();   // every image of this mini-batch has left shared memory
+      if (is_prod0) tma_wait_group_read<0>();   // every image of this mini-batch has left shared memory
       publish();
-      if (tid == 0 && j + 2 < gsz && !*abort_flag) issue_inputs(j + 2);
+      if (is_prod0 && j + 2 < gsz && !*abort_flag) issue_inputs(j + 2);
       if (*abort_flag) { aborted = true; break; }
     }
     if (aborted) break;
 
     // ================================================================== reverse sweep
     // dL/dW state: global (fp32) -> tensor memory
-    {
+    if (is_comp) {
 #pragma unroll 1
       for (int half = 0; half < 2; ++half) {
         uint32_t v[32];
@@ -673,9 +680,9 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // scratch was written partly with generic-proxy stores by all threads, partly with bulk
     // stores by thread 0: order both before the bulk (async-proxy) copies that read it back
     asm volatile("fence.proxy.async;" ::: "memory");
-    if (tid == 0) tma_wait_group<0>();
+    if (is_prod0) tma_wait_group<0>();
     publish();
-    if (tid == 0) {
+    if (is_prod0) {
       issue_tiles_a(gsz - 1);
       load_big(ib2, p.sc_Z1b + (slot0 + gsz - 1) * BIG);
       issue_rest(gsz - 1);
@@ -689,7 +696,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       // ---- S4: backward of the output LayerNorm
       wait_bar(BAR_T + 0);
       wait_bar(BAR_T + 1);
-      {
+      if (is_comp) {
         float go[16], xl[16], gam[8];
         tok_ld_tile(tm, t_go, go);
         tok_ld_tile(tm, t_a, xl);
@@ -720,7 +727,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tok_st_tile(tm, t_g, go);
       }
       publish();
-      if (warp == 0) {
+      if (warp == 8) {
         if (lane == 0) {
         // G1: gX2b^T = W2+ gZ2b^T
         tc_fence_after_sync();
@@ -746,7 +753,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       wait_mma();
       wait_bar(BAR_BIG + ib2);
       // ---- E1: gZ1b^T = gX2b^T * gelu'(Z1b^T), in place over Z1b^T
-      {
+      if (is_comp) {
         uint8_t* bz = big(ib2);
         float bsum = 0.f;
 #pragma unroll 1
@@ -769,14 +776,14 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         Gb1 += bsum;
       }
       publish();
-      if (tid == 0) {   // x_hat_ln and its column sums are consumed: bring grad_output_fused into that tile
+      if (is_prod0) {   // x_hat_ln and its column sums are consumed: bring grad_output_fused into that tile
         mbar_expect_tx(&bars[BAR_T + 1], TILE);
         bulk_load_1d(t_a, p.sc_gof + slot * TILE, TILE, &bars[BAR_T + 1]);
         pending |= 1u << (BAR_T + 1);
       }
       wait_bar(BAR_BIG + ib3);
       wait_bar(BAR_T + 2);
-      if (warp == 0) {
+      if (warp == 8) {
         if (lane == 0) {
         tc_fence_after_sync();
         mma_hidden_major(tmem + TM_S2, smem_u32(big(ib3)), smem_u32(t_g), true, true);   // G2
@@ -788,7 +795,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       wait_mma();
       // ---- E2: bf16 snapshots of the gradient state; dQ
-      {
+      if (is_comp) {
         uint8_t* s1b = big(ib0);
         uint8_t* s2b = big(ib1);
 #pragma unroll 1
@@ -810,7 +817,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         sGb1[hrow] = Gb1;
       }
-      {   // dQ = go + gZ1b W1+^T, staged over the dL/dOut tile and stored by TMA
+      if (is_comp) {   // dQ = go + gZ1b W1+^T, staged over the dL/dOut tile and stored by TMA
         float acc[16], go[16];
         tok_ld(tm, tmem + TM_B, acc);
         tok_ld_tile(tm, t_go, go);
@@ -819,7 +826,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tok_st_tile(tm, t_go, go);
       }
       publish();
-      if (tid == 0) {
+      if (is_prod0) {
         tma_store_2d(&tmDQ, t_go, 0, row0);
         tma_commit_group();
         load_big(ib2, p.sc_Z1 + slot * BIG);
@@ -827,7 +834,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       wait_bar(BAR_BIG + ib4);
       // ---- partial sums over the hidden units of gZ1 * G_b1 (fourth term of d_eta)
-      {
+      if (is_comp) {
         const int q = tid >> 6, t = tid & 63;
         const uint8_t* bg = big(ib4);
         float acc = 0.f;
@@ -838,7 +845,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
       wait_bar(BAR_T + 4);
       wait_bar(BAR_BIG + ib3);
-      if (warp == 0) {
+      if (warp == 8) {
         if (lane == 0) {
         tc_fence_after_sync();
         mma_hidden_major(tmem + TM_A, smem_u32(big(ib0)), smem_u32(t_k), false, false);   // G4
@@ -849,13 +856,13 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
-      if (tid == 0) {
+      if (is_prod0) {
         load_big(ib3, p.sc_W2 + slot * 65536);
         tma_wait_group_read<0>();     // dQ has left the dL/dOut tile (E4 reuses it for dV)
       }
       wait_bar(BAR_BIG + ib2);
       // ---- E3: A1, P = A1 gelu'(Z1), S = A1 gelu''(Z1), gelu'(Z1)
-      {
+      if (is_comp) {
         uint8_t* bz = big(ib2);
         uint8_t* bp = big(ib4);
         uint8_t* bgp = big(ib0);
@@ -885,7 +892,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
       wait_bar(BAR_BIG + ib3);
       wait_bar(BAR_T + 5);
-      if (warp == 0) {
+      if (warp == 8) {
         if (lane == 0) {
         tc_fence_after_sync();
         mma_token_major(tmem + TM_A, smem_u32(big(ib4)), smem_u32(big(ib3)));                 // G6
@@ -895,11 +902,11 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
-      if (tid == 0) load_big(ib4, p.sc_W1 + slot * 65536);
+      if (is_prod0) load_big(ib4, p.sc_W1 + slot * 65536);
       wait_bar(BAR_T + 6);
       wait_bar(BAR_T + 1);   // grad_output_fused
       // ---- E4: second order through the fused LayerNorm + L2 gradient (token-major, all 8 warps)
-      {
+      if (is_comp) {
         float A2[16], t1[16], gz[16], xh[16], go[16];
         float gam[8];
         tok_ld_cols(tm, sGamma, gam);
@@ -997,7 +1004,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
       publish();
-      if (warp == 0) {
+      if (warp == 8) {
         if (lane == 0) {
         tma_store_2d(&tmDV, t_go, 0, row0);
         tma_commit_group();
@@ -1017,9 +1024,9 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       wait_mma();
       // the state-gradient snapshot buffer is free: bring the next step's Z1_bar into it
-      if (tid == 0 && j > 0) load_big(ib1, p.sc_Z1b + (slot - 1) * BIG);
+      if (is_prod0 && j > 0) load_big(ib1, p.sc_Z1b + (slot - 1) * BIG);
       // ---- E5: gZ1in^T = gX2^T gelu'(Z1^T) + R^T S^T, in place over S^T
-      {
+      if (is_comp) {
         uint8_t* bs = big(ib2);
         const uint8_t* bgp = big(ib0);
         float bsum = 0.f;
@@ -1045,14 +1052,14 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         Gb1 += bsum;
       }
       publish();
-      if (tid == 0) {
+      if (is_prod0) {
         load_big(ib0, p.sc_X2 + slot * BIG);
         tma_wait_group_read<0>();     // dV has left its tile
         if (j > 0) issue_tiles_a(j - 1);
       }
       wait_bar(BAR_BIG + ib4);
       wait_bar(BAR_BIG + ib0);
-      if (warp == 0) {
+      if (warp == 8) {
         if (lane == 0) {
         tc_fence_after_sync();
         mma_token_major(tmem + TM_A, smem_u32(big(ib2)), smem_u32(big(ib4)));                 // G13
@@ -1064,7 +1071,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       wait_mma();
       // ---- E6: dK = partial + gZ1in W1^T, staged over the gZ2in tile and stored by TMA
-      {
+      if (is_comp) {
         float acc[16];
         tok_ld(tm, tmem + TM_A, acc);
 #pragma unroll
@@ -1072,7 +1079,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tok_st_tile(tm, t_q, kp);
       }
       publish();
-      if (tid == 0) {
+      if (is_prod0) {
         tma_store_2d(&tmDK, t_q, 0, row0);
         tma_commit_group();
         tma_wait_group_read<0>();     // the next step's Q lands in the same tile
@@ -1082,13 +1089,13 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const int n0 = ib4, n1 = ib3, n2 = ib1, n3 = ib2, n4 = ib0;
         ib0 = n0; ib1 = n1; ib2 = n2; ib3 = n3; ib4 = n4;
       }
-      if (tid == 0 && j > 0 && !*abort_flag) issue_rest(j - 1);
+      if (is_prod0 && j > 0 && !*abort_flag) issue_rest(j - 1);
       if (*abort_flag) { aborted = true; break; }
     }
     if (aborted) break;
 
     // ---- park the gradient state (tensor memory -> grad_L_W*_init); the last group leaves the result
-    {
+    if (is_comp) {
       __syncwarp();
 #pragma unroll 1
       for (int half = 0; half < 2; ++half) {
@@ -1112,7 +1119,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   }
 
   // ---- final vector outputs
-  if (!aborted) {
+  if (!aborted && is_comp) {
     p.gb1[sid * 256 + hrow] = Gb1;
     if (tid < 64) {
       p.gb2[sid * 64 + tid] = sGb2[tid];
@@ -1120,8 +1127,8 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       p.d_beta[sid * 64 + tid] = sDB[tid];
     }
   }
-  if (tid == 0) tma_wait_group<0>();
-  if (tid == 0 && (aborted || *abort_flag)) {
+  if (is_prod0) tma_wait_group<0>();
+  if (is_prod0 && (aborted || *abort_flag)) {
     for (int b = 0; b < 16; ++b)
       if (pending & (1u << b)) mbar_wait_bounded(&bars[b], (ph >> b) & 1u, abort_flag, limit);
     atomicExch(p.status, static_cast<uint32_t>(TTT_B200_ERR_TIMEOUT));
