@@ -86,7 +86,7 @@ constexpr uint32_t OFF_GB1 = OFF_SIGF + 256;         // fp32[256] copy of the pe
 constexpr uint32_t OFF_PART = OFF_GB1 + 1024;        // fp32[4][64] partial sums for d_eta
 constexpr uint32_t OFF_ETA = OFF_PART + 1024;        // bf16[2][64]
 constexpr uint32_t OFF_BAR = OFF_ETA + 256;          // 16 mbarriers
-constexpr uint32_t OFF_MISC = OFF_BAR + 128;
+constexpr uint32_t OFF_MISC = OFF_BAR + 192;
 constexpr uint32_t OFF_XCH = OFF_MISC + 64;        // fp32[2][64][8] row-sum exchange between warp pairs
 constexpr uint32_t SMEM_USED = OFF_XCH + 4096;
 constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;
@@ -98,6 +98,8 @@ constexpr int BAR_T = 5;       // +tile index (0..6)
 constexpr int BAR_IN = 12;     // +stage (0..1), recompute inputs
 constexpr int BAR_MMA = 14;
 constexpr int BAR_V = 15;      // recompute: the single V tile
+constexpr int BAR_MMB = 16;    // second MMA barrier: products whose results are not needed at once
+constexpr int NUM_BARS = 17;
 
 constexpr uint32_t TM_S1 = 0;      // W1^T / dL/dW1^T
 constexpr uint32_t TM_S2 = 128;    // W2   / dL/dW2
@@ -137,6 +139,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool is_comp = warp < 8;              // compute warps run the epilogues
+  const bool is_prod = !is_comp;              // the producer warp (all lanes follow the barriers)
   const bool is_prod0 = (tid == kComputeThreads);   // lane 0 of the producer warp issues every MMA and copy
   const int quad = warp & 3, wg = (warp >> 2) & 1;
   const int hrow = wg * 128 + quad * 32 + lane;
@@ -166,7 +169,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const uint64_t limit = p.wait_limit_ns;
 
   if (tid == 0) {
-    for (int i = 0; i < 16; ++i) mbar_init(&bars[i], 1);
+    for (int i = 0; i < NUM_BARS; ++i) mbar_init(&bars[i], 1);
     fence_mbar_init();
     *abort_flag = 0;
     prefetch_tmap(&tmQ);
@@ -376,11 +379,6 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
       publish();
-      if (is_prod0) {
-        bulk_store_1d(p.sc_X2 + slot * BIG, bX2, BIG);
-        bulk_store_1d(p.sc_Z1 + slot * BIG, bZ1, BIG);
-        tma_commit_group();
-      }
 
       // MMA2: Z2 = X2 W2
       if (warp == 8) {
@@ -388,6 +386,9 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tc_fence_after_sync();
         mma_token_major(tmem + TM_B, smem_u32(bX2), smem_u32(bW2));
         commit();
+        bulk_store_1d(p.sc_X2 + slot * BIG, bX2, BIG);
+        bulk_store_1d(p.sc_Z1 + slot * BIG, bZ1, BIG);
+        tma_commit_group();
       }
         __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
@@ -501,12 +502,12 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       // MMA4: W1^T += U1^T K ; W2 += X2^T U2
       if (warp == 8) {
         if (lane == 0) {
-        bulk_store_1d(p.sc_gZ1 + slot * BIG, bGP, BIG);
-        tma_commit_group();
         tc_fence_after_sync();
         mma_hidden_major(tmem + TM_S1, smem_u32(bZ1), smem_u32(sK), true, true);
         mma_hidden_major(tmem + TM_S2, smem_u32(bX2), smem_u32(tU2), true, true);
         commit();
+        bulk_store_1d(p.sc_gZ1 + slot * BIG, bGP, BIG);
+        tma_commit_group();
       }
         __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
@@ -543,14 +544,14 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       // MMA5: Z1b^T = W1+^T Q^T
       if (warp == 8) {
         if (lane == 0) {
+        tc_fence_after_sync();
+        mma_hidden_major(tmem + TM_A, smem_u32(bW1), smem_u32(sQ), false, false);
+        commit();
         if (j + 1 < gsz) {   // the new weights are the next mini-batch's pre-update weights
           bulk_store_1d(p.sc_W1 + (slot + 1) * 65536, bW1, BIG);
           bulk_store_1d(p.sc_W2 + (slot + 1) * 65536, bW2, BIG);
           tma_commit_group();
         }
-        tc_fence_after_sync();
-        mma_hidden_major(tmem + TM_A, smem_u32(bW1), smem_u32(sQ), false, false);
-        commit();
       }
         __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
@@ -580,12 +581,12 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       // MMA6: Z2b = X2b W2+ ; output LayerNorm statistics
       if (warp == 8) {
         if (lane == 0) {
-        bulk_store_1d(p.sc_X2b + slot * BIG, bX2, BIG);
-        bulk_store_1d(p.sc_Z1b + slot * BIG, bZ1, BIG);
-        tma_commit_group();
         tc_fence_after_sync();
         mma_token_major(tmem + TM_B, smem_u32(bX2), smem_u32(bW2));
         commit();
+        bulk_store_1d(p.sc_X2b + slot * BIG, bX2, BIG);
+        bulk_store_1d(p.sc_Z1b + slot * BIG, bZ1, BIG);
+        tma_commit_group();
       }
         __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
@@ -774,6 +775,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           }
         }
         Gb1 += bsum;
+        sGb1[hrow] = Gb1;
       }
       publish();
       if (is_prod0) {   // x_hat_ln and its column sums are consumed: bring grad_output_fused into that tile
@@ -794,7 +796,12 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
-      // ---- E2: bf16 snapshots of the gradient state; dQ
+      if (is_prod0) {   // gZ1b^T and X2b^T are consumed: bring Z1^T and X2^T in while E2 runs
+        load_big(ib2, p.sc_Z1 + slot * BIG);
+        load_big(ib3, p.sc_X2 + slot * BIG);
+      }
+      wait_bar(BAR_BIG + ib4);
+      // ---- E2: bf16 snapshots of the gradient state; dQ; partial sums for d_eta
       if (is_comp) {
         uint8_t* s1b = big(ib0);
         uint8_t* s2b = big(ib1);
@@ -815,7 +822,6 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 #pragma unroll
           for (int c = 0; c < 4; ++c) st_chunk(s2b, hrow, half * 4 + c, f + c * 8);
         }
-        sGb1[hrow] = Gb1;
       }
       if (is_comp) {   // dQ = go + gZ1b W1+^T, staged over the dL/dOut tile and stored by TMA
         float acc[16], go[16];
@@ -825,14 +831,6 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         for (int q = 0; q < 16; ++q) go[q] += acc[q];
         tok_st_tile(tm, t_go, go);
       }
-      publish();
-      if (is_prod0) {
-        tma_store_2d(&tmDQ, t_go, 0, row0);
-        tma_commit_group();
-        load_big(ib2, p.sc_Z1 + slot * BIG);
-        load_big(ib3, p.sc_X2 + slot * BIG);
-      }
-      wait_bar(BAR_BIG + ib4);
       // ---- partial sums over the hidden units of gZ1 * G_b1 (fourth term of d_eta)
       if (is_comp) {
         const int q = tid >> 6, t = tid & 63;
@@ -850,15 +848,22 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tc_fence_after_sync();
         mma_hidden_major(tmem + TM_A, smem_u32(big(ib0)), smem_u32(t_k), false, false);   // G4
         mma_token_major(tmem + TM_B, smem_u32(big(ib4)), smem_u32(big(ib0)));             // G8
-        mma_token_major(tmem + TM_B + 64, smem_u32(big(ib3)), smem_u32(big(ib1)));        // G5
         commit();
+        mma_token_major(tmem + TM_B + 64, smem_u32(big(ib3)), smem_u32(big(ib1)));        // G5: needed by E4 only
+        umma_commit(&bars[BAR_MMB]);
+        tma_store_2d(&tmDQ, t_go, 0, row0);
+        tma_commit_group();
       }
         __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
-      if (is_prod0) {
-        load_big(ib3, p.sc_W2 + slot * 65536);
-        tma_wait_group_read<0>();     // dQ has left the dL/dOut tile (E4 reuses it for dV)
+      if (is_prod) {   // while the compute warps run E3: X2^T is consumed once G5 is done -> W2 (pre-update)
+        wait_bar(BAR_MMB);
+        if (lane == 0) {
+          load_big(ib3, p.sc_W2 + slot * 65536);
+          tma_wait_group_read<0>();     // dQ has left the dL/dOut tile (E4 reuses it for dV)
+        }
+        __syncwarp();
       }
       wait_bar(BAR_BIG + ib2);
       // ---- E3: A1, P = A1 gelu'(Z1), S = A1 gelu''(Z1), gelu'(Z1)
@@ -890,19 +895,25 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
       publish();
+      if (is_comp) wait_bar(BAR_MMB);                       // G5 (acc1) is complete
       wait_bar(BAR_BIG + ib3);
       wait_bar(BAR_T + 5);
       if (warp == 8) {
         if (lane == 0) {
         tc_fence_after_sync();
         mma_token_major(tmem + TM_A, smem_u32(big(ib4)), smem_u32(big(ib3)));                 // G6
-        mma_hidden_major(tmem + TM_S2, smem_u32(big(ib4)), smem_u32(t_gz2), true, true);     // G10
         commit();
+        mma_hidden_major(tmem + TM_S2, smem_u32(big(ib4)), smem_u32(t_gz2), true, true);     // G10: state only
+        umma_commit(&bars[BAR_MMB]);
       }
         __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
-      if (is_prod0) load_big(ib4, p.sc_W1 + slot * 65536);
+      if (is_prod) {   // while the compute warps run E4: P^T is consumed once G10 is done -> W1^T (pre-update)
+        wait_bar(BAR_MMB);
+        if (lane == 0) load_big(ib4, p.sc_W1 + slot * 65536);
+        __syncwarp();
+      }
       wait_bar(BAR_T + 6);
       wait_bar(BAR_T + 1);   // grad_output_fused
       // ---- E4: second order through the fused LayerNorm + L2 gradient (token-major, all 8 warps)
@@ -1004,15 +1015,16 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
       publish();
+      if (is_comp) wait_bar(BAR_MMB);                       // G10 (tracking only)
       if (warp == 8) {
         if (lane == 0) {
-        tma_store_2d(&tmDV, t_go, 0, row0);
-        tma_commit_group();
         tc_fence_after_sync();
         mma_hidden_major(tmem + TM_B, smem_u32(big(ib3)), smem_u32(t_q), false, false);      // G11
         mma_hidden_major(tmem + TM_B, smem_u32(big(ib1)), smem_u32(t_g), false, true);       // + G_W2snap U2^T
         mma_hidden_major(tmem + TM_A, smem_u32(big(ib3)), smem_u32(t_gz2), false, false);    // G12
         commit();
+        tma_store_2d(&tmDV, t_go, 0, row0);
+        tma_commit_group();
       }
         __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
@@ -1052,37 +1064,40 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         Gb1 += bsum;
       }
       publish();
-      if (is_prod0) {
-        load_big(ib0, p.sc_X2 + slot * BIG);
-        tma_wait_group_read<0>();     // dV has left its tile
-        if (j > 0) issue_tiles_a(j - 1);
-      }
+      if (is_prod0) load_big(ib0, p.sc_X2 + slot * BIG);   // X2^T again, for the last state product
       wait_bar(BAR_BIG + ib4);
-      wait_bar(BAR_BIG + ib0);
-      if (warp == 8) {
+      if (is_prod) {
         if (lane == 0) {
-        tc_fence_after_sync();
-        mma_token_major(tmem + TM_A, smem_u32(big(ib2)), smem_u32(big(ib4)));                 // G13
-        mma_hidden_major(tmem + TM_S1, smem_u32(big(ib2)), smem_u32(t_k), true, true);       // G15
-        mma_hidden_major(tmem + TM_S2, smem_u32(big(ib0)), smem_u32(t_q), true, true);       // G14
-        commit();
-      }
-        __syncwarp();   // the other lanes do not spin while lane 0 issues
+          tc_fence_after_sync();
+          mma_token_major(tmem + TM_A, smem_u32(big(ib2)), smem_u32(big(ib4)));                 // G13
+          mma_hidden_major(tmem + TM_S1, smem_u32(big(ib2)), smem_u32(t_k), true, true);       // G15
+          commit();
+        }
+        wait_bar(BAR_BIG + ib0);
+        if (lane == 0) {
+          mma_hidden_major(tmem + TM_S2, smem_u32(big(ib0)), smem_u32(t_q), true, true);       // G14: state only
+          umma_commit(&bars[BAR_MMB]);
+          tma_wait_group_read<0>();     // dV has left its tile
+          if (j > 0) issue_tiles_a(j - 1);
+        }
+        __syncwarp();
       }
       wait_mma();
-      // ---- E6: dK = partial + gZ1in W1^T, staged over the gZ2in tile and stored by TMA
+      // ---- E6: dK = partial + gZ1in W1^T, staged over the K tile (G15 has consumed it), stored by TMA
       if (is_comp) {
         float acc[16];
         tok_ld(tm, tmem + TM_A, acc);
 #pragma unroll
         for (int q = 0; q < 16; ++q) kp[q] += acc[q];
-        tok_st_tile(tm, t_q, kp);
+        tok_st_tile(tm, t_k, kp);
       }
       publish();
+      if (is_comp) wait_bar(BAR_BIG + ib0);                 // tracking only
+      wait_bar(BAR_MMB);                                    // G14 done: the state and every operand tile are settled
       if (is_prod0) {
-        tma_store_2d(&tmDK, t_q, 0, row0);
+        tma_store_2d(&tmDK, t_k, 0, row0);
         tma_commit_group();
-        tma_wait_group_read<0>();     // the next step's Q lands in the same tile
+        tma_wait_group_read<0>();     // the next step's K lands in the same tile
       }
       // pre-update weights of this mini-batch are the post-update weights of the previous one
       {
@@ -1129,7 +1144,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   }
   if (is_prod0) tma_wait_group<0>();
   if (is_prod0 && (aborted || *abort_flag)) {
-    for (int b = 0; b < 16; ++b)
+    for (int b = 0; b < NUM_BARS; ++b)
       if (pending & (1u << b)) mbar_wait_bounded(&bars[b], (ph >> b) & 1u, abort_flag, limit);
     atomicExch(p.status, static_cast<uint32_t>(TTT_B200_ERR_TIMEOUT));
   }
