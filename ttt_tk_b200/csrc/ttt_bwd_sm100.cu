@@ -42,6 +42,7 @@
 #include <cstdio>
 #include <mutex>
 
+#define TTT_MMA_ROLLED 1
 #include "ttt_device.cuh"
 #include "ttt_internal.h"
 
@@ -359,19 +360,19 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       wait_mma();
       if (is_comp) {
 #pragma unroll 1
-        for (int half = 0; half < 2; ++half) {
-          uint32_t v[32];
-          tmem_ld32(tmem + lane_base + TM_A + wg * 64 + half * 32, v);
+        for (int half = 0; half < 4; ++half) {   // 16 columns per pass
+          uint32_t v[16];
+          tmem_ld16(tmem + lane_base + TM_A + wg * 64 + half * 16, v);
           tmem_wait_ld();
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2; ++c) {
             float z[8], g[8], gp[8];
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
               z[k] = __uint_as_float(v[c * 8 + k]) + b1v;
               gelu_pair(z[k], g[k], gp[k]);
             }
-            const uint32_t off = sw128_off(hrow, half * 4 + c);
+            const uint32_t off = sw128_off(hrow, half * 2 + c);
             *reinterpret_cast<uint4*>(bX2 + off) = pack_chunk(g);
             *reinterpret_cast<uint4*>(bGP + off) = pack_chunk(gp);
             *reinterpret_cast<uint4*>(bZ1 + off) = pack_chunk(z);
@@ -472,14 +473,14 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       if (is_comp) {
         float bsum = 0.f;
 #pragma unroll 1
-        for (int half = 0; half < 2; ++half) {
-          uint32_t v[32];
-          tmem_ld32(tmem + lane_base + TM_A + wg * 64 + half * 32, v);
+        for (int half = 0; half < 4; ++half) {   // 16 columns per pass
+          uint32_t v[16];
+          tmem_ld16(tmem + lane_base + TM_A + wg * 64 + half * 16, v);
           tmem_wait_ld();
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2; ++c) {
             float gp[8], u[8];
-            const uint32_t off = sw128_off(hrow, half * 4 + c);
+            const uint32_t off = sw128_off(hrow, half * 2 + c);
             unpack_chunk(*reinterpret_cast<const uint4*>(bGP + off), gp);
 #pragma unroll
             for (int k = 0; k < 8; ++k) gp[k] *= __uint_as_float(v[c * 8 + k]);     // dl/dZ1
@@ -489,7 +490,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             unpack_chunk(w, gb);
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
-              u[k] = -__bfloat162float(eta[half * 32 + c * 8 + k]) * gb[k];
+              u[k] = -__bfloat162float(eta[half * 16 + c * 8 + k]) * gb[k];
               bsum += u[k];
             }
             *reinterpret_cast<uint4*>(bZ1 + off) = pack_chunk(u);  // U1 = -eta dl/dZ1, over Z1
@@ -514,27 +515,27 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       wait_mma();
       if (is_comp) {
 #pragma unroll 1
-        for (int half = 0; half < 2; ++half) {
-          uint32_t v[32];
-          float f[32];
-          tmem_ld32(tmem + lane_base + TM_S1 + wg * 64 + half * 32, v);
+        for (int half = 0; half < 4; ++half) {   // 16 columns per pass
+          uint32_t v[16];
+          float f[16];
+          tmem_ld16(tmem + lane_base + TM_S1 + wg * 64 + half * 16, v);
           tmem_wait_ld();
 #pragma unroll
-          for (int q = 0; q < 32; ++q) f[q] = __uint_as_float(v[q]);
+          for (int q = 0; q < 16; ++q) f[q] = __uint_as_float(v[q]);
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2; ++c) {
             const uint4 w = pack_chunk(f + c * 8);
-            const uint32_t off = sw128_off(hrow, half * 4 + c);
+            const uint32_t off = sw128_off(hrow, half * 2 + c);
             *reinterpret_cast<uint4*>(bW1 + off) = w;
           }
-          tmem_ld32(tmem + lane_base + TM_S2 + wg * 64 + half * 32, v);
+          tmem_ld16(tmem + lane_base + TM_S2 + wg * 64 + half * 16, v);
           tmem_wait_ld();
 #pragma unroll
-          for (int q = 0; q < 32; ++q) f[q] = __uint_as_float(v[q]);
+          for (int q = 0; q < 16; ++q) f[q] = __uint_as_float(v[q]);
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2; ++c) {
             const uint4 w = pack_chunk(f + c * 8);
-            const uint32_t off = sw128_off(hrow, half * 4 + c);
+            const uint32_t off = sw128_off(hrow, half * 2 + c);
             *reinterpret_cast<uint4*>(bW2 + off) = w;
           }
         }
@@ -558,19 +559,19 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       wait_mma();
       if (is_comp) {
 #pragma unroll 1
-        for (int half = 0; half < 2; ++half) {
-          uint32_t v[32];
-          tmem_ld32(tmem + lane_base + TM_A + wg * 64 + half * 32, v);
+        for (int half = 0; half < 4; ++half) {   // 16 columns per pass
+          uint32_t v[16];
+          tmem_ld16(tmem + lane_base + TM_A + wg * 64 + half * 16, v);
           tmem_wait_ld();
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2; ++c) {
             float z[8], g[8];
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
               z[k] = __uint_as_float(v[c * 8 + k]) + b1v;
               g[k] = gelu_only(z[k]);
             }
-            const uint32_t off = sw128_off(hrow, half * 4 + c);
+            const uint32_t off = sw128_off(hrow, half * 2 + c);
             *reinterpret_cast<uint4*>(bX2 + off) = pack_chunk(g);
             *reinterpret_cast<uint4*>(bZ1 + off) = pack_chunk(z);
           }
@@ -758,20 +759,20 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         uint8_t* bz = big(ib2);
         float bsum = 0.f;
 #pragma unroll 1
-        for (int half = 0; half < 2; ++half) {
-          uint32_t v[32];
-          tmem_ld32(tmem + lane_base + TM_A + wg * 64 + half * 32, v);
+        for (int half = 0; half < 4; ++half) {   // 16 columns per pass
+          uint32_t v[16];
+          tmem_ld16(tmem + lane_base + TM_A + wg * 64 + half * 16, v);
           tmem_wait_ld();
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2; ++c) {
             float z[8];
-            ld_chunk(bz, hrow, half * 4 + c, z);
+            ld_chunk(bz, hrow, half * 2 + c, z);
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
               z[k] = __uint_as_float(v[c * 8 + k]) * gelu_grad(z[k]);
               bsum += z[k];
             }
-            st_chunk(bz, hrow, half * 4 + c, z);
+            st_chunk(bz, hrow, half * 2 + c, z);
           }
         }
         Gb1 += bsum;
@@ -806,21 +807,21 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         uint8_t* s1b = big(ib0);
         uint8_t* s2b = big(ib1);
 #pragma unroll 1
-        for (int half = 0; half < 2; ++half) {
-          uint32_t v[32];
-          float f[32];
-          tmem_ld32(tmem + lane_base + TM_S1 + wg * 64 + half * 32, v);
+        for (int half = 0; half < 4; ++half) {   // 16 columns per pass
+          uint32_t v[16];
+          float f[16];
+          tmem_ld16(tmem + lane_base + TM_S1 + wg * 64 + half * 16, v);
           tmem_wait_ld();
 #pragma unroll
-          for (int q = 0; q < 32; ++q) f[q] = __uint_as_float(v[q]);
+          for (int q = 0; q < 16; ++q) f[q] = __uint_as_float(v[q]);
 #pragma unroll
-          for (int c = 0; c < 4; ++c) st_chunk(s1b, hrow, half * 4 + c, f + c * 8);
-          tmem_ld32(tmem + lane_base + TM_S2 + wg * 64 + half * 32, v);
+          for (int c = 0; c < 2; ++c) st_chunk(s1b, hrow, half * 2 + c, f + c * 8);
+          tmem_ld16(tmem + lane_base + TM_S2 + wg * 64 + half * 16, v);
           tmem_wait_ld();
 #pragma unroll
-          for (int q = 0; q < 32; ++q) f[q] = __uint_as_float(v[q]);
+          for (int q = 0; q < 16; ++q) f[q] = __uint_as_float(v[q]);
 #pragma unroll
-          for (int c = 0; c < 4; ++c) st_chunk(s2b, hrow, half * 4 + c, f + c * 8);
+          for (int c = 0; c < 2; ++c) st_chunk(s2b, hrow, half * 2 + c, f + c * 8);
         }
       }
       if (is_comp) {   // dQ = go + gZ1b W1+^T, staged over the dL/dOut tile and stored by TMA
@@ -872,25 +873,25 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         uint8_t* bp = big(ib4);
         uint8_t* bgp = big(ib0);
 #pragma unroll 1
-        for (int half = 0; half < 2; ++half) {
-          uint32_t v[32];
-          tmem_ld32(tmem + lane_base + TM_A + wg * 64 + half * 32, v);
+        for (int half = 0; half < 4; ++half) {   // 16 columns per pass
+          uint32_t v[16];
+          tmem_ld16(tmem + lane_base + TM_A + wg * 64 + half * 16, v);
           tmem_wait_ld();
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2; ++c) {
             float z[8], pp[8], gp[8];
-            ld_chunk(bz, hrow, half * 4 + c, z);
+            ld_chunk(bz, hrow, half * 2 + c, z);
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
-              const float a1 = -__bfloat162float(sEta[half * 32 + c * 8 + k]) * (__uint_as_float(v[c * 8 + k]) + Gb1);
+              const float a1 = -__bfloat162float(sEta[half * 16 + c * 8 + k]) * (__uint_as_float(v[c * 8 + k]) + Gb1);
               float gpp;
               gelu_grad_pair(z[k], gp[k], gpp);
               pp[k] = a1 * gp[k];
               z[k] = a1 * gpp;
             }
-            st_chunk(bp, hrow, half * 4 + c, pp);
-            st_chunk(bz, hrow, half * 4 + c, z);
-            st_chunk(bgp, hrow, half * 4 + c, gp);
+            st_chunk(bp, hrow, half * 2 + c, pp);
+            st_chunk(bz, hrow, half * 2 + c, z);
+            st_chunk(bgp, hrow, half * 2 + c, gp);
           }
         }
       }
@@ -1043,22 +1044,22 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const uint8_t* bgp = big(ib0);
         float bsum = 0.f;
 #pragma unroll 1
-        for (int half = 0; half < 2; ++half) {
-          uint32_t v[32], w[32];
-          tmem_ld32(tmem + lane_base + TM_B + wg * 64 + half * 32, v);
-          tmem_ld32(tmem + lane_base + TM_A + wg * 64 + half * 32, w);
+        for (int half = 0; half < 4; ++half) {   // 16 columns per pass
+          uint32_t v[16], w[16];
+          tmem_ld16(tmem + lane_base + TM_B + wg * 64 + half * 16, v);
+          tmem_ld16(tmem + lane_base + TM_A + wg * 64 + half * 16, w);
           tmem_wait_ld();
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2; ++c) {
             float gp[8], sv[8];
-            ld_chunk(bgp, hrow, half * 4 + c, gp);
-            ld_chunk(bs, hrow, half * 4 + c, sv);
+            ld_chunk(bgp, hrow, half * 2 + c, gp);
+            ld_chunk(bs, hrow, half * 2 + c, sv);
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
               sv[k] = fmaf(__uint_as_float(v[c * 8 + k]), gp[k], __uint_as_float(w[c * 8 + k]) * sv[k]);
               bsum += sv[k];
             }
-            st_chunk(bs, hrow, half * 4 + c, sv);
+            st_chunk(bs, hrow, half * 2 + c, sv);
           }
         }
         Gb1 += bsum;

@@ -73,6 +73,17 @@ __device__ __forceinline__ float ld_elem(const uint8_t* tile, uint32_t row, uint
       *reinterpret_cast<const __nv_bfloat16*>(tile + sw128_off(row, col >> 3) + (col & 7) * 2));
 }
 
+// A kernel whose instruction footprint exceeds the instruction cache defines TTT_MMA_ROLLED 1 before
+// including this header (rolled issue loops); a small kernel keeps them unrolled (lower issue latency).
+#ifndef TTT_MMA_ROLLED
+#define TTT_MMA_ROLLED 0
+#endif
+#if TTT_MMA_ROLLED
+#define TTT_MMA_LOOP _Pragma("unroll 1")
+#else
+#define TTT_MMA_LOOP _Pragma("unroll")
+#endif
+
 // ---- MMA issue.  One thread issues every MMA of the kernels, so the instruction stream
 // around each tcgen05.mma is kept to two integer adds: the descriptors' high words are the
 // same constant for every operand (stride byte offset 1024, version 1, 128-byte swizzle) and
@@ -102,11 +113,11 @@ __device__ __forceinline__ void mma_hidden_major_t(uint32_t tmem_d, uint32_t a_s
   const uint32_t a0 = desc_lo(a_smem, 16);
   const uint32_t b0 = desc_lo(b_smem, kBMn ? 8192 : 16);
   constexpr uint32_t bstep = kBMn ? (2048u >> 4) : (32u >> 4);
-#pragma unroll
+TTT_MMA_LOOP
   for (int blk = 0; blk < 2; ++blk) {
     if (kAccumulate) mma_issue<true>(tmem_d + blk * 64, a0 + blk * (16384u >> 4), b0, idesc);
     else             mma_issue<false>(tmem_d + blk * 64, a0 + blk * (16384u >> 4), b0, idesc);
-#pragma unroll
+TTT_MMA_LOOP
     for (int j = 1; j < 4; ++j)
       mma_issue<true>(tmem_d + blk * 64, a0 + blk * (16384u >> 4) + j * 2, b0 + j * bstep, idesc);
   }
@@ -128,7 +139,7 @@ __device__ __forceinline__ void mma_token_major(uint32_t tmem_d, uint32_t x_smem
   const uint32_t a0 = desc_lo(x_smem, BIG);
   const uint32_t b0 = desc_lo(w_smem, BIG);
   mma_issue<false>(tmem_d, a0, b0, idesc);
-#pragma unroll
+TTT_MMA_LOOP
   for (int j = 1; j < 16; ++j) mma_issue<true>(tmem_d, a0 + j * (2048u >> 4), b0 + j * (2048u >> 4), idesc);
 }
 
