@@ -40,6 +40,11 @@ WORKLOADS = {
 U_FLOP = 2 * 64 * 64 * 256            # one GEMM unit per mini-batch per (b,h)
 FWD_U, BWD_U = 7, 22                  # algorithmic GEMM units: forward; backward (7 recompute + 15 sweep)
 STATE_BYTES = 132352                  # fp32 W1 + b1 + W2 + b2 of one (b,h)
+# DRAM bytes per (stream, mini-batch) from the ncu capture summarised in profiles/ttt_fwd_bwd_kernels_current.md
+# (dram__bytes_read.sum + dram__bytes_write.sum over 128 streams x 16 mini-batches); the traffic grows in
+# proportion to the number of (stream, mini-batch) pairs, so a full-size launch is scaled from it.
+NCU_BWD_DRAM_BYTES_PER_MB = (587722752 + 605817856) / 2048
+NCU_FWD_DRAM_BYTES_PER_MB = (67628288 + 7943680) / 2048
 
 
 def algorithmic_bytes(B, H, NC, cgs):
@@ -286,7 +291,9 @@ def run_ours(args, rank, world, local_rank):
                     "bwd_algorithmic_gbs": bwd_bytes / (bwd_ms * 1e-3) / 1e9,
                     "streams_per_gpu": B * H},
         "roofline": {"kernel": "ttt_bwd_kernel", "bound": "tensor", "achieved": bwd_tf, "peak": peak_tf,
-                     "unit": "TFLOP/s", "frac": bwd_tf / peak_tf, "traffic": None,
+                     "unit": "TFLOP/s", "frac": bwd_tf / peak_tf,
+                     "traffic": NCU_BWD_DRAM_BYTES_PER_MB * B * H * NC,
+                     "traffic_note": "bytes per launch, scaled from an ncu capture of a smaller launch by (streams x mini-batches)",
                      "peak_source": f"{pk_src} (sustained cuBLAS bf16: kernel timed inside a long step)"},
         "e2e": {"value": tokens_per_step / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
