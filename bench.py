@@ -338,7 +338,7 @@ def run_reference(args, rank, world):
         return None
     B, H, NC, cgs, desc = WORKLOADS[args.workload]
     threads = os.cpu_count() or 1
-    sB, sH = 1, min(4, H)
+    sB, sH = 1, H          # one batch element, all heads: enough parallel work for every host core
     K, W = args.steps, args.warmup
     rate, sec = cpu_oracle_rate(sB, sH, NC, cgs, H, reps=max(1, min(K, 5)), threads=threads)
     sample = (f"PyTorch-eager fp32 oracle, fwd + hand-derived bwd, slice B={sB} H={sH} of the workload's "
@@ -386,7 +386,7 @@ def main():
         if world == 1 and not args.no_cpu_baseline:
             B, H, NC, cgs, _ = WORKLOADS[args.workload]
             threads = os.cpu_count() or 1
-            sB, sH = 1, min(4, H)
+            sB, sH = 1, H      # one batch element, all heads (about 10-20 s of CPU work in total)
             rate, sec = cpu_oracle_rate(sB, sH, NC, cgs, H, reps=3, threads=threads)
             res["cpu_baseline"] = {
                 "value": rate, "unit": "tokens/s", "cores": threads, "kind": "port",
