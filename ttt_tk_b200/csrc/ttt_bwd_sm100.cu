@@ -39,7 +39,6 @@
 //
 // Deviations from the reference kernel (see include/ttt_mlp_b200.h): outputs are overwritten,
 // not accumulated; `Out` is never touched.  Every wait is bounded.
-#include <cstdio>
 #include <mutex>
 
 #define TTT_MMA_ROLLED 1
@@ -50,8 +49,7 @@ using namespace tttdev;
 
 namespace {
 
-constexpr int kComputeThreads = 256;   // 8 compute warps: epilogues
-constexpr int kThreads = 288;          // + 1 producer warp: MMA issue, bulk loads and stores
+constexpr int kThreads = 256;
 
 // Optional timeline of CTA 0 (compile with -DTTT_STAMPS): thread 0 records the global timer
 // whenever a wait or a publish step returns.  Off in the shipped library.
@@ -87,7 +85,7 @@ constexpr uint32_t OFF_GB1 = OFF_SIGF + 256;         // fp32[256] copy of the pe
 constexpr uint32_t OFF_PART = OFF_GB1 + 1024;        // fp32[4][64] partial sums for d_eta
 constexpr uint32_t OFF_ETA = OFF_PART + 1024;        // bf16[2][64]
 constexpr uint32_t OFF_BAR = OFF_ETA + 256;          // 16 mbarriers
-constexpr uint32_t OFF_MISC = OFF_BAR + 192;
+constexpr uint32_t OFF_MISC = OFF_BAR + 128;
 constexpr uint32_t OFF_XCH = OFF_MISC + 64;        // fp32[2][64][8] row-sum exchange between warp pairs
 constexpr uint32_t SMEM_USED = OFF_XCH + 4096;
 constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;
@@ -99,8 +97,6 @@ constexpr int BAR_T = 5;       // +tile index (0..6)
 constexpr int BAR_IN = 12;     // +stage (0..1), recompute inputs
 constexpr int BAR_MMA = 14;
 constexpr int BAR_V = 15;      // recompute: the single V tile
-constexpr int BAR_MMB = 16;    // second MMA barrier: products whose results are not needed at once
-constexpr int NUM_BARS = 17;
 
 constexpr uint32_t TM_S1 = 0;      // W1^T / dL/dW1^T
 constexpr uint32_t TM_S2 = 128;    // W2   / dL/dW2
@@ -139,10 +135,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const bool is_comp = warp < 8;              // compute warps run the epilogues
-  const bool is_prod = !is_comp;              // the producer warp (all lanes follow the barriers)
-  const bool is_prod0 = (tid == kComputeThreads);   // lane 0 of the producer warp issues every MMA and copy
-  const int quad = warp & 3, wg = (warp >> 2) & 1;
+  const int quad = warp & 3, wg = warp >> 2;
   const int hrow = wg * 128 + quad * 32 + lane;
   const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
   const TokMap tm(warp, lane);          // this thread's fragment of the 64 x 64 token-major tiles
@@ -170,7 +163,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const uint64_t limit = p.wait_limit_ns;
 
   if (tid == 0) {
-    for (int i = 0; i < NUM_BARS; ++i) mbar_init(&bars[i], 1);
+    for (int i = 0; i < 16; ++i) mbar_init(&bars[i], 1);
     fence_mbar_init();
     *abort_flag = 0;
     prefetch_tmap(&tmQ);
@@ -206,9 +199,6 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       ph ^= 1u << b;
       pending &= ~(1u << b);
     }
-#ifdef TTT_DEBUG_WAIT
-    else if ((tid & 31) == 0) printf("wait gave up: bar %d warp %d blk %d\n", b, warp, (int)blockIdx.x);
-#endif
     TTT_STAMP(0x40 + b);
   };
   auto wait_mma = [&]() {
@@ -286,7 +276,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       tma_load_2d(tV, &tmV, &bars[BAR_V], 0, static_cast<int>(tok_rows0 + (long)(i0 + j) * 64));
       pending |= 1u << BAR_V;
     };
-    if (is_prod0) {
+    if (tid == 0) {
       issue_inputs(0);
       issue_v(0);
       if (gsz > 1) issue_inputs(1);
@@ -295,7 +285,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // ---- checkpoint -> tensor memory (fp32) + shared memory (bf16) + scratch slot 0 (bf16)
     float b1v = p.b1c[(sid * p.nck + ck) * 256 + hrow];
     if (tid < 64) sB2[tid] = p.b2c[(sid * p.nck + ck) * 64 + tid];
-    if (is_comp) {
+    {
       const float* W1g = p.W1c + (sid * p.nck + ck) * (64 * 256);
       const float* W2g = p.W2c + (sid * p.nck + ck) * (256 * 64) + hrow * 64;
 #pragma unroll 1
@@ -332,7 +322,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       tmem_wait_st();
     }
     publish();
-    if (is_prod0) {   // bf16 images of the checkpoint = pre-update weights of the group's first mini-batch
+    if (tid == 0) {   // bf16 images of the checkpoint = pre-update weights of the group's first mini-batch
       bulk_store_1d(p.sc_W1 + slot0 * 65536, bW1, BIG);
       bulk_store_1d(p.sc_W2 + slot0 * 65536, bW2, BIG);
       tma_commit_group();
@@ -349,7 +339,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       wait_bar(BAR_IN + s);
 
       // MMA1: Z1^T = W1^T K^T
-      if (warp == 8) {
+      if (warp == 0) {
         if (lane == 0) {
         tc_fence_after_sync();
         mma_hidden_major(tmem + TM_A, smem_u32(bW1), smem_u32(sK), false, false);
@@ -358,7 +348,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
-      if (is_comp) {
+      {
 #pragma unroll 1
         for (int half = 0; half < 4; ++half) {   // 16 columns per pass
           uint32_t v[16];
@@ -380,22 +370,24 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
       publish();
+      if (tid == 0) {
+        bulk_store_1d(p.sc_X2 + slot * BIG, bX2, BIG);
+        bulk_store_1d(p.sc_Z1 + slot * BIG, bZ1, BIG);
+        tma_commit_group();
+      }
 
       // MMA2: Z2 = X2 W2
-      if (warp == 8) {
+      if (warp == 0) {
         if (lane == 0) {
         tc_fence_after_sync();
         mma_token_major(tmem + TM_B, smem_u32(bX2), smem_u32(bW2));
         commit();
-        bulk_store_1d(p.sc_X2 + slot * BIG, bX2, BIG);
-        bulk_store_1d(p.sc_Z1 + slot * BIG, bZ1, BIG);
-        tma_commit_group();
       }
         __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
       wait_bar(BAR_V);
-      if (is_comp) {
+      {
         float xh[16], b2c[8], gam[8], bet[8];
         tok_ld(tm, tmem + TM_B, xh);
         tok_ld_cols(tm, sB2, b2c);
@@ -455,11 +447,11 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           p.sc_sigf[slot * 64 + tm.r1] = 1.f / rs1;
         }
       }
-      if (is_prod0) tma_wait_group_read<0>();   // Z1 / X2 images have left shared memory
+      if (tid == 0) tma_wait_group_read<0>();   // Z1 / X2 images have left shared memory
       publish();
 
       // MMA3: R^T = W2 gZ2^T
-      if (warp == 8) {
+      if (warp == 0) {
         if (lane == 0) {
         if (j + 1 < gsz) issue_v(j + 1);        // V is consumed
         tc_fence_after_sync();
@@ -470,7 +462,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       if (tid >= 128 && tid < 192) sB2[tid - 128] += colsum(tU2, tid - 128);
       wait_mma();
-      if (is_comp) {
+      {
         float bsum = 0.f;
 #pragma unroll 1
         for (int half = 0; half < 4; ++half) {   // 16 columns per pass
@@ -501,19 +493,19 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
 
       // MMA4: W1^T += U1^T K ; W2 += X2^T U2
-      if (warp == 8) {
+      if (warp == 0) {
         if (lane == 0) {
+        bulk_store_1d(p.sc_gZ1 + slot * BIG, bGP, BIG);
+        tma_commit_group();
         tc_fence_after_sync();
         mma_hidden_major(tmem + TM_S1, smem_u32(bZ1), smem_u32(sK), true, true);
         mma_hidden_major(tmem + TM_S2, smem_u32(bX2), smem_u32(tU2), true, true);
         commit();
-        bulk_store_1d(p.sc_gZ1 + slot * BIG, bGP, BIG);
-        tma_commit_group();
       }
         __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
-      if (is_comp) {
+      {
 #pragma unroll 1
         for (int half = 0; half < 4; ++half) {   // 16 columns per pass
           uint32_t v[16];
@@ -543,21 +535,21 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
 
       // MMA5: Z1b^T = W1+^T Q^T
-      if (warp == 8) {
+      if (warp == 0) {
         if (lane == 0) {
-        tc_fence_after_sync();
-        mma_hidden_major(tmem + TM_A, smem_u32(bW1), smem_u32(sQ), false, false);
-        commit();
         if (j + 1 < gsz) {   // the new weights are the next mini-batch's pre-update weights
           bulk_store_1d(p.sc_W1 + (slot + 1) * 65536, bW1, BIG);
           bulk_store_1d(p.sc_W2 + (slot + 1) * 65536, bW2, BIG);
           tma_commit_group();
         }
+        tc_fence_after_sync();
+        mma_hidden_major(tmem + TM_A, smem_u32(bW1), smem_u32(sQ), false, false);
+        commit();
       }
         __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
-      if (is_comp) {
+      {
 #pragma unroll 1
         for (int half = 0; half < 4; ++half) {   // 16 columns per pass
           uint32_t v[16];
@@ -580,19 +572,19 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
 
       // MMA6: Z2b = X2b W2+ ; output LayerNorm statistics
-      if (warp == 8) {
+      if (warp == 0) {
         if (lane == 0) {
-        tc_fence_after_sync();
-        mma_token_major(tmem + TM_B, smem_u32(bX2), smem_u32(bW2));
-        commit();
         bulk_store_1d(p.sc_X2b + slot * BIG, bX2, BIG);
         bulk_store_1d(p.sc_Z1b + slot * BIG, bZ1, BIG);
         tma_commit_group();
+        tc_fence_after_sync();
+        mma_token_major(tmem + TM_B, smem_u32(bX2), smem_u32(bW2));
+        commit();
       }
         __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
-      if (is_comp) {
+      {
         float z[16], b2c[8];
         tok_ld(tm, tmem + TM_B, z);
         tok_ld_cols(tm, sB2, b2c);
@@ -614,16 +606,16 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           p.sc_sigln[slot * 64 + tm.r1] = 1.f / rs1;
         }
       }
-      if (is_prod0) tma_wait_group_read<0>();   // every image of this mini-batch has left shared memory
+      if (tid == 0) tma_wait_group_read<0>();   // every image of this mini-batch has left shared memory
       publish();
-      if (is_prod0 && j + 2 < gsz && !*abort_flag) issue_inputs(j + 2);
+      if (tid == 0 && j + 2 < gsz && !*abort_flag) issue_inputs(j + 2);
       if (*abort_flag) { aborted = true; break; }
     }
     if (aborted) break;
 
     // ================================================================== reverse sweep
     // dL/dW state: global (fp32) -> tensor memory
-    if (is_comp) {
+    {
 #pragma unroll 1
       for (int half = 0; half < 2; ++half) {
         uint32_t v[32];
@@ -682,9 +674,9 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // scratch was written partly with generic-proxy stores by all threads, partly with bulk
     // stores by thread 0: order both before the bulk (async-proxy) copies that read it back
     asm volatile("fence.proxy.async;" ::: "memory");
-    if (is_prod0) tma_wait_group<0>();
+    if (tid == 0) tma_wait_group<0>();
     publish();
-    if (is_prod0) {
+    if (tid == 0) {
       issue_tiles_a(gsz - 1);
       load_big(ib2, p.sc_Z1b + (slot0 + gsz - 1) * BIG);
       issue_rest(gsz - 1);
@@ -698,7 +690,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       // ---- S4: backward of the output LayerNorm
       wait_bar(BAR_T + 0);
       wait_bar(BAR_T + 1);
-      if (is_comp) {
+      {
         float go[16], xl[16], gam[8];
         tok_ld_tile(tm, t_go, go);
         tok_ld_tile(tm, t_a, xl);
@@ -729,7 +721,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tok_st_tile(tm, t_g, go);
       }
       publish();
-      if (warp == 8) {
+      if (warp == 0) {
         if (lane == 0) {
         // G1: gX2b^T = W2+ gZ2b^T
         tc_fence_after_sync();
@@ -755,7 +747,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       wait_mma();
       wait_bar(BAR_BIG + ib2);
       // ---- E1: gZ1b^T = gX2b^T * gelu'(Z1b^T), in place over Z1b^T
-      if (is_comp) {
+      {
         uint8_t* bz = big(ib2);
         float bsum = 0.f;
 #pragma unroll 1
@@ -776,17 +768,16 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           }
         }
         Gb1 += bsum;
-        sGb1[hrow] = Gb1;
       }
       publish();
-      if (is_prod0) {   // x_hat_ln and its column sums are consumed: bring grad_output_fused into that tile
+      if (tid == 0) {   // x_hat_ln and its column sums are consumed: bring grad_output_fused into that tile
         mbar_expect_tx(&bars[BAR_T + 1], TILE);
         bulk_load_1d(t_a, p.sc_gof + slot * TILE, TILE, &bars[BAR_T + 1]);
         pending |= 1u << (BAR_T + 1);
       }
       wait_bar(BAR_BIG + ib3);
       wait_bar(BAR_T + 2);
-      if (warp == 8) {
+      if (warp == 0) {
         if (lane == 0) {
         tc_fence_after_sync();
         mma_hidden_major(tmem + TM_S2, smem_u32(big(ib3)), smem_u32(t_g), true, true);   // G2
@@ -797,13 +788,8 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
-      if (is_prod0) {   // gZ1b^T and X2b^T are consumed: bring Z1^T and X2^T in while E2 runs
-        load_big(ib2, p.sc_Z1 + slot * BIG);
-        load_big(ib3, p.sc_X2 + slot * BIG);
-      }
-      wait_bar(BAR_BIG + ib4);
-      // ---- E2: bf16 snapshots of the gradient state; dQ; partial sums for d_eta
-      if (is_comp) {
+      // ---- E2: bf16 snapshots of the gradient state; dQ
+      {
         uint8_t* s1b = big(ib0);
         uint8_t* s2b = big(ib1);
 #pragma unroll 1
@@ -823,8 +809,9 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 #pragma unroll
           for (int c = 0; c < 2; ++c) st_chunk(s2b, hrow, half * 2 + c, f + c * 8);
         }
+        sGb1[hrow] = Gb1;
       }
-      if (is_comp) {   // dQ = go + gZ1b W1+^T, staged over the dL/dOut tile and stored by TMA
+      {   // dQ = go + gZ1b W1+^T, staged over the dL/dOut tile and stored by TMA
         float acc[16], go[16];
         tok_ld(tm, tmem + TM_B, acc);
         tok_ld_tile(tm, t_go, go);
@@ -832,8 +819,16 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         for (int q = 0; q < 16; ++q) go[q] += acc[q];
         tok_st_tile(tm, t_go, go);
       }
+      publish();
+      if (tid == 0) {
+        tma_store_2d(&tmDQ, t_go, 0, row0);
+        tma_commit_group();
+        load_big(ib2, p.sc_Z1 + slot * BIG);
+        load_big(ib3, p.sc_X2 + slot * BIG);
+      }
+      wait_bar(BAR_BIG + ib4);
       // ---- partial sums over the hidden units of gZ1 * G_b1 (fourth term of d_eta)
-      if (is_comp) {
+      {
         const int q = tid >> 6, t = tid & 63;
         const uint8_t* bg = big(ib4);
         float acc = 0.f;
@@ -844,31 +839,24 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
       wait_bar(BAR_T + 4);
       wait_bar(BAR_BIG + ib3);
-      if (warp == 8) {
+      if (warp == 0) {
         if (lane == 0) {
         tc_fence_after_sync();
         mma_hidden_major(tmem + TM_A, smem_u32(big(ib0)), smem_u32(t_k), false, false);   // G4
         mma_token_major(tmem + TM_B, smem_u32(big(ib4)), smem_u32(big(ib0)));             // G8
+        mma_token_major(tmem + TM_B + 64, smem_u32(big(ib3)), smem_u32(big(ib1)));        // G5
         commit();
-        mma_token_major(tmem + TM_B + 64, smem_u32(big(ib3)), smem_u32(big(ib1)));        // G5: needed by E4 only
-        umma_commit(&bars[BAR_MMB]);
-        tma_store_2d(&tmDQ, t_go, 0, row0);
-        tma_commit_group();
       }
         __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
-      if (is_prod) {   // while the compute warps run E3: X2^T is consumed once G5 is done -> W2 (pre-update)
-        wait_bar(BAR_MMB);
-        if (lane == 0) {
-          load_big(ib3, p.sc_W2 + slot * 65536);
-          tma_wait_group_read<0>();     // dQ has left the dL/dOut tile (E4 reuses it for dV)
-        }
-        __syncwarp();
+      if (tid == 0) {
+        load_big(ib3, p.sc_W2 + slot * 65536);
+        tma_wait_group_read<0>();     // dQ has left the dL/dOut tile (E4 reuses it for dV)
       }
       wait_bar(BAR_BIG + ib2);
       // ---- E3: A1, P = A1 gelu'(Z1), S = A1 gelu''(Z1), gelu'(Z1)
-      if (is_comp) {
+      {
         uint8_t* bz = big(ib2);
         uint8_t* bp = big(ib4);
         uint8_t* bgp = big(ib0);
@@ -896,29 +884,23 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
       publish();
-      if (is_comp) wait_bar(BAR_MMB);                       // G5 (acc1) is complete
       wait_bar(BAR_BIG + ib3);
       wait_bar(BAR_T + 5);
-      if (warp == 8) {
+      if (warp == 0) {
         if (lane == 0) {
         tc_fence_after_sync();
         mma_token_major(tmem + TM_A, smem_u32(big(ib4)), smem_u32(big(ib3)));                 // G6
+        mma_hidden_major(tmem + TM_S2, smem_u32(big(ib4)), smem_u32(t_gz2), true, true);     // G10
         commit();
-        mma_hidden_major(tmem + TM_S2, smem_u32(big(ib4)), smem_u32(t_gz2), true, true);     // G10: state only
-        umma_commit(&bars[BAR_MMB]);
       }
         __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
-      if (is_prod) {   // while the compute warps run E4: P^T is consumed once G10 is done -> W1^T (pre-update)
-        wait_bar(BAR_MMB);
-        if (lane == 0) load_big(ib4, p.sc_W1 + slot * 65536);
-        __syncwarp();
-      }
+      if (tid == 0) load_big(ib4, p.sc_W1 + slot * 65536);
       wait_bar(BAR_T + 6);
       wait_bar(BAR_T + 1);   // grad_output_fused
       // ---- E4: second order through the fused LayerNorm + L2 gradient (token-major, all 8 warps)
-      if (is_comp) {
+      {
         float A2[16], t1[16], gz[16], xh[16], go[16];
         float gam[8];
         tok_ld_cols(tm, sGamma, gam);
@@ -1016,16 +998,15 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
       publish();
-      if (is_comp) wait_bar(BAR_MMB);                       // G10 (tracking only)
-      if (warp == 8) {
+      if (warp == 0) {
         if (lane == 0) {
+        tma_store_2d(&tmDV, t_go, 0, row0);
+        tma_commit_group();
         tc_fence_after_sync();
         mma_hidden_major(tmem + TM_B, smem_u32(big(ib3)), smem_u32(t_q), false, false);      // G11
         mma_hidden_major(tmem + TM_B, smem_u32(big(ib1)), smem_u32(t_g), false, true);       // + G_W2snap U2^T
         mma_hidden_major(tmem + TM_A, smem_u32(big(ib3)), smem_u32(t_gz2), false, false);    // G12
         commit();
-        tma_store_2d(&tmDV, t_go, 0, row0);
-        tma_commit_group();
       }
         __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
@@ -1037,9 +1018,9 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       wait_mma();
       // the state-gradient snapshot buffer is free: bring the next step's Z1_bar into it
-      if (is_prod0 && j > 0) load_big(ib1, p.sc_Z1b + (slot - 1) * BIG);
+      if (tid == 0 && j > 0) load_big(ib1, p.sc_Z1b + (slot - 1) * BIG);
       // ---- E5: gZ1in^T = gX2^T gelu'(Z1^T) + R^T S^T, in place over S^T
-      if (is_comp) {
+      {
         uint8_t* bs = big(ib2);
         const uint8_t* bgp = big(ib0);
         float bsum = 0.f;
@@ -1065,53 +1046,50 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         Gb1 += bsum;
       }
       publish();
-      if (is_prod0) load_big(ib0, p.sc_X2 + slot * BIG);   // X2^T again, for the last state product
+      if (tid == 0) {
+        load_big(ib0, p.sc_X2 + slot * BIG);
+        tma_wait_group_read<0>();     // dV has left its tile
+        if (j > 0) issue_tiles_a(j - 1);
+      }
       wait_bar(BAR_BIG + ib4);
-      if (is_prod) {
+      wait_bar(BAR_BIG + ib0);
+      if (warp == 0) {
         if (lane == 0) {
-          tc_fence_after_sync();
-          mma_token_major(tmem + TM_A, smem_u32(big(ib2)), smem_u32(big(ib4)));                 // G13
-          mma_hidden_major(tmem + TM_S1, smem_u32(big(ib2)), smem_u32(t_k), true, true);       // G15
-          commit();
-        }
-        wait_bar(BAR_BIG + ib0);
-        if (lane == 0) {
-          mma_hidden_major(tmem + TM_S2, smem_u32(big(ib0)), smem_u32(t_q), true, true);       // G14: state only
-          umma_commit(&bars[BAR_MMB]);
-          tma_wait_group_read<0>();     // dV has left its tile
-          if (j > 0) issue_tiles_a(j - 1);
-        }
-        __syncwarp();
+        tc_fence_after_sync();
+        mma_token_major(tmem + TM_A, smem_u32(big(ib2)), smem_u32(big(ib4)));                 // G13
+        mma_hidden_major(tmem + TM_S1, smem_u32(big(ib2)), smem_u32(t_k), true, true);       // G15
+        mma_hidden_major(tmem + TM_S2, smem_u32(big(ib0)), smem_u32(t_q), true, true);       // G14
+        commit();
+      }
+        __syncwarp();   // the other lanes do not spin while lane 0 issues
       }
       wait_mma();
-      // ---- E6: dK = partial + gZ1in W1^T, staged over the K tile (G15 has consumed it), stored by TMA
-      if (is_comp) {
+      // ---- E6: dK = partial + gZ1in W1^T, staged over the gZ2in tile and stored by TMA
+      {
         float acc[16];
         tok_ld(tm, tmem + TM_A, acc);
 #pragma unroll
         for (int q = 0; q < 16; ++q) kp[q] += acc[q];
-        tok_st_tile(tm, t_k, kp);
+        tok_st_tile(tm, t_q, kp);
       }
       publish();
-      if (is_comp) wait_bar(BAR_BIG + ib0);                 // tracking only
-      wait_bar(BAR_MMB);                                    // G14 done: the state and every operand tile are settled
-      if (is_prod0) {
-        tma_store_2d(&tmDK, t_k, 0, row0);
+      if (tid == 0) {
+        tma_store_2d(&tmDK, t_q, 0, row0);
         tma_commit_group();
-        tma_wait_group_read<0>();     // the next step's K lands in the same tile
+        tma_wait_group_read<0>();     // the next step's Q lands in the same tile
       }
       // pre-update weights of this mini-batch are the post-update weights of the previous one
       {
         const int n0 = ib4, n1 = ib3, n2 = ib1, n3 = ib2, n4 = ib0;
         ib0 = n0; ib1 = n1; ib2 = n2; ib3 = n3; ib4 = n4;
       }
-      if (is_prod0 && j > 0 && !*abort_flag) issue_rest(j - 1);
+      if (tid == 0 && j > 0 && !*abort_flag) issue_rest(j - 1);
       if (*abort_flag) { aborted = true; break; }
     }
     if (aborted) break;
 
     // ---- park the gradient state (tensor memory -> grad_L_W*_init); the last group leaves the result
-    if (is_comp) {
+    {
       __syncwarp();
 #pragma unroll 1
       for (int half = 0; half < 2; ++half) {
@@ -1135,7 +1113,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   }
 
   // ---- final vector outputs
-  if (!aborted && is_comp) {
+  if (!aborted) {
     p.gb1[sid * 256 + hrow] = Gb1;
     if (tid < 64) {
       p.gb2[sid * 64 + tid] = sGb2[tid];
@@ -1143,9 +1121,9 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       p.d_beta[sid * 64 + tid] = sDB[tid];
     }
   }
-  if (is_prod0) tma_wait_group<0>();
-  if (is_prod0 && (aborted || *abort_flag)) {
-    for (int b = 0; b < NUM_BARS; ++b)
+  if (tid == 0) tma_wait_group<0>();
+  if (tid == 0 && (aborted || *abort_flag)) {
+    for (int b = 0; b < 16; ++b)
       if (pending & (1u << b)) mbar_wait_bounded(&bars[b], (ph >> b) & 1u, abort_flag, limit);
     atomicExch(p.status, static_cast<uint32_t>(TTT_B200_ERR_TIMEOUT));
   }
