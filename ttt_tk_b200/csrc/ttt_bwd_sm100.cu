@@ -41,7 +41,9 @@
 // not accumulated; `Out` is never touched.  Every wait is bounded.
 #include <mutex>
 
+#ifndef TTT_MMA_ROLLED
 #define TTT_MMA_ROLLED 1
+#endif
 #include "ttt_device.cuh"
 #include "ttt_internal.h"
 
@@ -50,6 +52,22 @@ using namespace tttdev;
 namespace {
 
 constexpr int kThreads = 256;
+
+// The MMAs of one phase are issued by lane 0 of warps 0..3: four instruction streams on four
+// schedulers instead of one.  Every issuer commits (an issuer without work too), so the MMA
+// barrier counts four arrivals per phase.
+#define TTT_ISSUE(W0, W1, W2, W3)   \
+  if (warp < 4) {                   \
+    if (lane == 0) {                \
+      tc_fence_after_sync();        \
+      if (warp == 0) { W0; }        \
+      else if (warp == 1) { W1; }   \
+      else if (warp == 2) { W2; }   \
+      else { W3; }                  \
+      commit();                     \
+    }                               \
+    __syncwarp();                   \
+  }
 
 // Optional timeline of CTA 0 (compile with -DTTT_STAMPS): thread 0 records the global timer
 // whenever a wait or a publish step returns.  Off in the shipped library.
@@ -163,7 +181,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const uint64_t limit = p.wait_limit_ns;
 
   if (tid == 0) {
-    for (int i = 0; i < 16; ++i) mbar_init(&bars[i], 1);
+    for (int i = 0; i < 16; ++i) mbar_init(&bars[i], i == BAR_MMA ? 4 : 1);
     fence_mbar_init();
     *abort_flag = 0;
     prefetch_tmap(&tmQ);
@@ -339,14 +357,10 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       wait_bar(BAR_IN + s);
 
       // MMA1: Z1^T = W1^T K^T
-      if (warp == 0) {
-        if (lane == 0) {
-        tc_fence_after_sync();
-        mma_hidden_major(tmem + TM_A, smem_u32(bW1), smem_u32(sK), false, false);
-        commit();
-      }
-        __syncwarp();   // the other lanes do not spin while lane 0 issues
-      }
+      TTT_ISSUE(mma_hidden_half(tmem + TM_A, smem_u32(bW1), smem_u32(sK), false, false, 0),
+                mma_hidden_half(tmem + TM_A, smem_u32(bW1), smem_u32(sK), false, false, 1),
+                ,
+                )
       wait_mma();
       {
 #pragma unroll 1
@@ -377,14 +391,10 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
 
       // MMA2: Z2 = X2 W2
-      if (warp == 0) {
-        if (lane == 0) {
-        tc_fence_after_sync();
-        mma_token_major(tmem + TM_B, smem_u32(bX2), smem_u32(bW2));
-        commit();
-      }
-        __syncwarp();   // the other lanes do not spin while lane 0 issues
-      }
+      TTT_ISSUE(mma_token_major(tmem + TM_B, smem_u32(bX2), smem_u32(bW2)),
+                ,
+                ,
+                )
       wait_mma();
       wait_bar(BAR_V);
       {
@@ -451,15 +461,13 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
 
       // MMA3: R^T = W2 gZ2^T
-      if (warp == 0) {
-        if (lane == 0) {
+      if (tid == 0) {
         if (j + 1 < gsz) issue_v(j + 1);        // V is consumed
-        tc_fence_after_sync();
-        mma_hidden_major(tmem + TM_A, smem_u32(bW2), smem_u32(tGZ2), false, false);
-        commit();
       }
-        __syncwarp();   // the other lanes do not spin while lane 0 issues
-      }
+      TTT_ISSUE(mma_hidden_half(tmem + TM_A, smem_u32(bW2), smem_u32(tGZ2), false, false, 0),
+                mma_hidden_half(tmem + TM_A, smem_u32(bW2), smem_u32(tGZ2), false, false, 1),
+                ,
+                )
       if (tid >= 128 && tid < 192) sB2[tid - 128] += colsum(tU2, tid - 128);
       wait_mma();
       {
@@ -493,17 +501,14 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
 
       // MMA4: W1^T += U1^T K ; W2 += X2^T U2
-      if (warp == 0) {
-        if (lane == 0) {
+      if (tid == 0) {
         bulk_store_1d(p.sc_gZ1 + slot * BIG, bGP, BIG);
         tma_commit_group();
-        tc_fence_after_sync();
-        mma_hidden_major(tmem + TM_S1, smem_u32(bZ1), smem_u32(sK), true, true);
-        mma_hidden_major(tmem + TM_S2, smem_u32(bX2), smem_u32(tU2), true, true);
-        commit();
       }
-        __syncwarp();   // the other lanes do not spin while lane 0 issues
-      }
+      TTT_ISSUE(mma_hidden_half(tmem + TM_S1, smem_u32(bZ1), smem_u32(sK), true, true, 0),
+                mma_hidden_half(tmem + TM_S1, smem_u32(bZ1), smem_u32(sK), true, true, 1),
+                mma_hidden_half(tmem + TM_S2, smem_u32(bX2), smem_u32(tU2), true, true, 0),
+                mma_hidden_half(tmem + TM_S2, smem_u32(bX2), smem_u32(tU2), true, true, 1))
       wait_mma();
       {
 #pragma unroll 1
@@ -535,19 +540,17 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
 
       // MMA5: Z1b^T = W1+^T Q^T
-      if (warp == 0) {
-        if (lane == 0) {
+      if (tid == 0) {
         if (j + 1 < gsz) {   // the new weights are the next mini-batch's pre-update weights
           bulk_store_1d(p.sc_W1 + (slot + 1) * 65536, bW1, BIG);
           bulk_store_1d(p.sc_W2 + (slot + 1) * 65536, bW2, BIG);
           tma_commit_group();
         }
-        tc_fence_after_sync();
-        mma_hidden_major(tmem + TM_A, smem_u32(bW1), smem_u32(sQ), false, false);
-        commit();
       }
-        __syncwarp();   // the other lanes do not spin while lane 0 issues
-      }
+      TTT_ISSUE(mma_hidden_half(tmem + TM_A, smem_u32(bW1), smem_u32(sQ), false, false, 0),
+                mma_hidden_half(tmem + TM_A, smem_u32(bW1), smem_u32(sQ), false, false, 1),
+                ,
+                )
       wait_mma();
       {
 #pragma unroll 1
@@ -572,17 +575,15 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
 
       // MMA6: Z2b = X2b W2+ ; output LayerNorm statistics
-      if (warp == 0) {
-        if (lane == 0) {
+      if (tid == 0) {
         bulk_store_1d(p.sc_X2b + slot * BIG, bX2, BIG);
         bulk_store_1d(p.sc_Z1b + slot * BIG, bZ1, BIG);
         tma_commit_group();
-        tc_fence_after_sync();
-        mma_token_major(tmem + TM_B, smem_u32(bX2), smem_u32(bW2));
-        commit();
       }
-        __syncwarp();   // the other lanes do not spin while lane 0 issues
-      }
+      TTT_ISSUE(mma_token_major(tmem + TM_B, smem_u32(bX2), smem_u32(bW2)),
+                ,
+                ,
+                )
       wait_mma();
       {
         float z[16], b2c[8];
@@ -721,15 +722,11 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tok_st_tile(tm, t_g, go);
       }
       publish();
-      if (warp == 0) {
-        if (lane == 0) {
-        // G1: gX2b^T = W2+ gZ2b^T
-        tc_fence_after_sync();
-        mma_hidden_major(tmem + TM_A, smem_u32(big(ib1)), smem_u32(t_g), false, false);
-        commit();
-      }
-        __syncwarp();   // the other lanes do not spin while lane 0 issues
-      }
+      // G1: gX2b^T = W2+ gZ2b^T
+      TTT_ISSUE(mma_hidden_half(tmem + TM_A, smem_u32(big(ib1)), smem_u32(t_g), false, false, 0),
+                mma_hidden_half(tmem + TM_A, smem_u32(big(ib1)), smem_u32(t_g), false, false, 1),
+                ,
+                )
       if (tid >= 128 && tid < 192) {
         // column sums over the tokens: d_beta += sum go, d_gamma += sum go * x_hat_ln, G_b2 += sum gZ2b
         const int f = tid - 128;
@@ -777,16 +774,11 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       wait_bar(BAR_BIG + ib3);
       wait_bar(BAR_T + 2);
-      if (warp == 0) {
-        if (lane == 0) {
-        tc_fence_after_sync();
-        mma_hidden_major(tmem + TM_S2, smem_u32(big(ib3)), smem_u32(t_g), true, true);   // G2
-        mma_hidden_major(tmem + TM_S1, smem_u32(big(ib2)), smem_u32(t_q), true, true);   // G3
-        mma_token_major(tmem + TM_B, smem_u32(big(ib2)), smem_u32(big(ib0)));            // G7
-        commit();
-      }
-        __syncwarp();   // the other lanes do not spin while lane 0 issues
-      }
+      // G2 // G3 // G7
+      TTT_ISSUE(mma_token_major(tmem + TM_B, smem_u32(big(ib2)), smem_u32(big(ib0))),
+                mma_hidden_major(tmem + TM_S2, smem_u32(big(ib3)), smem_u32(t_g), true, true),
+                mma_hidden_half(tmem + TM_S1, smem_u32(big(ib2)), smem_u32(t_q), true, true, 0),
+                mma_hidden_half(tmem + TM_S1, smem_u32(big(ib2)), smem_u32(t_q), true, true, 1))
       wait_mma();
       // ---- E2: bf16 snapshots of the gradient state; dQ
       {
@@ -839,16 +831,11 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
       wait_bar(BAR_T + 4);
       wait_bar(BAR_BIG + ib3);
-      if (warp == 0) {
-        if (lane == 0) {
-        tc_fence_after_sync();
-        mma_hidden_major(tmem + TM_A, smem_u32(big(ib0)), smem_u32(t_k), false, false);   // G4
-        mma_token_major(tmem + TM_B, smem_u32(big(ib4)), smem_u32(big(ib0)));             // G8
-        mma_token_major(tmem + TM_B + 64, smem_u32(big(ib3)), smem_u32(big(ib1)));        // G5
-        commit();
-      }
-        __syncwarp();   // the other lanes do not spin while lane 0 issues
-      }
+      // G4 // G8 // G5
+      TTT_ISSUE(mma_token_major(tmem + TM_B, smem_u32(big(ib4)), smem_u32(big(ib0))),
+                mma_token_major(tmem + TM_B + 64, smem_u32(big(ib3)), smem_u32(big(ib1))),
+                mma_hidden_half(tmem + TM_A, smem_u32(big(ib0)), smem_u32(t_k), false, false, 0),
+                mma_hidden_half(tmem + TM_A, smem_u32(big(ib0)), smem_u32(t_k), false, false, 1))
       wait_mma();
       if (tid == 0) {
         load_big(ib3, p.sc_W2 + slot * 65536);
@@ -886,15 +873,11 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
       wait_bar(BAR_BIG + ib3);
       wait_bar(BAR_T + 5);
-      if (warp == 0) {
-        if (lane == 0) {
-        tc_fence_after_sync();
-        mma_token_major(tmem + TM_A, smem_u32(big(ib4)), smem_u32(big(ib3)));                 // G6
-        mma_hidden_major(tmem + TM_S2, smem_u32(big(ib4)), smem_u32(t_gz2), true, true);     // G10
-        commit();
-      }
-        __syncwarp();   // the other lanes do not spin while lane 0 issues
-      }
+      // G6 // G10
+      TTT_ISSUE(mma_token_major(tmem + TM_A, smem_u32(big(ib4)), smem_u32(big(ib3))),
+                mma_hidden_half(tmem + TM_S2, smem_u32(big(ib4)), smem_u32(t_gz2), true, true, 0),
+                mma_hidden_half(tmem + TM_S2, smem_u32(big(ib4)), smem_u32(t_gz2), true, true, 1),
+                )
       wait_mma();
       if (tid == 0) load_big(ib4, p.sc_W1 + slot * 65536);
       wait_bar(BAR_T + 6);
@@ -998,18 +981,17 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
       publish();
-      if (warp == 0) {
-        if (lane == 0) {
+      // G11
+      // + G_W2snap U2^T
+      // G12
+      if (tid == 0) {
         tma_store_2d(&tmDV, t_go, 0, row0);
         tma_commit_group();
-        tc_fence_after_sync();
-        mma_hidden_major(tmem + TM_B, smem_u32(big(ib3)), smem_u32(t_q), false, false);      // G11
-        mma_hidden_major(tmem + TM_B, smem_u32(big(ib1)), smem_u32(t_g), false, true);       // + G_W2snap U2^T
-        mma_hidden_major(tmem + TM_A, smem_u32(big(ib3)), smem_u32(t_gz2), false, false);    // G12
-        commit();
       }
-        __syncwarp();   // the other lanes do not spin while lane 0 issues
-      }
+      TTT_ISSUE(mma_hidden_half(tmem + TM_B, smem_u32(big(ib3)), smem_u32(t_q), false, false, 0); mma_hidden_half(tmem + TM_B, smem_u32(big(ib1)), smem_u32(t_g), false, true, 0),
+                mma_hidden_half(tmem + TM_B, smem_u32(big(ib3)), smem_u32(t_q), false, false, 1); mma_hidden_half(tmem + TM_B, smem_u32(big(ib1)), smem_u32(t_g), false, true, 1),
+                mma_hidden_half(tmem + TM_A, smem_u32(big(ib3)), smem_u32(t_gz2), false, false, 0),
+                mma_hidden_half(tmem + TM_A, smem_u32(big(ib3)), smem_u32(t_gz2), false, false, 1))
       if (tid >= 128 && tid < 192) {
         const int f = tid - 128;
         sGb2[f] += colsum(t_q, f);
@@ -1053,16 +1035,11 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       wait_bar(BAR_BIG + ib4);
       wait_bar(BAR_BIG + ib0);
-      if (warp == 0) {
-        if (lane == 0) {
-        tc_fence_after_sync();
-        mma_token_major(tmem + TM_A, smem_u32(big(ib2)), smem_u32(big(ib4)));                 // G13
-        mma_hidden_major(tmem + TM_S1, smem_u32(big(ib2)), smem_u32(t_k), true, true);       // G15
-        mma_hidden_major(tmem + TM_S2, smem_u32(big(ib0)), smem_u32(t_q), true, true);       // G14
-        commit();
-      }
-        __syncwarp();   // the other lanes do not spin while lane 0 issues
-      }
+      // G13 // G15 // G14
+      TTT_ISSUE(mma_token_major(tmem + TM_A, smem_u32(big(ib2)), smem_u32(big(ib4))),
+                mma_hidden_major(tmem + TM_S1, smem_u32(big(ib2)), smem_u32(t_k), true, true),
+                mma_hidden_half(tmem + TM_S2, smem_u32(big(ib0)), smem_u32(t_q), true, true, 0),
+                mma_hidden_half(tmem + TM_S2, smem_u32(big(ib0)), smem_u32(t_q), true, true, 1))
       wait_mma();
       // ---- E6: dK = partial + gZ1in W1^T, staged over the gZ2in tile and stored by TMA
       {

@@ -78,10 +78,15 @@ __device__ __forceinline__ float ld_elem(const uint8_t* tile, uint32_t row, uint
 #ifndef TTT_MMA_ROLLED
 #define TTT_MMA_ROLLED 0
 #endif
-#if TTT_MMA_ROLLED
+#if TTT_MMA_ROLLED == 1
 #define TTT_MMA_LOOP _Pragma("unroll 1")
+#define TTT_MMA_OUTER _Pragma("unroll 1")
+#elif TTT_MMA_ROLLED == 2
+#define TTT_MMA_LOOP _Pragma("unroll 4")
+#define TTT_MMA_OUTER _Pragma("unroll 1")
 #else
 #define TTT_MMA_LOOP _Pragma("unroll")
+#define TTT_MMA_OUTER _Pragma("unroll")
 #endif
 
 // ---- MMA issue.  One thread issues every MMA of the kernels, so the instruction stream
@@ -107,19 +112,33 @@ __device__ __forceinline__ void mma_issue(uint32_t tmem_d, uint32_t a_lo, uint32
 // "Hidden-major" product: D[256 x 64] (two M=128 blocks, 64 fp32 columns each, at tmem_d and
 // tmem_d + 64) (+)= A * B with A a [256][64] bf16 tile read K-major (row = hidden unit) and B a
 // [64][64] tile read K-major (row = N index) or MN-major (row = K index).
+// One M = 128 block (`blk` = 0 or 1: hidden units 128 blk .. 128 blk + 127) of the product.  The two
+// blocks are independent, so two threads may issue one each.
 template <bool kBMn, bool kAccumulate>
-__device__ __forceinline__ void mma_hidden_major_t(uint32_t tmem_d, uint32_t a_smem, uint32_t b_smem) {
+__device__ __forceinline__ void mma_hidden_half_t(uint32_t tmem_d, uint32_t a_smem, uint32_t b_smem, int blk) {
   constexpr uint32_t idesc = umma_idesc_bf16(128, 64, false, kBMn, false);
-  const uint32_t a0 = desc_lo(a_smem, 16);
+  const uint32_t a0 = desc_lo(a_smem, 16) + blk * (16384u >> 4);
   const uint32_t b0 = desc_lo(b_smem, kBMn ? 8192 : 16);
   constexpr uint32_t bstep = kBMn ? (2048u >> 4) : (32u >> 4);
+  const uint32_t d = tmem_d + blk * 64;
+  if (kAccumulate) mma_issue<true>(d, a0, b0, idesc);
+  else             mma_issue<false>(d, a0, b0, idesc);
 TTT_MMA_LOOP
-  for (int blk = 0; blk < 2; ++blk) {
-    if (kAccumulate) mma_issue<true>(tmem_d + blk * 64, a0 + blk * (16384u >> 4), b0, idesc);
-    else             mma_issue<false>(tmem_d + blk * 64, a0 + blk * (16384u >> 4), b0, idesc);
-TTT_MMA_LOOP
-    for (int j = 1; j < 4; ++j)
-      mma_issue<true>(tmem_d + blk * 64, a0 + blk * (16384u >> 4) + j * 2, b0 + j * bstep, idesc);
+  for (int j = 1; j < 4; ++j) mma_issue<true>(d, a0 + j * 2, b0 + j * bstep, idesc);
+}
+template <bool kBMn, bool kAccumulate>
+__device__ __forceinline__ void mma_hidden_major_t(uint32_t tmem_d, uint32_t a_smem, uint32_t b_smem) {
+TTT_MMA_OUTER
+  for (int blk = 0; blk < 2; ++blk) mma_hidden_half_t<kBMn, kAccumulate>(tmem_d, a_smem, b_smem, blk);
+}
+__device__ __forceinline__ void mma_hidden_half(uint32_t tmem_d, uint32_t a_smem, uint32_t b_smem, bool b_mn,
+                                                bool accumulate, int blk) {
+  if (b_mn) {
+    if (accumulate) mma_hidden_half_t<true, true>(tmem_d, a_smem, b_smem, blk);
+    else            mma_hidden_half_t<true, false>(tmem_d, a_smem, b_smem, blk);
+  } else {
+    if (accumulate) mma_hidden_half_t<false, true>(tmem_d, a_smem, b_smem, blk);
+    else            mma_hidden_half_t<false, false>(tmem_d, a_smem, b_smem, blk);
   }
 }
 __device__ __forceinline__ void mma_hidden_major(uint32_t tmem_d, uint32_t a_smem, uint32_t b_smem, bool b_mn,
