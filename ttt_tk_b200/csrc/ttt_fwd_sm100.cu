@@ -83,6 +83,22 @@ struct FwdParams {
   uint64_t wait_limit_ns;
 };
 
+// The MMAs of one phase are issued by lane 0 of warps 0..3: four instruction streams on four
+// schedulers instead of one.  Every issuer commits (an issuer without work too), so the MMA
+// barrier counts four arrivals per phase.
+#define TTT_ISSUE(W0, W1, W2, W3)   \
+  if (warp < 4) {                   \
+    if (lane == 0) {                \
+      tc_fence_after_sync();        \
+      if (warp == 0) { W0; }        \
+      else if (warp == 1) { W1; }   \
+      else if (warp == 2) { W2; }   \
+      else { W3; }                  \
+      umma_commit(mma_bar);         \
+    }                               \
+    __syncwarp();                   \
+  }
+
 __global__ void __launch_bounds__(kThreads, 1)
 ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmOut,
@@ -118,7 +134,7 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) mbar_init(&full[s], 1);
-    mbar_init(mma_bar, 1);
+    mbar_init(mma_bar, 4);
     fence_mbar_init();
     *abort_flag = 0;
     prefetch_tmap(&tmQ);
@@ -243,14 +259,10 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     mbar_wait_bounded(&full[s], (it / kStages) & 1, abort_flag, limit);
 
     // ---- MMA1: Z1^T = W1^T K^T
-    if (warp == 0) {
-        if (lane == 0) {
-      tc_fence_after_sync();
-      mma_hidden_major(tmem + TM_A, smem_u32(sW1), smem_u32(sK), false, false);
-      umma_commit(mma_bar);
-    }
-        __syncwarp();   // the other lanes do not spin while lane 0 issues
-      }
+    TTT_ISSUE(mma_hidden_half(tmem + TM_A, smem_u32(sW1), smem_u32(sK), false, false, 0),
+              mma_hidden_half(tmem + TM_A, smem_u32(sW1), smem_u32(sK), false, false, 1),
+              ,
+              )
     wait_mma();
     // ---- EPI1: X2^T = gelu(Z1^T + b1), G' = gelu'(Z1^T + b1)
 #pragma unroll 1
@@ -270,14 +282,10 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     publish();
 
     // ---- MMA2: Z2 = X2 W2
-    if (warp == 0) {
-        if (lane == 0) {
-      tc_fence_after_sync();
-      mma_token_major(tmem + TM_Z, smem_u32(sX2), smem_u32(sW2));
-      umma_commit(mma_bar);
-    }
-        __syncwarp();   // the other lanes do not spin while lane 0 issues
-      }
+    TTT_ISSUE(mma_token_major(tmem + TM_Z, smem_u32(sX2), smem_u32(sW2)),
+              ,
+              ,
+              )
     wait_mma();
     // ---- LN: fused LayerNorm + L2 gradient, U2 = -eta * dl/dZ2 (all 8 warps, 16 values each)
     {
@@ -327,14 +335,10 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     publish();
 
     // ---- MMA3: R^T = W2 U2^T
-    if (warp == 0) {
-        if (lane == 0) {
-      tc_fence_after_sync();
-      mma_hidden_major(tmem + TM_A, smem_u32(sW2), smem_u32(sU2), false, false);
-      umma_commit(mma_bar);
-    }
-        __syncwarp();   // the other lanes do not spin while lane 0 issues
-      }
+    TTT_ISSUE(mma_hidden_half(tmem + TM_A, smem_u32(sW2), smem_u32(sU2), false, false, 0),
+              mma_hidden_half(tmem + TM_A, smem_u32(sW2), smem_u32(sU2), false, false, 1),
+              ,
+              )
     // b2 += column sums of U2 (bf16 values, the operand the W2 update sees), fp32 accumulate
     if (tid >= 128 && tid < 192) {
       const int f = tid - 128;
@@ -371,15 +375,10 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     publish();
 
     // ---- MMA4: W1^T += U1^T K ;  W2 += X2^T U2
-    if (warp == 0) {
-        if (lane == 0) {
-      tc_fence_after_sync();
-      mma_hidden_major(tmem + TM_W1, smem_u32(sGP), smem_u32(sK), true, true);
-      mma_hidden_major(tmem + TM_W2, smem_u32(sX2), smem_u32(sU2), true, true);
-      umma_commit(mma_bar);
-    }
-        __syncwarp();   // the other lanes do not spin while lane 0 issues
-      }
+    TTT_ISSUE(mma_hidden_half(tmem + TM_W1, smem_u32(sGP), smem_u32(sK), true, true, 0),
+              mma_hidden_half(tmem + TM_W1, smem_u32(sGP), smem_u32(sK), true, true, 1),
+              mma_hidden_half(tmem + TM_W2, smem_u32(sX2), smem_u32(sU2), true, true, 0),
+              mma_hidden_half(tmem + TM_W2, smem_u32(sX2), smem_u32(sU2), true, true, 1))
     wait_mma();
     // ---- EPI4: refresh the bf16 operand copies of the state
 #pragma unroll 1
@@ -402,14 +401,10 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     publish();
 
     // ---- MMA5: Z1b^T = W1^T Q^T
-    if (warp == 0) {
-        if (lane == 0) {
-      tc_fence_after_sync();
-      mma_hidden_major(tmem + TM_A, smem_u32(sW1), smem_u32(sQ), false, false);
-      umma_commit(mma_bar);
-    }
-        __syncwarp();   // the other lanes do not spin while lane 0 issues
-      }
+    TTT_ISSUE(mma_hidden_half(tmem + TM_A, smem_u32(sW1), smem_u32(sQ), false, false, 0),
+              mma_hidden_half(tmem + TM_A, smem_u32(sW1), smem_u32(sQ), false, false, 1),
+              ,
+              )
     wait_mma();
     // ---- EPI5: X2b^T = gelu(Z1b^T + b1)
 #pragma unroll 1
@@ -428,14 +423,10 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     publish();
 
     // ---- MMA6: Z2b = X2b W2
-    if (warp == 0) {
-        if (lane == 0) {
-      tc_fence_after_sync();
-      mma_token_major(tmem + TM_Z, smem_u32(sX2), smem_u32(sW2));
-      umma_commit(mma_bar);
-    }
-        __syncwarp();   // the other lanes do not spin while lane 0 issues
-      }
+    TTT_ISSUE(mma_token_major(tmem + TM_Z, smem_u32(sX2), smem_u32(sW2)),
+              ,
+              ,
+              )
     wait_mma();
     // ---- OUT: Q + gamma * LN(Z2b + b2) + beta
     {
