@@ -11,7 +11,9 @@ ranks with one NCCL all-reduce, the only exchange the path has.
 
 Prints ONE JSON line (rank 0).  `value` is device-timed with the inputs resident in HBM;
 `e2e` is measured through the public operator API with pinned host buffers, host<->device
-copies inside the timed region.  `--impl reference` times the CPU oracle (the PyTorch-eager
+copies inside the timed region: every step copies all of its inputs in and all of its results
+out; the independent (batch element, head range) chunks run on their own CUDA streams and are
+not joined between steps, so a step's copies overlap the neighbouring steps' kernels.  `--impl reference` times the CPU oracle (the PyTorch-eager
 restatement of the reference's own PyTorch functions; the reference's CUDA kernels are
 sm_90a-only and cannot run on this GPU) on the host cores on a bounded sample of the same
 workload.
@@ -137,22 +139,24 @@ class DeviceStep:
         self.norm_grads = torch.zeros(2, H, 64, device=dev)
         self.ev = None
 
-    def forward(self, sl=(slice(None), slice(None))):
+    def forward(self, sl=(slice(None), slice(None)), norm=None):
         """Forward over the streams `sl` = (batch element b:b+1 or all, head range): such a slice of a
         contiguous [B, H, ...] tensor is contiguous."""
         from ttt_tk_b200 import ttt_forward
         t = self.t
         hs = (slice(None), sl[1])
-        ttt_forward(t["XQ"][sl], t["XK"][sl], t["XV"][sl], t["last_eta"][sl], t["ttt_norm_weight"][hs],
-                    t["ttt_norm_bias"][hs], t["W1"][sl], t["b1"][sl], t["W2"][sl], t["b2"][sl],
+        nw, nb = norm if norm is not None else (t["ttt_norm_weight"][hs], t["ttt_norm_bias"][hs])
+        ttt_forward(t["XQ"][sl], t["XK"][sl], t["XV"][sl], t["last_eta"][sl], nw,
+                    nb, t["W1"][sl], t["b1"][sl], t["W2"][sl], t["b2"][sl],
                     *[c[sl] for c in self.ck], self.out[sl], self.cgs)
 
-    def backward(self, sl=(slice(None), slice(None))):
+    def backward(self, sl=(slice(None), slice(None)), norm=None):
         from ttt_tk_b200 import ttt_backward
         t = self.t
         hs = (slice(None), sl[1])
-        ttt_backward(t["XQ"][sl], t["XK"][sl], t["XV"][sl], t["last_eta5"][sl], t["ttt_norm_weight"][hs],
-                     t["ttt_norm_bias"][hs], *[c[sl] for c in self.ck], self.out[sl],
+        nw, nb = norm if norm is not None else (t["ttt_norm_weight"][hs], t["ttt_norm_bias"][hs])
+        ttt_backward(t["XQ"][sl], t["XK"][sl], t["XV"][sl], t["last_eta5"][sl], nw,
+                     nb, *[c[sl] for c in self.ck], self.out[sl],
                      *[x[sl] for x in self.scratch],
                      t["grad_L_W1_last"][sl], t["grad_L_b1_last"][sl], t["grad_L_W2_last"][sl],
                      t["grad_L_b2_last"][sl], t["grad_L_XQW_mini_batch"][sl],
@@ -221,44 +225,71 @@ def run_ours(args, rank, world, local_rank):
     h2d = sum(v.numel() * v.element_size() for v in pin_in.values())
     d2h = sum(v.numel() * v.element_size() for v in pin_out.values())
 
-    # The batch elements are independent, so the step is pipelined over them: each batch element's
-    # host->device copies, forward, backward and device->host copies go to their own CUDA stream; the
-    # two copy directions and the kernels of different batch elements then overlap.
+    # The (batch element, head range) chunks are independent, so each one runs on its own CUDA stream:
+    # its host->device copies, forward, backward and device->host copies follow one another there, and
+    # the chunks are not joined at a step boundary.  Chunk c of step i+1 therefore starts copying in
+    # while other chunks of step i still compute or copy out (a training loop that prefetches its
+    # next batch): both copy directions and the kernels stay busy.  Every step still copies all of its
+    # inputs in and all of its results out, and the norm-gradient batch sum of a step is taken before
+    # the next step's backward may overwrite its addends.
     hsplit = max(1, min(args.e2e_head_chunks, H))
     hb = [(i * H // hsplit, (i + 1) * H // hsplit) for i in range(hsplit)]
     chunks = [(slice(b, b + 1), slice(h0, h1)) for b in range(B) for (h0, h1) in hb]
-    streams = [torch.cuda.Stream(device=dev) for _ in range(min(len(chunks), 8))]
+    streams = [torch.cuda.Stream(device=dev) for _ in chunks]        # copies in + kernels of a chunk
+    out_streams = [torch.cuda.Stream(device=dev) for _ in chunks]    # copies out of a chunk
     shared_keys = ["ttt_norm_weight", "ttt_norm_bias"]
     step.t["last_eta5"] = step.t["last_eta"].unsqueeze(-1)     # a view: follows the copies into last_eta
+    # every chunk keeps its own device copy of its heads' norm parameters (no chunk reads what another writes)
+    norm_dev = [tuple(torch.empty_like(step.t[k][:, sl[1]]) for k in shared_keys) for sl in chunks]
 
-    def e2e_step():
+    def e2e_steps_run(n_steps):
         main = torch.cuda.current_stream(dev)
-        for k in shared_keys:
-            step.t[k].copy_(pin_in[k], non_blocking=True)
-        ready = torch.cuda.Event()
-        ready.record(main)
-        for st in streams:
-            st.wait_event(ready)
-        for i, sl in enumerate(chunks):
-            st = streams[i % len(streams)]
-            with torch.cuda.stream(st):
-                for k, v in pin_in.items():
-                    if k not in shared_keys:
-                        step.t[k][sl].copy_(v[sl], non_blocking=True)
-                step.forward(sl)
-                step.backward(sl)
-                for k, v in out_t.items():
-                    pin_out[k][sl].copy_(v[sl], non_blocking=True)
-        for st in streams:
-            main.wait_stream(st)
-        step.reduce_norm_grads(world)
+        start = torch.cuda.Event()
+        start.record(main)
+        reduced = None
+        copied_out = [None] * len(chunks)
+        for _ in range(n_steps):
+            done = []
+            for i, sl in enumerate(chunks):
+                st, so = streams[i], out_streams[i]
+                with torch.cuda.stream(st):
+                    st.wait_event(start)
+                    # the inputs of this step go in while the chunk's previous results still go out
+                    for k, v in pin_in.items():
+                        if k not in shared_keys:
+                            step.t[k][sl].copy_(v[sl], non_blocking=True)
+                    for k, d in zip(shared_keys, norm_dev[i]):
+                        d.copy_(pin_in[k][:, sl[1]], non_blocking=True)
+                    if copied_out[i] is not None:
+                        st.wait_event(copied_out[i])     # the kernels overwrite the previous step's results
+                    step.forward(sl, norm=norm_dev[i])
+                    if reduced is not None:
+                        st.wait_event(reduced)      # the previous step's norm gradients have been summed
+                    step.backward(sl, norm=norm_dev[i])
+                    ev_c = torch.cuda.Event()
+                    ev_c.record(st)
+                    done.append(ev_c)
+                with torch.cuda.stream(so):
+                    so.wait_event(ev_c)
+                    for k, v in out_t.items():
+                        pin_out[k][sl].copy_(v[sl], non_blocking=True)
+                    copied_out[i] = torch.cuda.Event()
+                    copied_out[i].record(so)
+            for ev_c in done:
+                main.wait_event(ev_c)
+            step.reduce_norm_grads(world)
+            reduced = torch.cuda.Event()
+            reduced.record(main)
+        for so in out_streams:
+            main.wait_stream(so)
 
-    e2e_step()
+    e2e_steps_run(2)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
+    t_issue = time.perf_counter()
+    e2e_steps_run(e2e_steps)
+    t_issue = (time.perf_counter() - t_issue) * 1e3 / e2e_steps      # host time spent queueing one step
     e1.record()
     barrier()
     et = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
@@ -297,8 +328,10 @@ def run_ours(args, rank, world, local_rank):
                      "peak_source": f"{pk_src} (sustained cuBLAS bf16: kernel timed inside a long step)"},
         "e2e": {"value": tokens_per_step / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
-                "pipelining": f"{len(chunks)} (batch element, head range) chunks on {len(streams)} CUDA streams "
-                              "(copies and kernels overlap)"},
+                "host_issue_ms_per_step": t_issue,
+                "pipelining": f"{len(chunks)} (batch element, head range) chunks, each with a stream for copies in + "
+                              "kernels and one for copies out, not joined between steps: copies in, kernels and copies out "
+                              "of neighbouring steps overlap"},
         "gpu_launches": 2 * K,
         "clocks": clocks,
     }
@@ -361,8 +394,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
-    ap.add_argument("--e2e-steps", type=int, default=3)
-    ap.add_argument("--e2e-head-chunks", type=int, default=2,
+    ap.add_argument("--e2e-steps", type=int, default=8)
+    ap.add_argument("--e2e-head-chunks", type=int, default=1,
                     help="end-to-end step: split every batch element's heads into this many chunks")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
