@@ -58,7 +58,7 @@ constexpr int kThreads = 256;
 // barrier counts four arrivals per phase.
 #define TTT_ISSUE(W0, W1, W2, W3)   \
   if (warp < 4) {                   \
-    if (lane == 0) {                \
+    if (elect_one()) {              \
       tc_fence_after_sync();        \
       if (warp == 0) { W0; }        \
       else if (warp == 1) { W1; }   \
@@ -152,7 +152,8 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);   // same value, known to be warp-uniform
   const int quad = warp & 3, wg = warp >> 2;
   const int hrow = wg * 128 + quad * 32 + lane;
   const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;

@@ -78,6 +78,9 @@ __device__ __forceinline__ float ld_elem(const uint8_t* tile, uint32_t row, uint
 #ifndef TTT_MMA_ROLLED
 #define TTT_MMA_ROLLED 0
 #endif
+#ifndef TTT_MMA_SHARED_LOOP
+#define TTT_MMA_SHARED_LOOP (TTT_MMA_ROLLED == 1)
+#endif
 #if TTT_MMA_ROLLED == 1
 #define TTT_MMA_LOOP _Pragma("unroll 1")
 #define TTT_MMA_OUTER _Pragma("unroll 1")
@@ -109,6 +112,36 @@ __device__ __forceinline__ void mma_issue(uint32_t tmem_d, uint32_t a_lo, uint32
       : "memory");
 }
 
+// Issue with the accumulate flag in a register, and the one shared copy of the issue loop that a
+// kernel with rolled loops (TTT_MMA_ROLLED 1) calls for every product: n MMAs whose operand
+// descriptors advance by a constant per K step; the first one overwrites D unless `acc` is set.
+// A tcgen05.mma costs about ten instructions of set-up, so one out-of-line loop instead of one per
+// product shrinks such a kernel by roughly a tenth; only the issuing threads ever run it.
+__device__ __forceinline__ void mma_issue_rt(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %4};\n\t"
+      "mov.b64 db, {%2, %4};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}" ::"r"(tmem_d),
+      "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(kDescHi), "r"(accumulate)
+      : "memory");
+}
+static __device__ __noinline__ void mma_run(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                            uint32_t n, uint32_t astep, uint32_t bstep, uint32_t acc) {
+  // n is a multiple of 4 at every call
+#pragma unroll 1
+  for (uint32_t j = 0; j < n; j += 4) {
+    mma_issue_rt(tmem_d, a_lo, b_lo, idesc, acc | j);
+    mma_issue_rt(tmem_d, a_lo + astep, b_lo + bstep, idesc, 1u);
+    mma_issue_rt(tmem_d, a_lo + 2 * astep, b_lo + 2 * bstep, idesc, 1u);
+    mma_issue_rt(tmem_d, a_lo + 3 * astep, b_lo + 3 * bstep, idesc, 1u);
+    a_lo += 4 * astep;
+    b_lo += 4 * bstep;
+  }
+}
+
 // "Hidden-major" product: D[256 x 64] (two M=128 blocks, 64 fp32 columns each, at tmem_d and
 // tmem_d + 64) (+)= A * B with A a [256][64] bf16 tile read K-major (row = hidden unit) and B a
 // [64][64] tile read K-major (row = N index) or MN-major (row = K index).
@@ -121,10 +154,14 @@ __device__ __forceinline__ void mma_hidden_half_t(uint32_t tmem_d, uint32_t a_sm
   const uint32_t b0 = desc_lo(b_smem, kBMn ? 8192 : 16);
   constexpr uint32_t bstep = kBMn ? (2048u >> 4) : (32u >> 4);
   const uint32_t d = tmem_d + blk * 64;
+#if TTT_MMA_SHARED_LOOP
+  mma_run(d, a0, b0, idesc, 4, 2, bstep, kAccumulate ? 1u : 0u);
+#else
   if (kAccumulate) mma_issue<true>(d, a0, b0, idesc);
   else             mma_issue<false>(d, a0, b0, idesc);
 TTT_MMA_LOOP
   for (int j = 1; j < 4; ++j) mma_issue<true>(d, a0 + j * 2, b0 + j * bstep, idesc);
+#endif
 }
 template <bool kBMn, bool kAccumulate>
 __device__ __forceinline__ void mma_hidden_major_t(uint32_t tmem_d, uint32_t a_smem, uint32_t b_smem) {
@@ -157,9 +194,13 @@ __device__ __forceinline__ void mma_token_major(uint32_t tmem_d, uint32_t x_smem
   constexpr uint32_t idesc = umma_idesc_bf16(64, 64, true, true, false);
   const uint32_t a0 = desc_lo(x_smem, BIG);
   const uint32_t b0 = desc_lo(w_smem, BIG);
+#if TTT_MMA_SHARED_LOOP
+  mma_run(tmem_d, a0, b0, idesc, 16, 2048u >> 4, 2048u >> 4, 0u);
+#else
   mma_issue<false>(tmem_d, a0, b0, idesc);
 TTT_MMA_LOOP
   for (int j = 1; j < 16; ++j) mma_issue<true>(tmem_d, a0 + j * (2048u >> 4), b0 + j * (2048u >> 4), idesc);
+#endif
 }
 
 // ---- Token-major 64 x 64 accumulators spread over 8 warps (256 threads).
