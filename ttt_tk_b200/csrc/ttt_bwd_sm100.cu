@@ -758,9 +758,12 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             float z[8];
             ld_chunk(bz, hrow, half * 2 + c, z);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              z[k] = __uint_as_float(v[c * 8 + k]) * gelu_grad(z[k]);
-              bsum += z[k];
+            for (int k = 0; k < 8; k += 2) {
+              float g0, g1;
+              gelu_grad2(z[k], z[k + 1], g0, g1);
+              z[k] = __uint_as_float(v[c * 8 + k]) * g0;
+              z[k + 1] = __uint_as_float(v[c * 8 + k + 1]) * g1;
+              bsum += z[k] + z[k + 1];
             }
             st_chunk(bz, hrow, half * 2 + c, z);
           }
@@ -858,12 +861,16 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             float z[8], pp[8], gp[8];
             ld_chunk(bz, hrow, half * 2 + c, z);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              const float a1 = -__bfloat162float(sEta[half * 16 + c * 8 + k]) * (__uint_as_float(v[c * 8 + k]) + Gb1);
-              float gpp;
-              gelu_grad_pair(z[k], gp[k], gpp);
-              pp[k] = a1 * gp[k];
-              z[k] = a1 * gpp;
+            for (int k = 0; k < 8; k += 2) {
+              const float a10 = -__bfloat162float(sEta[half * 16 + c * 8 + k]) * (__uint_as_float(v[c * 8 + k]) + Gb1);
+              const float a11 =
+                  -__bfloat162float(sEta[half * 16 + c * 8 + k + 1]) * (__uint_as_float(v[c * 8 + k + 1]) + Gb1);
+              float gpp0, gpp1;
+              gelu_grad_pair2(z[k], z[k + 1], gp[k], gp[k + 1], gpp0, gpp1);
+              pp[k] = a10 * gp[k];
+              pp[k + 1] = a11 * gp[k + 1];
+              z[k] = a10 * gpp0;
+              z[k + 1] = a11 * gpp1;
             }
             st_chunk(bp, hrow, half * 2 + c, pp);
             st_chunk(bz, hrow, half * 2 + c, z);

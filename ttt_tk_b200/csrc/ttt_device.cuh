@@ -5,6 +5,7 @@
 #pragma once
 
 #include "sm100_ptx.cuh"
+#include <cuda_fp16.h>
 
 namespace tttdev {
 
@@ -45,6 +46,58 @@ __device__ __forceinline__ void gelu_grad_pair(float x, float& gp, float& gpp) {
   const float q = fmaf(kG2, x2, kG0);                 // kG0 + 3 kG0 kG1 x^2
   gp = fmaf(0.5f * x * s, q, 0.5f * (1.f + t));
   gpp = s * (fmaf(2.f * kG2, x2, kG0) - x * t * q * q);  // kG0 + 6 kG0 kG1 x^2 - x t q^2
+}
+
+// ---- The same family on two elements at a time in packed fp16 arithmetic.  The tanh-GELU and its
+// derivatives are O(1) functions of O(1) arguments, so fp16 (11 significand bits) evaluates them to
+// ~5e-4 (gelu'': ~2e-3), below the bf16 rounding (4e-3) every result meets when it is stored as an MMA
+// operand; one instruction then serves two elements.  The argument is clamped to +-20, beyond which
+// gelu' is 0 or 1 and gelu'' is 0 to fp16 precision (and x^3 would leave the fp16 range); gelu itself
+// itself stays in fp32: on fp32 arguments the conversions cost what the packed arithmetic saves, so
+// only the derivatives of arguments read from bf16 tiles use this path.
+struct GeluH2 {
+  __half2 x, x2, t, hh;   // clamped argument, its square, tanh(u), 0.5 (1 + tanh(u))
+};
+__device__ __forceinline__ __half2 h2c(float v) { return __float2half2_rn(v); }
+__device__ __forceinline__ __half2 tanh_h2(__half2 u) {
+  uint32_t r;
+  asm("tanh.approx.f16x2 %0, %1;" : "=r"(r) : "r"(*reinterpret_cast<const uint32_t*>(&u)));
+  return *reinterpret_cast<__half2*>(&r);
+}
+__device__ __forceinline__ GeluH2 gelu_h2_core(float x0, float x1) {
+  GeluH2 c;
+  c.x = __hmax2(__hmin2(__floats2half2_rn(x0, x1), h2c(20.f)), h2c(-20.f));
+  c.x2 = __hmul2(c.x, c.x);
+  const __half2 u = __hmul2(__hmul2(h2c(kG0), c.x), __hfma2(h2c(kG1), c.x2, h2c(1.f)));
+  c.t = tanh_h2(u);
+  c.hh = __hfma2(h2c(0.5f), c.t, h2c(0.5f));
+  return c;
+}
+// gelu'(x) from the core values
+__device__ __forceinline__ __half2 gelu_h2_grad(const GeluH2& c, __half2& s, __half2& q) {
+  s = __hfma2(__hneg2(c.t), c.t, h2c(1.f));
+  q = __hfma2(h2c(kG2), c.x2, h2c(kG0));
+  return __hfma2(__hmul2(__hmul2(h2c(0.5f), c.x), s), q, c.hh);
+}
+__device__ __forceinline__ void gelu_grad2(float x0, float x1, float& gp0, float& gp1) {
+  const GeluH2 c = gelu_h2_core(x0, x1);
+  __half2 s, q;
+  const float2 gp = __half22float2(gelu_h2_grad(c, s, q));
+  gp0 = gp.x;
+  gp1 = gp.y;
+}
+__device__ __forceinline__ void gelu_grad_pair2(float x0, float x1, float& gp0, float& gp1, float& gpp0,
+                                                float& gpp1) {
+  const GeluH2 c = gelu_h2_core(x0, x1);
+  __half2 s, q;
+  const float2 gp = __half22float2(gelu_h2_grad(c, s, q));
+  const __half2 cc = __hfma2(h2c(2.f * kG2), c.x2, h2c(kG0));
+  const __half2 xtq = __hmul2(__hmul2(c.x, c.t), q);
+  const float2 gpp = __half22float2(__hmul2(s, __hfma2(__hneg2(xtq), q, cc)));
+  gp0 = gp.x;
+  gp1 = gp.y;
+  gpp0 = gpp.x;
+  gpp1 = gpp.y;
 }
 
 __device__ __forceinline__ uint4 pack_chunk(const float* v) {
