@@ -52,7 +52,7 @@ __device__ __forceinline__ void gelu_grad_pair(float x, float& gp, float& gpp) {
 // derivatives are O(1) functions of O(1) arguments, so fp16 (11 significand bits) evaluates them to
 // ~5e-4 (gelu'': ~2e-3), below the bf16 rounding (4e-3) every result meets when it is stored as an MMA
 // operand; one instruction then serves two elements.  The argument is clamped to +-20, beyond which
-// gelu' is 0 or 1 and gelu'' is 0 to fp16 precision (and x^3 would leave the fp16 range); gelu itself
+// gelu' is 0 or 1 and gelu'' is 0 to fp16 precision (and x^3 would leave the fp16 range); gelu
 // itself stays in fp32: on fp32 arguments the conversions cost what the packed arithmetic saves, so
 // only the derivatives of arguments read from bf16 tiles use this path.
 struct GeluH2 {
