@@ -241,12 +241,19 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
   const long tok_rows0 = sid * NC * 64;      // first row of this stream in the [rows][64] token tensors
 
-  // ---- column sum over the 64 tokens of a token tile (threads 128..191, f = tid - 128)
-  auto colsum = [&](const uint8_t* t, int f) {
+  // ---- column sums over the 64 tokens of token tiles, while the MMAs of a phase run: every thread
+  // sums 16 rows of one column (rows 16 cs_q .., column cs_f) into `part` (the exchange buffer of the
+  // token-major epilogues, idle in these windows); after a CTA barrier threads 0..63 add the four parts.
+  const int cs_q = tid >> 6, cs_f = tid & 63;
+  float* part = sXch;      // [3][4][64]
+  auto colsum16 = [&](const uint8_t* t) {
     float acc = 0.f;
 #pragma unroll 8
-    for (int r = 0; r < 64; ++r) acc += ld_elem(t, r, f);
+    for (int r = cs_q * 16; r < cs_q * 16 + 16; ++r) acc += ld_elem(t, r, cs_f);
     return acc;
+  };
+  auto part_sum = [&](int k) {
+    return (part[k * 256 + tid] + part[k * 256 + 64 + tid]) + (part[k * 256 + 128 + tid] + part[k * 256 + 192 + tid]);
   };
 
   // the thread's fragment of a token tile -> the same swizzled image in global scratch
@@ -469,7 +476,9 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 mma_hidden_half(tmem + TM_A, smem_u32(bW2), smem_u32(tGZ2), false, false, 1),
                 ,
                 )
-      if (tid >= 128 && tid < 192) sB2[tid - 128] += colsum(tU2, tid - 128);
+      part[tid] = colsum16(tU2);
+      __syncthreads();
+      if (tid < 64) sB2[tid] += part_sum(0);
       wait_mma();
       {
         float bsum = 0.f;
@@ -487,11 +496,12 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             for (int k = 0; k < 8; ++k) gp[k] *= __uint_as_float(v[c * 8 + k]);     // dl/dZ1
             const uint4 w = pack_chunk(gp);
             *reinterpret_cast<uint4*>(bGP + off) = w;             // dl/dZ1 (bf16), in place over G'
-            float gb[8];
+            float gb[8], et[8];
             unpack_chunk(w, gb);
+            unpack_chunk(*reinterpret_cast<const uint4*>(eta + half * 16 + c * 8), et);   // one broadcast load
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
-              u[k] = -__bfloat162float(eta[half * 16 + c * 8 + k]) * gb[k];
+              u[k] = -et[k] * gb[k];
               bsum += u[k];
             }
             *reinterpret_cast<uint4*>(bZ1 + off) = pack_chunk(u);  // U1 = -eta dl/dZ1, over Z1
@@ -728,19 +738,24 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 mma_hidden_half(tmem + TM_A, smem_u32(big(ib1)), smem_u32(t_g), false, false, 1),
                 ,
                 )
-      if (tid >= 128 && tid < 192) {
+      {
         // column sums over the tokens: d_beta += sum go, d_gamma += sum go * x_hat_ln, G_b2 += sum gZ2b
-        const int f = tid - 128;
         float a = 0.f, b = 0.f;
 #pragma unroll 8
-        for (int r = 0; r < 64; ++r) {
-          const float go = ld_elem(t_go, r, f);
+        for (int r = cs_q * 16; r < cs_q * 16 + 16; ++r) {
+          const float go = ld_elem(t_go, r, cs_f);
           b += go;
-          a = fmaf(go, ld_elem(t_a, r, f), a);
+          a = fmaf(go, ld_elem(t_a, r, cs_f), a);
         }
-        sDB[f] += b;
-        sDG[f] += a;
-        sGb2[f] += colsum(t_g, f);
+        part[tid] = b;
+        part[256 + tid] = a;
+        part[512 + tid] = colsum16(t_g);
+        __syncthreads();
+        if (tid < 64) {
+          sDB[tid] += part_sum(0);
+          sDG[tid] += part_sum(1);
+          sGb2[tid] += part_sum(2);
+        }
       }
       wait_mma();
       wait_bar(BAR_BIG + ib2);
@@ -858,13 +873,13 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           tmem_wait_ld();
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
-            float z[8], pp[8], gp[8];
+            float z[8], pp[8], gp[8], et[8];
             ld_chunk(bz, hrow, half * 2 + c, z);
+            unpack_chunk(*reinterpret_cast<const uint4*>(sEta + half * 16 + c * 8), et);   // one broadcast load
 #pragma unroll
             for (int k = 0; k < 8; k += 2) {
-              const float a10 = -__bfloat162float(sEta[half * 16 + c * 8 + k]) * (__uint_as_float(v[c * 8 + k]) + Gb1);
-              const float a11 =
-                  -__bfloat162float(sEta[half * 16 + c * 8 + k + 1]) * (__uint_as_float(v[c * 8 + k + 1]) + Gb1);
+              const float a10 = -et[k] * (__uint_as_float(v[c * 8 + k]) + Gb1);
+              const float a11 = -et[k + 1] * (__uint_as_float(v[c * 8 + k + 1]) + Gb1);
               float gpp0, gpp1;
               gelu_grad_pair2(z[k], z[k + 1], gp[k], gp[k + 1], gpp0, gpp1);
               pp[k] = a10 * gp[k];
@@ -1000,11 +1015,16 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 mma_hidden_half(tmem + TM_B, smem_u32(big(ib3)), smem_u32(t_q), false, false, 1); mma_hidden_half(tmem + TM_B, smem_u32(big(ib1)), smem_u32(t_g), false, true, 1),
                 mma_hidden_half(tmem + TM_A, smem_u32(big(ib3)), smem_u32(t_gz2), false, false, 0),
                 mma_hidden_half(tmem + TM_A, smem_u32(big(ib3)), smem_u32(t_gz2), false, false, 1))
-      if (tid >= 128 && tid < 192) {
-        const int f = tid - 128;
-        sGb2[f] += colsum(t_q, f);
-        sDG[f] += colsum(t_a, f);
-        sDB[f] -= colsum(t_go, f);
+      {
+        part[tid] = colsum16(t_q);
+        part[256 + tid] = colsum16(t_a);
+        part[512 + tid] = colsum16(t_go);
+        __syncthreads();
+        if (tid < 64) {
+          sGb2[tid] += part_sum(0);
+          sDG[tid] += part_sum(1);
+          sDB[tid] -= part_sum(2);
+        }
       }
       wait_mma();
       // the state-gradient snapshot buffer is free: bring the next step's Z1_bar into it

@@ -340,15 +340,16 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               mma_hidden_half(tmem + TM_A, smem_u32(sW2), smem_u32(sU2), false, false, 1),
               ,
               )
-    // b2 += column sums of U2 (bf16 values, the operand the W2 update sees), fp32 accumulate
-    if (tid >= 128 && tid < 192) {
-      const int f = tid - 128;
+    // b2 += column sums of U2 (bf16 values, the operand the W2 update sees), fp32 accumulate: every
+    // thread sums 16 rows of one column while the MMA runs, threads 0..63 add the four parts
+    {
+      const int q = tid >> 6, f = tid & 63;
       float acc = 0.f;
 #pragma unroll 8
-      for (int t = 0; t < 64; ++t)
-        acc += __bfloat162float(
-            *reinterpret_cast<const __nv_bfloat16*>(sU2 + sw128_off(t, f >> 3) + (f & 7) * 2));
-      sB2[f] += acc;
+      for (int t = q * 16; t < q * 16 + 16; ++t) acc += ld_elem(sU2, t, f);
+      sXch[tid] = acc;     // the exchange buffer of the token-major epilogues is idle here
+      __syncthreads();
+      if (tid < 64) sB2[tid] += (sXch[tid] + sXch[64 + tid]) + (sXch[128 + tid] + sXch[192 + tid]);
     }
     wait_mma();
     // ---- EPI3: U1^T = R^T * G' (= -eta dl/dZ1), b1 += row sum
