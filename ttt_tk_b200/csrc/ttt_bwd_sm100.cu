@@ -69,14 +69,17 @@ constexpr int kThreads = 256;
     __syncwarp();                   \
   }
 
-// Optional timeline of CTA 0 (compile with -DTTT_STAMPS): thread 0 records the global timer
-// whenever a wait or a publish step returns.  Off in the shipped library.
+// Optional timeline of CTA 0 (compile with -DTTT_STAMPS): one thread records the global timer
+// whenever a wait returns and when a publish step begins and returns.  Off in the shipped library.
 #ifdef TTT_STAMPS
+#ifndef TTT_STAMP_TID
+#define TTT_STAMP_TID 0      // the recording thread
+#endif
 __device__ unsigned long long g_ttt_stamps[16384];
 __device__ unsigned int g_ttt_nstamps;
 #define TTT_STAMP(id)                                                            \
   do {                                                                           \
-    if (threadIdx.x == 0 && blockIdx.x == 0) {                                   \
+    if (threadIdx.x == TTT_STAMP_TID && blockIdx.x == 0) {                                  \
       const unsigned n_ = g_ttt_nstamps;                                         \
       if (n_ < 16384) {                                                          \
         g_ttt_stamps[n_] = (globaltimer_ns() << 8) | (unsigned long long)(id);   \
@@ -100,8 +103,8 @@ constexpr uint32_t OFF_DB = OFF_DG + 256;            // fp32[64]  d_beta accumul
 constexpr uint32_t OFF_SIGLN = OFF_DB + 256;         // fp32[64]
 constexpr uint32_t OFF_SIGF = OFF_SIGLN + 256;       // fp32[64]
 constexpr uint32_t OFF_GB1 = OFF_SIGF + 256;         // fp32[256] copy of the per-thread dL/db1
-constexpr uint32_t OFF_PART = OFF_GB1 + 1024;        // fp32[4][64] partial sums for d_eta
-constexpr uint32_t OFF_ETA = OFF_PART + 1024;        // bf16[2][64]
+constexpr uint32_t OFF_PART = OFF_GB1 + 1024;        // fp32[8][64] partial sums for d_eta (one row per warp)
+constexpr uint32_t OFF_ETA = OFF_PART + 2048;        // bf16[2][64]
 constexpr uint32_t OFF_BAR = OFF_ETA + 256;          // 16 mbarriers
 constexpr uint32_t OFF_MISC = OFF_BAR + 128;
 constexpr uint32_t OFF_XCH = OFF_MISC + 64;        // fp32[2][64][8] row-sum exchange between warp pairs
@@ -226,6 +229,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     tc_fence_after_sync();
   };
   auto publish = [&]() {
+    TTT_STAMP(0x11);
     fence_proxy_async_smem();   // generic-proxy writes to shared memory -> async proxy (MMA, bulk copies)
     tc_fence_before_sync();
     __syncthreads();
@@ -679,9 +683,15 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       tma_load_2d(t_k, &tmK, &bars[BAR_T + 4], 0, row0);
       bulk_load_1d(sEta, p.eta + (sid * NC + i0 + j) * 64, 128, &bars[BAR_T + 4]);
       load_big(ib4, p.sc_gZ1 + slot * BIG);
+      pending |= (1u << (BAR_T + 2)) | (1u << (BAR_T + 4));
+    };
+    // the dl/dZ2 tile of step j: its destination stages the previous step's dK on its way out, so this
+    // load goes out one phase into the step, when that store has long read the tile
+    auto issue_gz2 = [&](int j) {
+      tma_wait_group_read<0>();
       mbar_expect_tx(&bars[BAR_T + 5], TILE);
-      bulk_load_1d(t_gz2, p.sc_gZ2 + slot * TILE, TILE, &bars[BAR_T + 5]);
-      pending |= (1u << (BAR_T + 2)) | (1u << (BAR_T + 4)) | (1u << (BAR_T + 5));
+      bulk_load_1d(t_gz2, p.sc_gZ2 + (slot0 + j) * TILE, TILE, &bars[BAR_T + 5]);
+      pending |= 1u << (BAR_T + 5);
     };
     // scratch was written partly with generic-proxy stores by all threads, partly with bulk
     // stores by thread 0: order both before the bulk (async-proxy) copies that read it back
@@ -790,6 +800,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         mbar_expect_tx(&bars[BAR_T + 1], TILE);
         bulk_load_1d(t_a, p.sc_gof + slot * TILE, TILE, &bars[BAR_T + 1]);
         pending |= 1u << (BAR_T + 1);
+        issue_gz2(j);
       }
       wait_bar(BAR_BIG + ib3);
       wait_bar(BAR_T + 2);
@@ -838,23 +849,36 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         load_big(ib3, p.sc_X2 + slot * BIG);
       }
       wait_bar(BAR_BIG + ib4);
-      // ---- partial sums over the hidden units of gZ1 * G_b1 (fourth term of d_eta)
-      {
-        const int q = tid >> 6, t = tid & 63;
-        const uint8_t* bg = big(ib4);
-        float acc = 0.f;
-#pragma unroll 8
-        for (int h = q * 64; h < q * 64 + 64; ++h) acc = fmaf(ld_elem(bg, h, t), sGb1[h], acc);
-        sPart[q * 64 + t] = acc;
-      }
-      publish();
       wait_bar(BAR_T + 4);
-      wait_bar(BAR_BIG + ib3);
+      if (warp == 1) wait_bar(BAR_BIG + ib3);   // X2 was requested just now: only the issuer of G5 waits for it here
       // G4 // G8 // G5
       TTT_ISSUE(mma_token_major(tmem + TM_B, smem_u32(big(ib4)), smem_u32(big(ib0))),
                 mma_token_major(tmem + TM_B + 64, smem_u32(big(ib3)), smem_u32(big(ib1))),
                 mma_hidden_half(tmem + TM_A, smem_u32(big(ib0)), smem_u32(t_k), false, false, 0),
                 mma_hidden_half(tmem + TM_A, smem_u32(big(ib0)), smem_u32(t_k), false, false, 1))
+      // ---- while the MMAs run: partial sums over the hidden units of gZ1 * G_b1 (fourth term of d_eta)
+      {
+        // warp w takes hidden units 32 w .. 32 w + 31, lane l the token pair (2 l, 2 l + 1): one conflict-free
+        // 4-byte load per row, four independent accumulators
+        const uint8_t* bg = big(ib4) + (lane & 3) * 4;
+        const uint32_t chunk = lane >> 2;
+        float a0 = 0.f, a1 = 0.f, c0 = 0.f, c1 = 0.f;
+#pragma unroll
+        for (int hh = 0; hh < 32; hh += 4) {
+          const int h = warp * 32 + hh;
+          const float4 g = *reinterpret_cast<const float4*>(sGb1 + h);
+          const uint32_t w0 = *reinterpret_cast<const uint32_t*>(bg + sw128_off(h, chunk));
+          const uint32_t w1 = *reinterpret_cast<const uint32_t*>(bg + sw128_off(h + 1, chunk));
+          const uint32_t w2 = *reinterpret_cast<const uint32_t*>(bg + sw128_off(h + 2, chunk));
+          const uint32_t w3 = *reinterpret_cast<const uint32_t*>(bg + sw128_off(h + 3, chunk));
+          a0 = fmaf(bf16_lo(w0), g.x, a0); a1 = fmaf(bf16_hi(w0), g.x, a1);
+          c0 = fmaf(bf16_lo(w1), g.y, c0); c1 = fmaf(bf16_hi(w1), g.y, c1);
+          a0 = fmaf(bf16_lo(w2), g.z, a0); a1 = fmaf(bf16_hi(w2), g.z, a1);
+          c0 = fmaf(bf16_lo(w3), g.w, c0); c1 = fmaf(bf16_hi(w3), g.w, c1);
+        }
+        *reinterpret_cast<float2*>(sPart + warp * 64 + 2 * lane) = make_float2(a0 + c0, a1 + c1);
+      }
+      if (warp != 1) wait_bar(BAR_BIG + ib3);
       wait_mma();
       if (tid == 0) {
         load_big(ib3, p.sc_W2 + slot * 65536);
@@ -997,8 +1021,14 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tok_st_tile(tm, t_g, gz);
         if (tm.colhalf == 0 && tm.l3 == 0) {
           const int r0 = tm.r0, r1 = tm.r1;
-          const float de0 = -(ra[0] + ra[1] + sPart[r0] + sPart[64 + r0] + sPart[128 + r0] + sPart[192 + r0]);
-          const float de1 = -(rb[0] + rb[1] + sPart[r1] + sPart[64 + r1] + sPart[128 + r1] + sPart[192 + r1]);
+          float p0 = 0.f, p1 = 0.f;
+#pragma unroll
+          for (int w = 0; w < 8; ++w) {
+            p0 += sPart[w * 64 + r0];
+            p1 += sPart[w * 64 + r1];
+          }
+          const float de0 = -(ra[0] + ra[1] + p0);
+          const float de1 = -(rb[0] + rb[1] + p1);
           p.d_eta[(sid * NC + i0 + j) * 64 + r0] = __float2bfloat16(de0);
           p.d_eta[(sid * NC + i0 + j) * 64 + r1] = __float2bfloat16(de1);
         }
@@ -1069,19 +1099,19 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 mma_hidden_half(tmem + TM_S2, smem_u32(big(ib0)), smem_u32(t_q), true, true, 0),
                 mma_hidden_half(tmem + TM_S2, smem_u32(big(ib0)), smem_u32(t_q), true, true, 1))
       wait_mma();
-      // ---- E6: dK = partial + gZ1in W1^T, staged over the gZ2in tile and stored by TMA
+      // ---- E6: dK = partial + gZ1in W1^T, staged over the dl/dZ2 tile (dead since G12) and stored by TMA;
+      // nothing waits for the store here: the tile's next load is issue_gz2's
       {
         float acc[16];
         tok_ld(tm, tmem + TM_A, acc);
 #pragma unroll
         for (int q = 0; q < 16; ++q) kp[q] += acc[q];
-        tok_st_tile(tm, t_q, kp);
+        tok_st_tile(tm, t_gz2, kp);
       }
       publish();
       if (tid == 0) {
-        tma_store_2d(&tmDK, t_q, 0, row0);
+        tma_store_2d(&tmDK, t_gz2, 0, row0);
         tma_commit_group();
-        tma_wait_group_read<0>();     // the next step's Q lands in the same tile
       }
       // pre-update weights of this mini-batch are the post-update weights of the previous one
       {
@@ -1092,6 +1122,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       if (*abort_flag) { aborted = true; break; }
     }
     if (aborted) break;
+    if (tid == 0) tma_wait_group_read<0>();   // the last dK has left its tile (the recompute writes it again)
 
     // ---- park the gradient state (tensor memory -> grad_L_W*_init); the last group leaves the result
     {
