@@ -122,7 +122,8 @@ def run_reference(ref_fwd, ref_bwd, d, cgs):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get(
+        "TTT_REFERENCE_ROOT", os.path.join(os.path.expanduser("~"), "reference"))
     ref_fwd, ref_bwd = load_reference(ref_root)
     blob = {}
     with torch.no_grad():

@@ -85,7 +85,7 @@ def test_checkpoint_rule_and_ragged_count():
     assert torch.equal(r["Out"], r5["Out"])
 
 
-REF = os.environ.get("TTT_REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("TTT_REFERENCE_ROOT", os.path.join(os.path.expanduser("~"), "reference"))
 
 
 @pytest.mark.skipif(not os.path.exists(os.path.join(REF, "kernels/ttt_backward/matching.py")),
