@@ -113,6 +113,41 @@ def test_eta_scale_sweep_forward(eta_scale):
     assert orc.rel_l2(out.float().cpu(), f["Out"]) <= 1e-2
 
 
+def test_config4_full_size_forward_runs_in_waves():
+    """configs[4] (B=64, H=24, seq 4096, cgs 16) at full size: 1536 streams, i.e. ten waves of CTAs on the
+    148 SMs.  Inputs are drawn on the device (4 GB; same distributions as the seeded recipe).  Streams
+    from the first, a middle and the last wave, run alone, must give bit-identical results, and are
+    checked against the oracle."""
+    B, H, NC, cgs = 64, 24, 64, 16
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(4)
+    rn = lambda *s: torch.randn(*s, device=dev, generator=g)
+    t = {"XQ": rn(B, H, NC, 64, 64).bfloat16(), "XK": rn(B, H, NC, 64, 64).bfloat16(),
+         "XV": rn(B, H, NC, 64, 64).bfloat16(),
+         "last_eta": (0.1 * torch.sigmoid(rn(B, H, NC, 64)) / 64).bfloat16(),
+         "ttt_norm_weight": 1 + 0.02 * rn(1, H, 1, 64), "ttt_norm_bias": 0.02 * rn(1, H, 1, 64),
+         "W1": 0.02 * rn(B, H, 64, 256), "b1": torch.zeros(B, H, 1, 256, device=dev),
+         "W2": 0.02 * rn(B, H, 256, 64), "b2": torch.zeros(B, H, 1, 64, device=dev)}
+    names = ["XQ", "XK", "XV", "last_eta", "ttt_norm_weight", "ttt_norm_bias", "W1", "b1", "W2", "b2"]
+    ck = alloc_checkpoints(B, H, NC, cgs, dev)
+    out = torch.empty_like(t["XQ"])
+    ttt_forward(*[t[k] for k in names], *ck, out, cgs, sync=True)
+    assert take_status() == 0
+    assert torch.isfinite(out.float()).all()
+    for (b, h) in [(0, 0), (31, 7), (63, 23)]:
+        sub = {k: (v[:, h:h + 1] if v.shape[0] == 1 else v[b:b + 1, h:h + 1]).contiguous() for k, v in t.items()}
+        ck1 = alloc_checkpoints(1, 1, NC, cgs, dev)
+        out1 = torch.empty_like(sub["XQ"])
+        ttt_forward(*[sub[k] for k in names], *ck1, out1, cgs, sync=True)
+        assert torch.equal(out1[0, 0], out[b, h])
+        for c1, c in zip(ck1, ck):
+            assert torch.equal(c1[0, 0], c[b, h])
+        c = {k: v.cpu() for k, v in sub.items()}
+        f = orc.ttt_forward(*[c[k] for k in names], cgs)
+        assert orc.rel_l2(out1.float().cpu(), f["Out"]) <= 1e-2
+        assert orc.rel_l2(ck1[0].cpu(), f["W1_checkpoints"]) <= 1e-2
+
+
 def test_autograd_function_matches_oracle_autograd():
     B, H, NC, cgs = 2, 2, 6, 4
     d = make_inputs(B, H, NC, seed=9, backward=True)
