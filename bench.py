@@ -234,7 +234,10 @@ def run_ours(args, rank, world, local_rank):
     # the next step's backward may overwrite its addends.
     hsplit = max(1, min(args.e2e_head_chunks, H))
     hb = [(i * H // hsplit, (i + 1) * H // hsplit) for i in range(hsplit)]
-    chunks = [(slice(b, b + 1), slice(h0, h1)) for b in range(B) for (h0, h1) in hb]
+    bpc = max(1, min(args.e2e_batch_per_chunk, B))
+    chunks = [(slice(b, min(b + bpc, B)), slice(h0, h1)) for b in range(0, B, bpc) for (h0, h1) in hb]
+    if hsplit > 1:
+        assert bpc == 1, "a head range of several batch elements is not contiguous"
     streams = [torch.cuda.Stream(device=dev) for _ in chunks]        # copies in + kernels of a chunk
     out_streams = [torch.cuda.Stream(device=dev) for _ in chunks]    # copies out of a chunk
     shared_keys = ["ttt_norm_weight", "ttt_norm_bias"]
@@ -387,7 +390,16 @@ def run_reference(args, rank, world):
     }
 
 
+def _emit(res, out_fd):
+    os.write(out_fd, (json.dumps(res) + "\n").encode())
+
+
 def main():
+    # Libraries may write to stdout on their own (NCCL prints its version there); the one JSON line must
+    # be the only thing on it, so everything else is sent to stderr and the line goes to the saved stdout.
+    sys.stdout.flush()
+    out_fd = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
@@ -397,6 +409,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=8)
     ap.add_argument("--e2e-head-chunks", type=int, default=1,
                     help="end-to-end step: split every batch element's heads into this many chunks")
+    ap.add_argument("--e2e-batch-per-chunk", type=int, default=2,
+                    help="end-to-end step: batch elements per chunk (with --e2e-head-chunks 1)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -408,7 +422,7 @@ def main():
     if args.impl == "reference":
         res = run_reference(args, rank, world)
         if res is not None:
-            print(json.dumps(res), flush=True)
+            _emit(res, out_fd)
         return
 
     if world > 1:
@@ -425,7 +439,7 @@ def main():
                 "value": rate, "unit": "tokens/s", "cores": threads, "kind": "port",
                 "sample": (f"PyTorch-eager fp32 oracle, fwd + hand-derived bwd, slice B={sB} H={sH} at full "
                            f"sequence (NC={NC}), median of 3 ({sec:.2f} s each); tokens/s = token-heads/s / {H}")}
-        print(json.dumps(res), flush=True)
+        _emit(res, out_fd)
     if world > 1:
         import torch.distributed as dist
         dist.barrier()
