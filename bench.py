@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the TTT-MLP forward + backward path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1|c0|small]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1|c3|c4|c0|small|prof]
 
 One "step" = one forward + one backward over one batch of synthetic input of the named
 workload (default: the forward+backward configuration, B=4 H=32 seq 8192 cgs 8 per GPU).
@@ -36,6 +36,8 @@ WORKLOADS = {
     "c2": (4, 32, 128, 8, "configs[2]: fwd+bwd, B=4 H=32 seq=8192 (NC=128) cgs=8, per GPU"),
     "c1": (4, 12, 32, 4, "configs[1] shape run fwd+bwd, B=4 H=12 seq=2048 (NC=32) cgs=4, per GPU"),
     "c0": (1, 4, 32, 4, "configs[0] shape, B=1 H=4 seq=2048 (NC=32) cgs=4"),
+    "c3": (1, 32, 1024, 32, "configs[3] shape on one GPU, B=1 H=32 seq=65536 (NC=1024) cgs=32"),
+    "c4": (64, 24, 64, 16, "configs[4] shape run fwd+bwd on one GPU, B=64 H=24 seq=4096 (NC=64) cgs=16"),
     "small": (1, 8, 16, 4, "small case, B=1 H=8 seq=1024 cgs=4"),
     "prof": (4, 32, 16, 8, "profiling case: configs[2] streams (B=4 H=32) at seq=1024 (NC=16) cgs=8"),
 }
