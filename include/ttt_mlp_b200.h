@@ -216,6 +216,18 @@ int ttt_b200_umma_selftest(const float* A, const float* B, float* D, int M, int 
  * stays usable.  Synchronises. */
 int ttt_b200_wait_selftest(int limit_us, unsigned long long* waited_ns, void* stream);
 
+/* Token layout transforms either side of the operator (no counterpart in the reference, which
+ * asks its callers for contiguous [B, H, NC, 64, 64] tensors: README.md:98; a model's activations
+ * are [B, T, H*64]).  pack: src[k] is [B][T][H][64] bf16, dst[k] becomes [B][H][T][64]; unpack is
+ * the inverse (src[k] [B][H][T][64] -> dst[k] [B][T][H][64]).  Up to 4 tensors of the same shape
+ * move in one launch (Q, K, V, upstream gradient / Out, dQ, dK, dV).  Out of place, device
+ * pointers 16-byte aligned, T a multiple of 64, B*T*H < 2^31.  Stream-ordered, does not
+ * synchronise.  Returns a TTT_B200_* code. */
+int ttt_b200_pack_tokens(const void* const* src, void* const* dst, int n_tensors, int B, int T, int H,
+                         void* stream);
+int ttt_b200_unpack_tokens(const void* const* src, void* const* dst, int n_tensors, int B, int T, int H,
+                           void* stream);
+
 #ifdef __cplusplus
 }
 #endif

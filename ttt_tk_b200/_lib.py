@@ -44,7 +44,8 @@ class BwdNoAllocArgs(ctypes.Structure):
 
 
 EXPORTS = ["ttt_b200_forward", "ttt_b200_backward", "ttt_b200_backward_noalloc", "ttt_b200_last_error", "ttt_b200_take_status",
-           "ttt_b200_version", "ttt_b200_umma_selftest", "ttt_b200_wait_selftest"]
+           "ttt_b200_version", "ttt_b200_umma_selftest", "ttt_b200_wait_selftest", "ttt_b200_pack_tokens",
+           "ttt_b200_unpack_tokens"]
 
 FLAG_SYNC = 1
 
@@ -71,6 +72,10 @@ def load():
     lib.ttt_b200_umma_selftest.restype = ctypes.c_int
     lib.ttt_b200_wait_selftest.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_ulonglong), c_void_p]
     lib.ttt_b200_wait_selftest.restype = ctypes.c_int
+    for name in ("ttt_b200_pack_tokens", "ttt_b200_unpack_tokens"):
+        fn = getattr(lib, name)
+        fn.argtypes = [ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p)] + [ctypes.c_int] * 4 + [c_void_p]
+        fn.restype = ctypes.c_int
     return lib
 
 
