@@ -443,7 +443,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         tok_st_global(p.sc_xhf + slot * TILE, xh);
         tok_st_global(p.sc_gof + slot * TILE, e);
-        tok_row_allreduce<2>(tm, a, b, sXch);
+        tok_row_allreduce<2, 2>(tm, a, b, sXch);
         const float sc0 = rs0 * (1.f / 64.f), sc1 = rs1 * (1.f / 64.f);
         const float ne0 = -__bfloat162float(eta[tm.r0]), ne1 = -__bfloat162float(eta[tm.r1]);
 #pragma unroll
@@ -729,7 +729,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             b[0] += go[x1]; b[1] = fmaf(go[x1], xl[x1], b[1]);
           }
         }
-        tok_row_allreduce<2>(tm, a, b, sXch);
+        tok_row_allreduce<2, 2>(tm, a, b, sXch);
         const float q0 = 1.f / (64.f * sSigLn[tm.r0]), q1 = 1.f / (64.f * sSigLn[tm.r1]);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -968,7 +968,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             }
           }
         }
-        tok_row_allreduce<5>(tm, ra, rb, sXch);
+        tok_row_allreduce<5, 0>(tm, ra, rb, sXch);
         float sa[2] = {0.f, 0.f}, sb[2] = {0.f, 0.f};      // sum g_std, sum g_xhat
         float dga[16], dv[16];
 #pragma unroll
@@ -1005,7 +1005,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         tok_st_tile(tm, t_a, dga);       // d_gamma addends, over grad_output_fused
         tok_st_tile(tm, t_go, dv);       // dV: stored by TMA, and column-summed for d_beta
-        tok_row_allreduce<2>(tm, sa, sb, sXch);
+        tok_row_allreduce<2, 5>(tm, sa, sb, sXch);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
 #pragma unroll

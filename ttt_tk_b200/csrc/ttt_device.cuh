@@ -309,9 +309,12 @@ __device__ __forceinline__ void tok_ld_cols(const TokMap& m, const float* vec, f
   }
 }
 // All-reduce N per-row partial sums over the 8 threads that share each row.  a[] belongs to row
-// r0, b[] to row r1.  xch: fp32[2][64][8] in shared memory.
-template <int N>
+// r0, b[] to row r1.  xch: fp32[2][64][8] in shared memory; the call uses columns kSlot .. kSlot+N-1
+// of it.  There is no barrier after the read-back: the all-reduces of one epilogue phase must use
+// disjoint columns, and a CTA barrier must separate phases (every phase ends with one).
+template <int N, int kSlot>
 __device__ __forceinline__ void tok_row_allreduce(const TokMap& m, float (&a)[N], float (&b)[N], float* xch) {
+  static_assert(kSlot >= 0 && kSlot + N <= 8, "the exchange buffer has 8 columns per row");
 #pragma unroll
   for (int i = 0; i < N; ++i) {
     a[i] += __shfl_xor_sync(0xffffffffu, a[i], 1);
@@ -322,19 +325,19 @@ __device__ __forceinline__ void tok_row_allreduce(const TokMap& m, float (&a)[N]
   if (m.l3 == 0) {
 #pragma unroll
     for (int i = 0; i < N; ++i) {
-      xch[(m.colhalf * 64 + m.r0) * 8 + i] = a[i];
-      xch[(m.colhalf * 64 + m.r1) * 8 + i] = b[i];
+      xch[(m.colhalf * 64 + m.r0) * 8 + kSlot + i] = a[i];
+      xch[(m.colhalf * 64 + m.r1) * 8 + kSlot + i] = b[i];
     }
   }
   named_bar_sync(1 + m.quad, 64);
 #pragma unroll
   for (int i = 0; i < N; ++i) {
-    a[i] += xch[((m.colhalf ^ 1) * 64 + m.r0) * 8 + i];
-    b[i] += xch[((m.colhalf ^ 1) * 64 + m.r1) * 8 + i];
+    a[i] += xch[((m.colhalf ^ 1) * 64 + m.r0) * 8 + kSlot + i];
+    b[i] += xch[((m.colhalf ^ 1) * 64 + m.r1) * 8 + kSlot + i];
   }
-  named_bar_sync(1 + m.quad, 64);
 }
-// LayerNorm statistics of the thread's two rows: centres z in place, returns 1/std per row
+// LayerNorm statistics of the thread's two rows: centres z in place, returns 1/std per row.  Uses the
+// exchange columns 0 and 1.
 __device__ __forceinline__ void tok_layernorm(const TokMap& m, float (&z)[16], float eps, float* xch, float& rstd0,
                                               float& rstd1) {
   float s0[1] = {0.f}, s1[1] = {0.f};
@@ -343,7 +346,7 @@ __device__ __forceinline__ void tok_layernorm(const TokMap& m, float (&z)[16], f
     s0[0] += z[4 * j] + z[4 * j + 1];
     s1[0] += z[4 * j + 2] + z[4 * j + 3];
   }
-  tok_row_allreduce<1>(m, s0, s1, xch);
+  tok_row_allreduce<1, 0>(m, s0, s1, xch);
   const float mu0 = s0[0] * (1.f / 64.f), mu1 = s1[0] * (1.f / 64.f);
   s0[0] = 0.f; s1[0] = 0.f;
 #pragma unroll
@@ -353,7 +356,7 @@ __device__ __forceinline__ void tok_layernorm(const TokMap& m, float (&z)[16], f
     s0[0] = fmaf(z[4 * j], z[4 * j], fmaf(z[4 * j + 1], z[4 * j + 1], s0[0]));
     s1[0] = fmaf(z[4 * j + 2], z[4 * j + 2], fmaf(z[4 * j + 3], z[4 * j + 3], s1[0]));
   }
-  tok_row_allreduce<1>(m, s0, s1, xch);
+  tok_row_allreduce<1, 1>(m, s0, s1, xch);
   rstd0 = rsqrtf(s0[0] * (1.f / 64.f) + eps);
   rstd1 = rsqrtf(s1[0] * (1.f / 64.f) + eps);
 }

@@ -319,7 +319,7 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           b[0] += g[i1]; b[1] = fmaf(g[i1], xh[i1], b[1]);
         }
       }
-      tok_row_allreduce<2>(tm, a, b, sXch);
+      tok_row_allreduce<2, 2>(tm, a, b, sXch);
       const float sc0 = -__bfloat162float(sEta[tm.r0]) * rs0 * (1.f / 64.f);
       const float sc1 = -__bfloat162float(sEta[tm.r1]) * rs1 * (1.f / 64.f);
 #pragma unroll
