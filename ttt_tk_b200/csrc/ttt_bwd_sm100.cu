@@ -810,6 +810,10 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 mma_hidden_half(tmem + TM_S1, smem_u32(big(ib2)), smem_u32(t_q), true, true, 0),
                 mma_hidden_half(tmem + TM_S1, smem_u32(big(ib2)), smem_u32(t_q), true, true, 1))
       wait_mma();
+      if (tid == 0) {   // gZ1b and X2_bar are consumed: Z1 and X2 of this step can come in while E2 runs
+        load_big(ib2, p.sc_Z1 + slot * BIG);
+        load_big(ib3, p.sc_X2 + slot * BIG);
+      }
       // ---- E2: bf16 snapshots of the gradient state; dQ
       {
         uint8_t* s1b = big(ib0);
@@ -845,8 +849,6 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       if (tid == 0) {
         tma_store_2d(&tmDQ, t_go, 0, row0);
         tma_commit_group();
-        load_big(ib2, p.sc_Z1 + slot * BIG);
-        load_big(ib3, p.sc_X2 + slot * BIG);
       }
       wait_bar(BAR_BIG + ib4);
       wait_bar(BAR_T + 4);
@@ -1092,12 +1094,14 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         if (j > 0) issue_tiles_a(j - 1);
       }
       wait_bar(BAR_BIG + ib4);
-      wait_bar(BAR_BIG + ib0);
+      // X2 was requested just now: only the issuers of G14 wait for it before issuing, G13 and G15 start at once
+      if (warp == 2 || warp == 3) wait_bar(BAR_BIG + ib0);
       // G13 // G15 // G14
       TTT_ISSUE(mma_token_major(tmem + TM_A, smem_u32(big(ib2)), smem_u32(big(ib4))),
                 mma_hidden_major(tmem + TM_S1, smem_u32(big(ib2)), smem_u32(t_k), true, true),
                 mma_hidden_half(tmem + TM_S2, smem_u32(big(ib0)), smem_u32(t_q), true, true, 0),
                 mma_hidden_half(tmem + TM_S2, smem_u32(big(ib0)), smem_u32(t_q), true, true, 1))
+      if (warp != 2 && warp != 3) wait_bar(BAR_BIG + ib0);
       wait_mma();
       // ---- E6: dK = partial + gZ1in W1^T, staged over the dl/dZ2 tile (dead since G12) and stored by TMA;
       // nothing waits for the store here: the tile's next load is issue_gz2's
