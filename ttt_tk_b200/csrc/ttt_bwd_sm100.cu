@@ -397,6 +397,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       publish();
       if (tid == 0) {
+        tma_wait_group_read<0>();     // the previous mini-batch's x_hat_ln has left the U2 tile (rewritten after MMA2)
         bulk_store_1d(p.sc_X2 + slot * BIG, bX2, BIG);
         bulk_store_1d(p.sc_Z1 + slot * BIG, bZ1, BIG);
         tma_commit_group();
@@ -441,8 +442,9 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             b[0] += g[x1]; b[1] = fmaf(g[x1], xh[x1], b[1]);
           }
         }
-        tok_st_global(p.sc_xhf + slot * TILE, xh);
-        tok_st_global(p.sc_gof + slot * TILE, e);
+        // x_hat_fused leaves through the V tile (every thread overwrites exactly the elements it has just
+        // read) as a bulk store; grad_output_fused is not kept: the sweep rebuilds it from x_hat_fused, K, V
+        tok_st_tile(tm, tV, xh);
         tok_row_allreduce<2, 2>(tm, a, b, sXch);
         const float sc0 = rs0 * (1.f / 64.f), sc1 = rs1 * (1.f / 64.f);
         const float ne0 = -__bfloat162float(eta[tm.r0]), ne1 = -__bfloat162float(eta[tm.r1]);
@@ -457,7 +459,6 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           }
         }
         tok_st_tile(tm, tGZ2, g);
-        tok_st_global(p.sc_gZ2 + slot * TILE, g);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           g[4 * q] *= ne0; g[4 * q + 1] *= ne0;
@@ -474,7 +475,9 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
       // MMA3: R^T = W2 gZ2^T
       if (tid == 0) {
-        if (j + 1 < gsz) issue_v(j + 1);        // V is consumed
+        bulk_store_1d(p.sc_xhf + slot * TILE, tV, TILE);
+        bulk_store_1d(p.sc_gZ2 + slot * TILE, tGZ2, TILE);
+        tma_commit_group();
       }
       TTT_ISSUE(mma_hidden_half(tmem + TM_A, smem_u32(bW2), smem_u32(tGZ2), false, false, 0),
                 mma_hidden_half(tmem + TM_A, smem_u32(bW2), smem_u32(tGZ2), false, false, 1),
@@ -517,6 +520,8 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
       // MMA4: W1^T += U1^T K ; W2 += X2^T U2
       if (tid == 0) {
+        tma_wait_group_read<0>();               // x_hat_fused has left the V tile
+        if (j + 1 < gsz) issue_v(j + 1);
         bulk_store_1d(p.sc_gZ1 + slot * BIG, bGP, BIG);
         tma_commit_group();
       }
@@ -616,15 +621,19 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           z[4 * q] *= rs0; z[4 * q + 1] *= rs0;
           z[4 * q + 2] *= rs1; z[4 * q + 3] *= rs1;
         }
-        tok_st_global(p.sc_xhln + slot * TILE, z);
+        tok_st_tile(tm, tU2, z);      // the U2 tile is dead since MMA4; x_hat_ln leaves through it
         if (tm.colhalf == 0 && tm.l3 == 0) {
           p.sc_sigln[slot * 64 + tm.r0] = 1.f / rs0;
           p.sc_sigln[slot * 64 + tm.r1] = 1.f / rs1;
         }
       }
-      if (tid == 0) tma_wait_group_read<0>();   // every image of this mini-batch has left shared memory
+      if (tid == 0) tma_wait_group_read<0>();   // every big image of this mini-batch has left shared memory
       publish();
-      if (tid == 0 && j + 2 < gsz && !*abort_flag) issue_inputs(j + 2);
+      if (tid == 0) {
+        bulk_store_1d(p.sc_xhln + slot * TILE, tU2, TILE);
+        tma_commit_group();
+        if (j + 2 < gsz && !*abort_flag) issue_inputs(j + 2);
+      }
       if (*abort_flag) { aborted = true; break; }
     }
     if (aborted) break;
@@ -796,9 +805,10 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         Gb1 += bsum;
       }
       publish();
-      if (tid == 0) {   // x_hat_ln and its column sums are consumed: bring grad_output_fused into that tile
+      if (tid == 0) {   // x_hat_ln and its column sums are consumed: bring V into that tile (E4 rebuilds
+                        // grad_output_fused = gamma x_hat_fused + beta - (V - K) from it)
         mbar_expect_tx(&bars[BAR_T + 1], TILE);
-        bulk_load_1d(t_a, p.sc_gof + slot * TILE, TILE, &bars[BAR_T + 1]);
+        tma_load_2d(t_a, &tmV, &bars[BAR_T + 1], 0, row0);
         pending |= 1u << (BAR_T + 1);
         issue_gz2(j);
       }
@@ -943,17 +953,21 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tok_ld_tile(tm, t_a, go);
         float ra[5] = {0.f, 0.f, 0.f, 0.f, 0.f}, rb[5] = {0.f, 0.f, 0.f, 0.f, 0.f};   // d12, d3, sum A2, sum A2 xh, sum gxf xh
         {
-          float acc1[16], acc2[16], kk[16], gb2[8];
+          float acc1[16], acc2[16], kk[16], gb2[8], bet[8];
           tok_ld(tm, tmem + TM_B + 64, acc1);     // X2 G_W2
           tok_ld(tm, tmem + TM_A, acc2);          // P W2
           tok_ld(tm, tmem + TM_B, t1);            // gZ1 G_W1
           tok_ld_tile(tm, t_k, kk);
           tok_ld_cols(tm, sGb2, gb2);
+          tok_ld_cols(tm, sBeta, bet);
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
               const int x0 = 4 * q + h, x1 = 4 * q + 2 + h, c = 2 * q + h;
+              // go[] arrives holding V: grad_output_fused = gamma x_hat_fused + beta - (V - K)
+              go[x0] = fmaf(gam[c], xh[x0], bet[c]) - (go[x0] - kk[x0]);
+              go[x1] = fmaf(gam[c], xh[x1], bet[c]) - (go[x1] - kk[x1]);
               const float u0 = acc1[x0] + gb2[c], u1 = acc1[x1] + gb2[c];
               ra[0] = fmaf(gz[x0], u0, ra[0]);
               rb[0] = fmaf(gz[x1], u1, rb[0]);
