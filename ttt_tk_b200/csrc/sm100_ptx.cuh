@@ -142,6 +142,10 @@ __device__ __forceinline__ void tma_wait_group() {
 __device__ __forceinline__ void prefetch_tmap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
+// Bring the 128-byte line at `p` (global memory) into L2.
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
 
 // ------------------------------------------------------------------ tensor memory
 // One full warp executes alloc / dealloc.  ncols: power of two, 32..512.

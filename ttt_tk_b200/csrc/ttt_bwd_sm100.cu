@@ -248,6 +248,16 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   // ---- column sums over the 64 tokens of token tiles, while the MMAs of a phase run: every thread
   // sums 16 rows of one column (rows 16 cs_q .., column cs_f) into `part` (the exchange buffer of the
   // token-major epilogues, idle in these windows); after a CTA barrier threads 0..63 add the four parts.
+  // All CTAs reach a group boundary together, and each then reads 132 KB of state: the lines are asked
+  // into L2 one step ahead (two 64 KB matrices = 2 x 512 lines, two lines of each per thread).
+  auto prefetch_state = [&](const float* m1, const float* m2) {
+    const char* a = reinterpret_cast<const char*>(m1) + tid * 128;
+    const char* b = reinterpret_cast<const char*>(m2) + tid * 128;
+    prefetch_l2(a);
+    prefetch_l2(a + 32768);
+    prefetch_l2(b);
+    prefetch_l2(b + 32768);
+  };
   const int cs_q = tid >> 6, cs_f = tid & 63;
   float* part = sXch;      // [3][4][64]
   auto colsum16 = [&](const uint8_t* t) {
@@ -322,11 +332,14 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       for (int half = 0; half < 2; ++half) {
         uint32_t v[32];
         float f[32];
+        float4 q4[8];
+        // both matrices' loads of this half go out before either is used (one memory round trip, not two)
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          f[j] = W1g[(half * 32 + j) * 256 + hrow];
-          v[j] = __float_as_uint(f[j]);
-        }
+        for (int j = 0; j < 32; ++j) f[j] = W1g[(half * 32 + j) * 256 + hrow];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) q4[j] = reinterpret_cast<const float4*>(W2g)[half * 8 + j];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(f[j]);
         tmem_st32(tmem + lane_base + TM_S1 + wg * 64 + half * 32, v);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -336,8 +349,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const float4 q4 = reinterpret_cast<const float4*>(W2g)[half * 8 + j];
-          f[j * 4 + 0] = q4.x; f[j * 4 + 1] = q4.y; f[j * 4 + 2] = q4.z; f[j * 4 + 3] = q4.w;
+          f[j * 4 + 0] = q4[j].x; f[j * 4 + 1] = q4[j].y; f[j * 4 + 2] = q4[j].z; f[j * 4 + 3] = q4[j].w;
         }
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(f[j]);
@@ -366,6 +378,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       const uint8_t* sQ = tile(2 * s + 1);
       const uint8_t* sV = tV;
       const __nv_bfloat16* eta = sEta + s * 64;
+      if (j == gsz - 1) prefetch_state(Gsrc_W1, Gsrc_W2);    // read back when the sweep starts
       wait_bar(BAR_IN + s);
 
       // MMA1: Z1^T = W1^T K^T
@@ -639,25 +652,6 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     if (aborted) break;
 
     // ================================================================== reverse sweep
-    // dL/dW state: global (fp32) -> tensor memory
-    {
-#pragma unroll 1
-      for (int half = 0; half < 2; ++half) {
-        uint32_t v[32];
-#pragma unroll
-        for (int q = 0; q < 32; ++q) v[q] = __float_as_uint(Gsrc_W1[(half * 32 + q) * 256 + hrow]);
-        tmem_st32(tmem + lane_base + TM_S1 + wg * 64 + half * 32, v);
-        const float4* src = reinterpret_cast<const float4*>(Gsrc_W2 + hrow * 64 + half * 32);
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          const float4 q4 = src[q];
-          v[q * 4 + 0] = __float_as_uint(q4.x); v[q * 4 + 1] = __float_as_uint(q4.y);
-          v[q * 4 + 2] = __float_as_uint(q4.z); v[q * 4 + 3] = __float_as_uint(q4.w);
-        }
-        tmem_st32(tmem + lane_base + TM_S2 + wg * 64 + half * 32, v);
-      }
-      tmem_wait_st();
-    }
     // buffer roles: i0b = W1+ (bf16), i1b = W2+, the other three free
     int ib0 = 0, ib1 = 1, ib2 = 2, ib3 = 3, ib4 = 4;
     uint8_t* t_go = tile(0);
@@ -712,11 +706,36 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       load_big(ib2, p.sc_Z1b + (slot0 + gsz - 1) * BIG);
       issue_rest(gsz - 1);
     }
+    // (the first step's loads are in flight while the gradient state comes back)
+    // dL/dW state: global (fp32) -> tensor memory
+    {
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        uint32_t v[32];
+        float4 q4[8];
+        const float4* src = reinterpret_cast<const float4*>(Gsrc_W2 + hrow * 64 + half * 32);
+#pragma unroll
+        for (int q = 0; q < 32; ++q) v[q] = __float_as_uint(Gsrc_W1[(half * 32 + q) * 256 + hrow]);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) q4[q] = src[q];
+        tmem_st32(tmem + lane_base + TM_S1 + wg * 64 + half * 32, v);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          v[q * 4 + 0] = __float_as_uint(q4[q].x); v[q * 4 + 1] = __float_as_uint(q4[q].y);
+          v[q * 4 + 2] = __float_as_uint(q4[q].z); v[q * 4 + 3] = __float_as_uint(q4[q].w);
+        }
+        tmem_st32(tmem + lane_base + TM_S2 + wg * 64 + half * 32, v);
+      }
+      tmem_wait_st();
+    }
+    tc_fence_before_sync();   // the state columns are read by the MMAs of the first step
 
     for (int j = gsz - 1; j >= 0; --j) {
       const long slot = slot0 + j;
       const int row0 = static_cast<int>(tok_rows0 + (long)(i0 + j) * 64);   // first token row of this mini-batch
       float kp[16];                                                          // partial dK, completed in E6
+      if (j == 0 && ck > 0)                                                  // the next group's checkpoint
+        prefetch_state(p.W1c + (sid * p.nck + ck - 1) * (64 * 256), p.W2c + (sid * p.nck + ck - 1) * (256 * 64));
 
       // ---- S4: backward of the output LayerNorm
       wait_bar(BAR_T + 0);
