@@ -1173,11 +1173,9 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         for (int q = 0; q < 32; ++q) Gdst_W1[(half * 32 + q) * 256 + hrow] = __uint_as_float(v[q]);
         tmem_ld32(tmem + lane_base + TM_S2 + wg * 64 + half * 32, v);
         tmem_wait_ld();
-        float4* dst = reinterpret_cast<float4*>(Gdst_W2 + hrow * 64 + half * 32);
-#pragma unroll
-        for (int q = 0; q < 8; ++q)
-          dst[q] = make_float4(__uint_as_float(v[q * 4]), __uint_as_float(v[q * 4 + 1]),
-                               __uint_as_float(v[q * 4 + 2]), __uint_as_float(v[q * 4 + 3]));
+        // whole lines through a staging area in the first two hidden-major buffers (nothing is in flight
+        // into them at the end of a group)
+        store_rows_coalesced(Gdst_W2 + (hrow - lane) * 64 + half * 32, 64, v, big(0) + warp * kRowStageBytes, lane);
       }
       Gsrc_W1 = Gdst_W1;
       Gsrc_W2 = Gdst_W2;

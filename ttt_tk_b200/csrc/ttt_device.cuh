@@ -256,6 +256,28 @@ TTT_MMA_LOOP
 #endif
 }
 
+// ---- A warp's 32 rows x 32 fp32 columns (lane = row, v = the row's 32 values) -> a row-major global
+// matrix with `ld` floats per row, as whole 128-byte lines: written straight from the registers the
+// 16-byte stores of a warp would land in 32 different lines (measured: the fp32 W2 checkpoint written
+// that way cost 4 % of the forward), so the block is turned through a warp-private staging area
+// (32 rows x 144 bytes of shared memory; the 16-byte pad keeps both directions conflict-free).
+// `dst` points at the block's first element (row of lane 0, first of the 32 columns).
+__device__ __forceinline__ void store_rows_coalesced(float* dst, int ld, const uint32_t (&v)[32], uint8_t* stage,
+                                                     int lane) {
+#pragma unroll
+  for (int c = 0; c < 8; ++c)
+    *reinterpret_cast<uint4*>(stage + lane * 144 + c * 16) = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = 4 * i + (lane >> 3), ch = lane & 7;
+    const uint4 w = *reinterpret_cast<const uint4*>(stage + r * 144 + ch * 16);
+    *reinterpret_cast<uint4*>(dst + static_cast<long>(r) * ld + ch * 4) = w;
+  }
+  __syncwarp();
+}
+constexpr uint32_t kRowStageBytes = 32 * 144;     // per warp
+
 // ---- Token-major 64 x 64 accumulators spread over 8 warps (256 threads).
 // A token-major accumulator (M = 64) keeps row r in TMEM lane (r % 16) + 32 * (r / 16): quadrant q
 // holds rows 16q .. 16q+15 in its first 16 lanes.  The two warps that may touch quadrant q (q and

@@ -207,23 +207,27 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   tc_fence_after_sync();
 
   // fp32 state (tensor memory, registers, shared memory) -> global, reference layouts
-  auto store_state = [&](float* W1o, float* b1o, float* W2o, float* b2o) {
+  // Quarter q of the state: 0, 2 = the two 32-column halves of W1^T; 1, 3 = those of W2.
+  auto store_state_quarter = [&](int q, float* W1o, float* W2o) {
+    const int half = q >> 1;
+    uint32_t v[32];
     __syncwarp();
-#pragma unroll 1
-    for (int half = 0; half < 2; ++half) {
-      uint32_t v[32];
+    if ((q & 1) == 0) {
       tmem_ld32(tmem + lane_base + TM_W1 + wg * 64 + half * 32, v);
       tmem_wait_ld();
 #pragma unroll
       for (int j = 0; j < 32; ++j) W1o[(half * 32 + j) * 256 + hrow] = __uint_as_float(v[j]);
+    } else {
+      // through a staging area in the X2 / G' buffers: only called while those are free (before EPI1
+      // writes them: the first MMA window of a mini-batch, or after the last mini-batch)
       tmem_ld32(tmem + lane_base + TM_W2 + wg * 64 + half * 32, v);
       tmem_wait_ld();
-      float4* dst = reinterpret_cast<float4*>(W2o + hrow * 64 + half * 32);
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        dst[j] = make_float4(__uint_as_float(v[j * 4]), __uint_as_float(v[j * 4 + 1]),
-                             __uint_as_float(v[j * 4 + 2]), __uint_as_float(v[j * 4 + 3]));
+      store_rows_coalesced(W2o + (hrow - lane) * 64 + half * 32, 64, v, sX2 + warp * kRowStageBytes, lane);
     }
+  };
+  auto store_state = [&](float* W1o, float* b1o, float* W2o, float* b2o) {
+#pragma unroll 1
+    for (int q = 0; q < 4; ++q) store_state_quarter(q, W1o, W2o);
     b1o[hrow] = b1v;
     if (tid < 64) b2o[tid] = sB2[tid];
   };
@@ -250,11 +254,13 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const uint8_t* sQ = smem + OFF_Q + s * TILE;
     const __nv_bfloat16* sEta = reinterpret_cast<const __nv_bfloat16*>(smem + OFF_ETA + s * 128);
 
-    if (it % p.cgs == 0) {
-      const long c = stream_id * p.nck + it / p.cgs;
-      store_state(p.W1c + c * (64 * 256), p.b1c + c * 256, p.W2c + c * (256 * 64), p.b2c + c * 64);
-      tc_fence_before_sync();
-    }
+    // A checkpoint (the state before this mini-batch) is written while the first three MMA groups of the
+    // mini-batch run: they leave the state columns alone (the update is the fourth), and the stores use
+    // neither shared memory nor the tensor pipe.
+    const bool ckpt = it % p.cgs == 0;
+    const long ckc = stream_id * p.nck + it / p.cgs;
+    float* ckW1 = p.W1c + ckc * (64 * 256);
+    float* ckW2 = p.W2c + ckc * (256 * 64);
     if (tid == 0) tma_wait_group_read<0>();   // previous Out tile has left shared memory
 
     mbar_wait_bounded(&full[s], (it / kStages) & 1, abort_flag, limit);
@@ -264,6 +270,12 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               mma_hidden_half(tmem + TM_A, smem_u32(sW1), smem_u32(sK), false, false, 1),
               ,
               )
+    if (ckpt) {
+      store_state_quarter(1, ckW1, ckW2);
+      store_state_quarter(3, ckW1, ckW2);
+      p.b1c[ckc * 256 + hrow] = b1v;
+      if (tid < 64) p.b2c[ckc * 64 + tid] = sB2[tid];     // before this mini-batch's column sums reach b2
+    }
     wait_mma();
     // ---- EPI1: X2^T = gelu(Z1^T + b1), G' = gelu'(Z1^T + b1)
 #pragma unroll 1
@@ -287,6 +299,7 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               ,
               ,
               )
+    if (ckpt) store_state_quarter(0, ckW1, ckW2);
     wait_mma();
     // ---- LN: fused LayerNorm + L2 gradient, U2 = -eta * dl/dZ2 (all 8 warps, 16 values each)
     {
@@ -350,6 +363,10 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       sXch[tid] = acc;     // the exchange buffer of the token-major epilogues is idle here
       __syncthreads();
       if (tid < 64) sB2[tid] += (sXch[tid] + sXch[64 + tid]) + (sXch[128 + tid] + sXch[192 + tid]);
+    }
+    if (ckpt) {
+      store_state_quarter(2, ckW1, ckW2);
+      tc_fence_before_sync();      // the state columns are written by the next MMA group
     }
     wait_mma();
     // ---- EPI3: U1^T = R^T * G' (= -eta dl/dZ1), b1 += row sum
