@@ -15,37 +15,42 @@ constexpr uint32_t TILE = 8192;    // 64 x 64 bf16 tile
 constexpr uint32_t BIG = 32768;    // 256 x 64 bf16 tile ("hidden-major": one row per hidden unit)
 
 constexpr float kG0 = 0.79788456f, kG1 = 0.044715f, kG2 = 0.1070322243f;
+constexpr float kG01 = kG0 * kG1;      // tanh argument: kG0 x (1 + kG1 x^2) = x (kG0 + kG01 x^2), one multiply less
 
 __device__ __forceinline__ float tanh_fast(float x) {
   float y;
   asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// gelu(x) and gelu'(x), tanh approximation
+// gelu(x), gelu'(x), gelu''(x), tanh approximation.  With t = tanh(x (kG0 + kG01 x^2)), h = (1 + t) / 2
+// and q = kG0 + kG2 x^2 (the argument's derivative):
+//   gelu = x h,   gelu' = h + x (1 - t^2) q / 2 = h + (g - g t) q   (since (1 - t^2) / 2 = h (1 - t)),
+//   gelu'' = (1 - t^2) (kG0 + 2 kG2 x^2 - x t q^2).
 __device__ __forceinline__ void gelu_pair(float x, float& g, float& gp) {
   const float x2 = x * x;
-  const float t = tanh_fast(kG0 * x * fmaf(kG1, x2, 1.f));
-  const float h = 0.5f * (1.f + t);
+  const float t = tanh_fast(x * fmaf(kG01, x2, kG0));
+  const float h = fmaf(0.5f, t, 0.5f);
   g = x * h;
-  gp = fmaf(0.5f * x * (1.f - t * t), fmaf(kG2, x2, kG0), h);
+  gp = fmaf(fmaf(-g, t, g), fmaf(kG2, x2, kG0), h);
 }
 __device__ __forceinline__ float gelu_only(float x) {
-  const float t = tanh_fast(kG0 * x * fmaf(kG1, x * x, 1.f));
-  return 0.5f * x * (1.f + t);
+  const float t = tanh_fast(x * fmaf(kG01, x * x, kG0));
+  return x * fmaf(0.5f, t, 0.5f);
 }
 __device__ __forceinline__ float gelu_grad(float x) {
-  const float x2 = x * x;
-  const float t = tanh_fast(kG0 * x * fmaf(kG1, x2, 1.f));
-  return fmaf(0.5f * x * (1.f - t * t), fmaf(kG2, x2, kG0), 0.5f * (1.f + t));
+  float g, gp;
+  gelu_pair(x, g, gp);
+  return gp;
 }
 // gelu'(x) and gelu''(x)
 __device__ __forceinline__ void gelu_grad_pair(float x, float& gp, float& gpp) {
   const float x2 = x * x;
-  const float t = tanh_fast(kG0 * x * fmaf(kG1, x2, 1.f));
-  const float s = 1.f - t * t;
+  const float t = tanh_fast(x * fmaf(kG01, x2, kG0));
+  const float h = fmaf(0.5f, t, 0.5f);
+  const float g = x * h;
   const float q = fmaf(kG2, x2, kG0);                 // kG0 + 3 kG0 kG1 x^2
-  gp = fmaf(0.5f * x * s, q, 0.5f * (1.f + t));
-  gpp = s * (fmaf(2.f * kG2, x2, kG0) - x * t * q * q);  // kG0 + 6 kG0 kG1 x^2 - x t q^2
+  gp = fmaf(fmaf(-g, t, g), q, h);
+  gpp = fmaf(-t, t, 1.f) * fmaf(-(x * t * q), q, fmaf(2.f * kG2, x2, kG0));
 }
 
 // ---- The same family on two elements at a time in packed fp16 arithmetic.  The tanh-GELU and its
@@ -68,29 +73,30 @@ __device__ __forceinline__ GeluH2 gelu_h2_core(float x0, float x1) {
   GeluH2 c;
   c.x = __hmax2(__hmin2(__floats2half2_rn(x0, x1), h2c(20.f)), h2c(-20.f));
   c.x2 = __hmul2(c.x, c.x);
-  const __half2 u = __hmul2(__hmul2(h2c(kG0), c.x), __hfma2(h2c(kG1), c.x2, h2c(1.f)));
+  const __half2 u = __hmul2(c.x, __hfma2(h2c(kG01), c.x2, h2c(kG0)));
   c.t = tanh_h2(u);
   c.hh = __hfma2(h2c(0.5f), c.t, h2c(0.5f));
   return c;
 }
-// gelu'(x) from the core values
-__device__ __forceinline__ __half2 gelu_h2_grad(const GeluH2& c, __half2& s, __half2& q) {
-  s = __hfma2(__hneg2(c.t), c.t, h2c(1.f));
+// gelu'(x) from the core values: h + (g - g t) q
+__device__ __forceinline__ __half2 gelu_h2_grad(const GeluH2& c, __half2& q) {
+  const __half2 g = __hmul2(c.x, c.hh);
   q = __hfma2(h2c(kG2), c.x2, h2c(kG0));
-  return __hfma2(__hmul2(__hmul2(h2c(0.5f), c.x), s), q, c.hh);
+  return __hfma2(__hfma2(__hneg2(g), c.t, g), q, c.hh);
 }
 __device__ __forceinline__ void gelu_grad2(float x0, float x1, float& gp0, float& gp1) {
   const GeluH2 c = gelu_h2_core(x0, x1);
-  __half2 s, q;
-  const float2 gp = __half22float2(gelu_h2_grad(c, s, q));
+  __half2 q;
+  const float2 gp = __half22float2(gelu_h2_grad(c, q));
   gp0 = gp.x;
   gp1 = gp.y;
 }
 __device__ __forceinline__ void gelu_grad_pair2(float x0, float x1, float& gp0, float& gp1, float& gpp0,
                                                 float& gpp1) {
   const GeluH2 c = gelu_h2_core(x0, x1);
-  __half2 s, q;
-  const float2 gp = __half22float2(gelu_h2_grad(c, s, q));
+  __half2 q;
+  const float2 gp = __half22float2(gelu_h2_grad(c, q));
+  const __half2 s = __hfma2(__hneg2(c.t), c.t, h2c(1.f));
   const __half2 cc = __hfma2(h2c(2.f * kG2), c.x2, h2c(kG0));
   const __half2 xtq = __hmul2(__hmul2(c.x, c.t), q);
   const float2 gpp = __half22float2(__hmul2(s, __hfma2(__hneg2(xtq), q, cc)));
