@@ -270,15 +270,6 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     return (part[k * 256 + tid] + part[k * 256 + 64 + tid]) + (part[k * 256 + 128 + tid] + part[k * 256 + 192 + tid]);
   };
 
-  // the thread's fragment of a token tile -> the same swizzled image in global scratch
-  auto tok_st_global = [&](uint8_t* g, const float (&v)[16]) {
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      *reinterpret_cast<uint32_t*>(g + tm.off(tm.r0, q)) = pack_bf16(v[4 * q], v[4 * q + 1]);
-      *reinterpret_cast<uint32_t*>(g + tm.off(tm.r1, q)) = pack_bf16(v[4 * q + 2], v[4 * q + 3]);
-    }
-  };
-
   // =====================================================================================
   const float* Gsrc_W1 = p.gW1_last + sid * (64 * 256);
   const float* Gsrc_W2 = p.gW2_last + sid * (256 * 64);
