@@ -107,7 +107,7 @@ typedef struct ttt_b200_bwd_args {
   void* grad_l_wrt_Z2_group;         /* bf16 [B,H,cgs,64,64] */
   void* grad_l_wrt_Z1_group;         /* bf16 [B,H,cgs,64,256] */
   void* x_hat_fused_group;           /* bf16 [B,H,cgs,64,64] */
-  void* grad_x_hat_fused_group;      /* bf16 [B,H,cgs,64,64] */
+  void* grad_x_hat_fused_group;      /* bf16 [B,H,cgs,64,64]; validated, never touched */
   void* grad_output_fused_group;     /* bf16 [B,H,cgs,64,64]; validated, never touched (rebuilt from x_hat_fused, K, V) */
   float* std_fused_group;            /* fp32 [B,H,cgs,64] */
   /* upstream gradients */
