@@ -18,7 +18,7 @@
 // Scratch.  The recompute phase writes, per mini-batch slot of the group, into the caller's
 // `*_group` tensors (raw images of 128-byte-swizzled shared-memory tiles, so the sweep can
 // bring them back with plain bulk copies):
-//   Z1_group, X2_group, grad_l_wrt_Z1_group, Z1_bar_group, X2_bar_group : [256][64 tok] bf16
+//   Z1_group, X2_group, grad_l_wrt_Z1_group, Z1_bar_group (holds gelu'(Z1_bar)), X2_bar_group : [256][64 tok] bf16
 //   W1_init_group / W2_init_group (first 32 KB of each slot): bf16 W1^T / W2 before the update
 //   x_hat_fused, grad_output_fused, grad_l_wrt_Z2, x_hat_ln_group : [64 tok][64] bf16
 //   std_fused_group, std_ln_group : fp32 [64]
@@ -587,8 +587,8 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             float z[8], g[8];
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
-              z[k] = __uint_as_float(v[c * 8 + k]) + b1v;
-              g[k] = gelu_only(z[k]);
+              // the sweep needs gelu'(Z1_bar) only: it is cheaper here, next to gelu, than there from a bf16 copy
+              gelu_pair(__uint_as_float(v[c * 8 + k]) + b1v, g[k], z[k]);
             }
             const uint32_t off = sw128_off(hrow, half * 2 + c);
             *reinterpret_cast<uint4*>(bX2 + off) = pack_chunk(g);
@@ -802,12 +802,9 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             float z[8];
             ld_chunk(bz, hrow, half * 2 + c, z);
 #pragma unroll
-            for (int k = 0; k < 8; k += 2) {
-              float g0, g1;
-              gelu_grad2(z[k], z[k + 1], g0, g1);
-              z[k] = __uint_as_float(v[c * 8 + k]) * g0;
-              z[k + 1] = __uint_as_float(v[c * 8 + k + 1]) * g1;
-              bsum += z[k] + z[k + 1];
+            for (int k = 0; k < 8; ++k) {
+              z[k] *= __uint_as_float(v[c * 8 + k]);      // the tile holds gelu'(Z1_bar)
+              bsum += z[k];
             }
             st_chunk(bz, hrow, half * 2 + c, z);
           }

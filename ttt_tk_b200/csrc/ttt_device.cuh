@@ -37,11 +37,6 @@ __device__ __forceinline__ float gelu_only(float x) {
   const float t = tanh_fast(x * fmaf(kG01, x * x, kG0));
   return x * fmaf(0.5f, t, 0.5f);
 }
-__device__ __forceinline__ float gelu_grad(float x) {
-  float g, gp;
-  gelu_pair(x, g, gp);
-  return gp;
-}
 // gelu'(x) and gelu''(x)
 __device__ __forceinline__ void gelu_grad_pair(float x, float& gp, float& gpp) {
   const float x2 = x * x;
@@ -83,13 +78,6 @@ __device__ __forceinline__ __half2 gelu_h2_grad(const GeluH2& c, __half2& q) {
   const __half2 g = __hmul2(c.x, c.hh);
   q = __hfma2(h2c(kG2), c.x2, h2c(kG0));
   return __hfma2(__hfma2(__hneg2(g), c.t, g), q, c.hh);
-}
-__device__ __forceinline__ void gelu_grad2(float x0, float x1, float& gp0, float& gp1) {
-  const GeluH2 c = gelu_h2_core(x0, x1);
-  __half2 q;
-  const float2 gp = __half22float2(gelu_h2_grad(c, q));
-  gp0 = gp.x;
-  gp1 = gp.y;
 }
 __device__ __forceinline__ void gelu_grad_pair2(float x0, float x1, float& gp0, float& gp1, float& gpp0,
                                                 float& gpp1) {
