@@ -426,10 +426,10 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           xh[4 * q + 2] += b2c[2 * q]; xh[4 * q + 3] += b2c[2 * q + 1];
         }
         float rs0, rs1;
-        tok_layernorm(tm, xh, TTT_LN_EPS, sXch, rs0, rs1);
         float kk[16], vv[16], g[16], e[16];
-        tok_ld_tile(tm, sK, kk);
+        tok_ld_tile(tm, sK, kk);          // requested before the all-reduces of the LayerNorm, used after them
         tok_ld_tile(tm, sV, vv);
+        tok_layernorm(tm, xh, TTT_LN_EPS, sXch, rs0, rs1);
         float a[2] = {0.f, 0.f}, b[2] = {0.f, 0.f};
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -470,8 +470,8 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         tok_st_tile(tm, tU2, g);
         if (tm.colhalf == 0 && tm.l3 == 0) {
-          p.sc_sigf[slot * 64 + tm.r0] = 1.f / rs0;
-          p.sc_sigf[slot * 64 + tm.r1] = 1.f / rs1;
+          p.sc_sigf[slot * 64 + tm.r0] = rs0;     // the slot keeps 1/std: the sweep only ever divides by std
+          p.sc_sigf[slot * 64 + tm.r1] = rs1;
         }
       }
       if (tid == 0) tma_wait_group_read<0>();   // Z1 / X2 images have left shared memory
@@ -627,8 +627,8 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         tok_st_tile(tm, tU2, z);      // the U2 tile is dead since MMA4; x_hat_ln leaves through it
         if (tm.colhalf == 0 && tm.l3 == 0) {
-          p.sc_sigln[slot * 64 + tm.r0] = 1.f / rs0;
-          p.sc_sigln[slot * 64 + tm.r1] = 1.f / rs1;
+          p.sc_sigln[slot * 64 + tm.r0] = rs0;
+          p.sc_sigln[slot * 64 + tm.r1] = rs1;
         }
       }
       if (tid == 0) tma_wait_group_read<0>();   // every big image of this mini-batch has left shared memory
@@ -749,7 +749,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           }
         }
         tok_row_allreduce<2, 2>(tm, a, b, sXch);
-        const float q0 = 1.f / (64.f * sSigLn[tm.r0]), q1 = 1.f / (64.f * sSigLn[tm.r1]);
+        const float q0 = sSigLn[tm.r0] * (1.f / 64.f), q1 = sSigLn[tm.r1] * (1.f / 64.f);   // 1 / (64 std)
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
 #pragma unroll
@@ -954,7 +954,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         float gam[8];
         tok_ld_cols(tm, sGamma, gam);
         const float eta0 = __bfloat162float(sEta[tm.r0]), eta1 = __bfloat162float(sEta[tm.r1]);
-        const float rs0 = 1.f / sSigF[tm.r0], rs1 = 1.f / sSigF[tm.r1];
+        const float rs0 = sSigF[tm.r0], rs1 = sSigF[tm.r1];      // 1 / std
         tok_ld_tile(tm, t_gz2, gz);
         tok_ld_tile(tm, t_xf, xh);
         tok_ld_tile(tm, t_a, go);

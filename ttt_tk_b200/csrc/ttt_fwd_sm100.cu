@@ -314,10 +314,10 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         xh[4 * j + 2] += b2c[2 * j]; xh[4 * j + 3] += b2c[2 * j + 1];
       }
       float rs0, rs1;
-      tok_layernorm(tm, xh, TTT_LN_EPS, sXch, rs0, rs1);
       float kk[16], vv[16], g[16];
-      tok_ld_tile(tm, sK, kk);
+      tok_ld_tile(tm, sK, kk);          // requested before the all-reduces of the LayerNorm, used after them
       tok_ld_tile(tm, sV, vv);
+      tok_layernorm(tm, xh, TTT_LN_EPS, sXch, rs0, rs1);
       float a[2] = {0.f, 0.f}, b[2] = {0.f, 0.f};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -460,8 +460,8 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         z[4 * j + 2] += b2c[2 * j]; z[4 * j + 3] += b2c[2 * j + 1];
       }
       float rs0, rs1;
+      tok_ld_tile(tm, sQ, q);           // requested before the all-reduces of the LayerNorm, used after them
       tok_layernorm(tm, z, TTT_LN_EPS, sXch, rs0, rs1);
-      tok_ld_tile(tm, sQ, q);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
 #pragma unroll
