@@ -497,12 +497,13 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         for (int half = 0; half < 4; ++half) {   // 16 columns per pass
           uint32_t v[16];
           tmem_ld16(tmem + lane_base + TM_A + wg * 64 + half * 16, v);
+          const uint4 gr[2] = {ld_chunk_raw(bGP, hrow, half * 2), ld_chunk_raw(bGP, hrow, half * 2 + 1)};
           tmem_wait_ld();
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
             float gp[8], u[8];
             const uint32_t off = sw128_off(hrow, half * 2 + c);
-            unpack_chunk(*reinterpret_cast<const uint4*>(bGP + off), gp);
+            unpack_chunk(gr[c], gp);
 #pragma unroll
             for (int k = 0; k < 8; ++k) gp[k] *= __uint_as_float(v[c * 8 + k]);     // dl/dZ1
             const uint4 w = pack_chunk(gp);
@@ -796,11 +797,12 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         for (int half = 0; half < 4; ++half) {   // 16 columns per pass
           uint32_t v[16];
           tmem_ld16(tmem + lane_base + TM_A + wg * 64 + half * 16, v);
+          const uint4 zr[2] = {ld_chunk_raw(bz, hrow, half * 2), ld_chunk_raw(bz, hrow, half * 2 + 1)};
           tmem_wait_ld();
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
             float z[8];
-            ld_chunk(bz, hrow, half * 2 + c, z);
+            unpack_chunk(zr[c], z);
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
               z[k] *= __uint_as_float(v[c * 8 + k]);      // the tile holds gelu'(Z1_bar)
@@ -913,11 +915,12 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         for (int half = 0; half < 4; ++half) {   // 16 columns per pass
           uint32_t v[16];
           tmem_ld16(tmem + lane_base + TM_A + wg * 64 + half * 16, v);
+          const uint4 zr[2] = {ld_chunk_raw(bz, hrow, half * 2), ld_chunk_raw(bz, hrow, half * 2 + 1)};
           tmem_wait_ld();
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
             float z[8], pp[8], gp[8], et[8];
-            ld_chunk(bz, hrow, half * 2 + c, z);
+            unpack_chunk(zr[c], z);
             unpack_chunk(*reinterpret_cast<const uint4*>(sEta + half * 16 + c * 8), et);   // one broadcast load
 #pragma unroll
             for (int k = 0; k < 8; k += 2) {
@@ -961,10 +964,9 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         float ra[5] = {0.f, 0.f, 0.f, 0.f, 0.f}, rb[5] = {0.f, 0.f, 0.f, 0.f, 0.f};   // d12, d3, sum A2, sum A2 xh, sum gxf xh
         {
           float acc1[16], acc2[16], kk[16], gb2[8], bet[8];
-          tok_ld(tm, tmem + TM_B + 64, acc1);     // X2 G_W2
-          tok_ld(tm, tmem + TM_A, acc2);          // P W2
-          tok_ld(tm, tmem + TM_B, t1);            // gZ1 G_W1
           tok_ld_tile(tm, t_k, kk);
+          // X2 G_W2, P W2, gZ1 G_W1
+          tok_ld3(tm, tmem + TM_B + 64, acc1, tmem + TM_A, acc2, tmem + TM_B, t1);
           tok_ld_cols(tm, sGb2, gb2);
           tok_ld_cols(tm, sBeta, bet);
 #pragma unroll
@@ -1092,12 +1094,14 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           uint32_t v[16], w[16];
           tmem_ld16(tmem + lane_base + TM_B + wg * 64 + half * 16, v);
           tmem_ld16(tmem + lane_base + TM_A + wg * 64 + half * 16, w);
+          const uint4 gr[2] = {ld_chunk_raw(bgp, hrow, half * 2), ld_chunk_raw(bgp, hrow, half * 2 + 1)};
+          const uint4 sr[2] = {ld_chunk_raw(bs, hrow, half * 2), ld_chunk_raw(bs, hrow, half * 2 + 1)};
           tmem_wait_ld();
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
             float gp[8], sv[8];
-            ld_chunk(bgp, hrow, half * 2 + c, gp);
-            ld_chunk(bs, hrow, half * 2 + c, sv);
+            unpack_chunk(gr[c], gp);
+            unpack_chunk(sr[c], sv);
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
               sv[k] = fmaf(__uint_as_float(v[c * 8 + k]), gp[k], __uint_as_float(w[c * 8 + k]) * sv[k]);

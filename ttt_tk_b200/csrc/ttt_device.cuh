@@ -115,6 +115,10 @@ __device__ __forceinline__ void st_chunk(uint8_t* tile, uint32_t row, uint32_t c
 __device__ __forceinline__ void ld_chunk(const uint8_t* tile, uint32_t row, uint32_t chunk, float* v) {
   unpack_chunk(*reinterpret_cast<const uint4*>(tile + sw128_off(row, chunk)), v);
 }
+// the raw 16 bytes of a chunk: requested between a tensor-memory load and its wait, unpacked after
+__device__ __forceinline__ uint4 ld_chunk_raw(const uint8_t* tile, uint32_t row, uint32_t chunk) {
+  return *reinterpret_cast<const uint4*>(tile + sw128_off(row, chunk));
+}
 __device__ __forceinline__ float ld_elem(const uint8_t* tile, uint32_t row, uint32_t col) {
   return __bfloat162float(
       *reinterpret_cast<const __nv_bfloat16*>(tile + sw128_off(row, col >> 3) + (col & 7) * 2));
@@ -292,6 +296,21 @@ struct TokMap {
   // byte offset of the column pair j of row r inside a swizzled [64][64] bf16 tile
   __device__ __forceinline__ uint32_t off(int r, int j) const { return sw128_off(r, colhalf * 4 + j) + l3 * 4; }
 };
+// three accumulators with one wait (the loads overlap)
+__device__ __forceinline__ void tok_ld3(const TokMap& m, uint32_t acc_a, float (&a)[16], uint32_t acc_b,
+                                        float (&b)[16], uint32_t acc_c, float (&c)[16]) {
+  uint32_t ua[16], ub[16], uc[16];
+  tmem_ld_16x256b_x4(acc_a + m.taddr, ua);
+  tmem_ld_16x256b_x4(acc_b + m.taddr, ub);
+  tmem_ld_16x256b_x4(acc_c + m.taddr, uc);
+  tmem_wait_ld();
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    a[i] = __uint_as_float(ua[i]);
+    b[i] = __uint_as_float(ub[i]);
+    c[i] = __uint_as_float(uc[i]);
+  }
+}
 __device__ __forceinline__ void tok_ld(const TokMap& m, uint32_t tmem_acc, float (&v)[16]) {
   uint32_t u[16];
   tmem_ld_16x256b_x4(tmem_acc + m.taddr, u);

@@ -376,11 +376,13 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       for (int half = 0; half < 2; ++half) {
         uint32_t v[32];
         tmem_ld32(tmem + lane_base + TM_A + wg * 64 + half * 32, v);
+        const uint4 gr[4] = {ld_chunk_raw(sGP, hrow, half * 4), ld_chunk_raw(sGP, hrow, half * 4 + 1),
+                             ld_chunk_raw(sGP, hrow, half * 4 + 2), ld_chunk_raw(sGP, hrow, half * 4 + 3)};
         tmem_wait_ld();
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           float gp[8];
-          ld_chunk(sGP, hrow, half * 4 + c, gp);
+          unpack_chunk(gr[c], gp);
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             gp[k] *= __uint_as_float(v[c * 8 + k]);
