@@ -1082,8 +1082,14 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
       wait_mma();
-      // the state-gradient snapshot buffer is free: bring the next step's Z1_bar into it
-      if (tid == 0 && j > 0) load_big(ib1, p.sc_Z1b + (slot - 1) * BIG);
+      if (tid == 0) {
+        // the W2 state-gradient snapshot is consumed: X2 comes back into its buffer for G14 (it lands while
+        // E5 runs); dV has left its tile, the d_gamma addends and x_hat_fused are consumed: the next step's
+        // first tiles are requested now, two phases before they are needed
+        load_big(ib1, p.sc_X2 + slot * BIG);
+        tma_wait_group_read<0>();
+        if (j > 0) issue_tiles_a(j - 1);
+      }
       // ---- E5: gZ1in^T = gX2^T gelu'(Z1^T) + R^T S^T, in place over S^T
       {
         uint8_t* bs = big(ib2);
@@ -1113,20 +1119,15 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         Gb1 += bsum;
       }
       publish();
-      if (tid == 0) {
-        load_big(ib0, p.sc_X2 + slot * BIG);
-        tma_wait_group_read<0>();     // dV has left its tile
-        if (j > 0) issue_tiles_a(j - 1);
-      }
+      // gelu'(Z1) is consumed: the next step's gelu'(Z1_bar) comes into its buffer
+      if (tid == 0 && j > 0) load_big(ib0, p.sc_Z1b + (slot - 1) * BIG);
       wait_bar(BAR_BIG + ib4);
-      // X2 was requested just now: only the issuers of G14 wait for it before issuing, G13 and G15 start at once
-      if (warp == 2 || warp == 3) wait_bar(BAR_BIG + ib0);
+      wait_bar(BAR_BIG + ib1);
       // G13 // G15 // G14
       TTT_ISSUE(mma_token_major(tmem + TM_A, smem_u32(big(ib2)), smem_u32(big(ib4))),
                 mma_hidden_major(tmem + TM_S1, smem_u32(big(ib2)), smem_u32(t_k), true, true),
-                mma_hidden_half(tmem + TM_S2, smem_u32(big(ib0)), smem_u32(t_q), true, true, 0),
-                mma_hidden_half(tmem + TM_S2, smem_u32(big(ib0)), smem_u32(t_q), true, true, 1))
-      if (warp != 2 && warp != 3) wait_bar(BAR_BIG + ib0);
+                mma_hidden_half(tmem + TM_S2, smem_u32(big(ib1)), smem_u32(t_q), true, true, 0),
+                mma_hidden_half(tmem + TM_S2, smem_u32(big(ib1)), smem_u32(t_q), true, true, 1))
       wait_mma();
       // ---- E6: dK = partial + gZ1in W1^T, staged over the dl/dZ2 tile (dead since G12) and stored by TMA;
       // nothing waits for the store here: the tile's next load is issue_gz2's
@@ -1144,7 +1145,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       // pre-update weights of this mini-batch are the post-update weights of the previous one
       {
-        const int n0 = ib4, n1 = ib3, n2 = ib1, n3 = ib2, n4 = ib0;
+        const int n0 = ib4, n1 = ib3, n2 = ib0, n3 = ib2, n4 = ib1;
         ib0 = n0; ib1 = n1; ib2 = n2; ib3 = n3; ib4 = n4;
       }
       if (tid == 0 && j > 0 && !*abort_flag) issue_rest(j - 1);
