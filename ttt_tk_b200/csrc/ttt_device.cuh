@@ -259,7 +259,8 @@ TTT_MMA_LOOP
 // 16-byte stores of a warp would land in 32 different lines (measured: the fp32 W2 checkpoint written
 // that way cost 4 % of the forward), so the block is turned through a warp-private staging area
 // (32 rows x 144 bytes of shared memory; the 16-byte pad keeps both directions conflict-free).
-// `dst` points at the block's first element (row of lane 0, first of the 32 columns).
+// `dst` points at the block's first element (row of lane 0, first of the 32 columns).  The caller makes
+// sure that no other warp writes the bytes of this warp's staging area while the call runs.
 __device__ __forceinline__ void store_rows_coalesced(float* dst, int ld, const uint32_t (&v)[32], uint8_t* stage,
                                                      int lane) {
 #pragma unroll

@@ -275,6 +275,9 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       store_state_quarter(3, ckW1, ckW2);
       p.b1c[ckc * 256 + hrow] = b1v;
       if (tid < 64) p.b2c[ckc * 64 + tid] = sB2[tid];     // before this mini-batch's column sums reach b2
+      // a warp's staging area reaches into the X2 rows its neighbour writes in EPI1: nobody goes on to EPI1
+      // before every warp is done with its area
+      __syncthreads();
     }
     wait_mma();
     // ---- EPI1: X2^T = gelu(Z1^T + b1), G' = gelu'(Z1^T + b1)
