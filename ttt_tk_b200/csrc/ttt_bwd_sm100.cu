@@ -788,6 +788,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
       wait_mma();
+      if (tid == 0) load_big(ib1, p.sc_X2 + slot * BIG);   // W2+ is consumed (G1 was its only use): X2 for G5
       wait_bar(BAR_BIG + ib2);
       // ---- E1: gZ1b^T = gX2b^T * gelu'(Z1b^T), in place over Z1b^T
       {
@@ -829,14 +830,12 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 mma_hidden_half(tmem + TM_S1, smem_u32(big(ib2)), smem_u32(t_q), true, true, 0),
                 mma_hidden_half(tmem + TM_S1, smem_u32(big(ib2)), smem_u32(t_q), true, true, 1))
       wait_mma();
-      if (tid == 0) {   // gZ1b and X2_bar are consumed: Z1 and X2 of this step can come in while E2 runs
-        load_big(ib2, p.sc_Z1 + slot * BIG);
-        load_big(ib3, p.sc_X2 + slot * BIG);
-      }
+      // gZ1b is consumed: Z1 of this step comes in while E2 runs (X2_bar's buffer takes the W2 snapshot)
+      if (tid == 0) load_big(ib2, p.sc_Z1 + slot * BIG);
       // ---- E2: bf16 snapshots of the gradient state; dQ
       {
         uint8_t* s1b = big(ib0);
-        uint8_t* s2b = big(ib1);
+        uint8_t* s2b = big(ib3);
 #pragma unroll 1
         for (int half = 0; half < 4; ++half) {   // 16 columns per pass
           uint32_t v[16];
@@ -871,10 +870,10 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       wait_bar(BAR_BIG + ib4);
       wait_bar(BAR_T + 4);
-      if (warp == 1) wait_bar(BAR_BIG + ib3);   // X2 was requested just now: only the issuer of G5 waits for it here
+      wait_bar(BAR_BIG + ib1);      // X2, requested two phases ago
       // G4 // G8 // G5
       TTT_ISSUE(mma_token_major(tmem + TM_B, smem_u32(big(ib4)), smem_u32(big(ib0))),
-                mma_token_major(tmem + TM_B + 64, smem_u32(big(ib3)), smem_u32(big(ib1))),
+                mma_token_major(tmem + TM_B + 64, smem_u32(big(ib1)), smem_u32(big(ib3))),
                 mma_hidden_half(tmem + TM_A, smem_u32(big(ib0)), smem_u32(t_k), false, false, 0),
                 mma_hidden_half(tmem + TM_A, smem_u32(big(ib0)), smem_u32(t_k), false, false, 1))
       // ---- while the MMAs run: partial sums over the hidden units of gZ1 * G_b1 (fourth term of d_eta)
@@ -899,10 +898,9 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         *reinterpret_cast<float2*>(sPart + warp * 64 + 2 * lane) = make_float2(a0 + c0, a1 + c1);
       }
-      if (warp != 1) wait_bar(BAR_BIG + ib3);
       wait_mma();
       if (tid == 0) {
-        load_big(ib3, p.sc_W2 + slot * 65536);
+        load_big(ib1, p.sc_W2 + slot * 65536);      // X2 is consumed until G14: W2 takes its buffer
         tma_wait_group_read<0>();     // dQ has left the dL/dOut tile (E4 reuses it for dV)
       }
       wait_bar(BAR_BIG + ib2);
@@ -940,10 +938,10 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
       publish();
-      wait_bar(BAR_BIG + ib3);
+      wait_bar(BAR_BIG + ib1);
       wait_bar(BAR_T + 5);
       // G6 // G10
-      TTT_ISSUE(mma_token_major(tmem + TM_A, smem_u32(big(ib4)), smem_u32(big(ib3))),
+      TTT_ISSUE(mma_token_major(tmem + TM_A, smem_u32(big(ib4)), smem_u32(big(ib1))),
                 mma_hidden_half(tmem + TM_S2, smem_u32(big(ib4)), smem_u32(t_gz2), true, true, 0),
                 mma_hidden_half(tmem + TM_S2, smem_u32(big(ib4)), smem_u32(t_gz2), true, true, 1),
                 )
@@ -1066,10 +1064,10 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tma_store_2d(&tmDV, t_go, 0, row0);
         tma_commit_group();
       }
-      TTT_ISSUE(mma_hidden_half(tmem + TM_B, smem_u32(big(ib3)), smem_u32(t_q), false, false, 0); mma_hidden_half(tmem + TM_B, smem_u32(big(ib1)), smem_u32(t_g), false, true, 0),
-                mma_hidden_half(tmem + TM_B, smem_u32(big(ib3)), smem_u32(t_q), false, false, 1); mma_hidden_half(tmem + TM_B, smem_u32(big(ib1)), smem_u32(t_g), false, true, 1),
-                mma_hidden_half(tmem + TM_A, smem_u32(big(ib3)), smem_u32(t_gz2), false, false, 0),
-                mma_hidden_half(tmem + TM_A, smem_u32(big(ib3)), smem_u32(t_gz2), false, false, 1))
+      TTT_ISSUE(mma_hidden_half(tmem + TM_B, smem_u32(big(ib1)), smem_u32(t_q), false, false, 0); mma_hidden_half(tmem + TM_B, smem_u32(big(ib3)), smem_u32(t_g), false, true, 0),
+                mma_hidden_half(tmem + TM_B, smem_u32(big(ib1)), smem_u32(t_q), false, false, 1); mma_hidden_half(tmem + TM_B, smem_u32(big(ib3)), smem_u32(t_g), false, true, 1),
+                mma_hidden_half(tmem + TM_A, smem_u32(big(ib1)), smem_u32(t_gz2), false, false, 0),
+                mma_hidden_half(tmem + TM_A, smem_u32(big(ib1)), smem_u32(t_gz2), false, false, 1))
       {
         part[tid] = colsum16(t_q);
         part[256 + tid] = colsum16(t_a);
@@ -1086,7 +1084,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         // the W2 state-gradient snapshot is consumed: X2 comes back into its buffer for G14 (it lands while
         // E5 runs); dV has left its tile, the d_gamma addends and x_hat_fused are consumed: the next step's
         // first tiles are requested now, two phases before they are needed
-        load_big(ib1, p.sc_X2 + slot * BIG);
+        load_big(ib3, p.sc_X2 + slot * BIG);
         tma_wait_group_read<0>();
         if (j > 0) issue_tiles_a(j - 1);
       }
@@ -1122,12 +1120,12 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       // gelu'(Z1) is consumed: the next step's gelu'(Z1_bar) comes into its buffer
       if (tid == 0 && j > 0) load_big(ib0, p.sc_Z1b + (slot - 1) * BIG);
       wait_bar(BAR_BIG + ib4);
-      wait_bar(BAR_BIG + ib1);
+      wait_bar(BAR_BIG + ib3);
       // G13 // G15 // G14
       TTT_ISSUE(mma_token_major(tmem + TM_A, smem_u32(big(ib2)), smem_u32(big(ib4))),
                 mma_hidden_major(tmem + TM_S1, smem_u32(big(ib2)), smem_u32(t_k), true, true),
-                mma_hidden_half(tmem + TM_S2, smem_u32(big(ib1)), smem_u32(t_q), true, true, 0),
-                mma_hidden_half(tmem + TM_S2, smem_u32(big(ib1)), smem_u32(t_q), true, true, 1))
+                mma_hidden_half(tmem + TM_S2, smem_u32(big(ib3)), smem_u32(t_q), true, true, 0),
+                mma_hidden_half(tmem + TM_S2, smem_u32(big(ib3)), smem_u32(t_q), true, true, 1))
       wait_mma();
       // ---- E6: dK = partial + gZ1in W1^T, staged over the dl/dZ2 tile (dead since G12) and stored by TMA;
       // nothing waits for the store here: the tile's next load is issue_gz2's
@@ -1145,7 +1143,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       // pre-update weights of this mini-batch are the post-update weights of the previous one
       {
-        const int n0 = ib4, n1 = ib3, n2 = ib0, n3 = ib2, n4 = ib1;
+        const int n0 = ib4, n1 = ib1, n2 = ib0, n3 = ib2, n4 = ib3;
         ib0 = n0; ib1 = n1; ib2 = n2; ib3 = n3; ib4 = n4;
       }
       if (tid == 0 && j > 0 && !*abort_flag) issue_rest(j - 1);
