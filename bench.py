@@ -47,8 +47,8 @@ STATE_BYTES = 132352                  # fp32 W1 + b1 + W2 + b2 of one (b,h)
 # DRAM bytes per (stream, mini-batch) from the ncu capture summarised in profiles/ttt_fwd_bwd_kernels_current.md
 # (dram__bytes_read.sum + dram__bytes_write.sum over 128 streams x 16 mini-batches); the traffic grows in
 # proportion to the number of (stream, mini-batch) pairs, so a full-size launch is scaled from it.
-NCU_BWD_DRAM_BYTES_PER_MB = (582834688 + 585313792) / 2048
-NCU_FWD_DRAM_BYTES_PER_MB = (67619072 + 9522688) / 2048
+NCU_BWD_DRAM_BYTES_PER_MB = (583610880 + 585072384) / 2048
+NCU_FWD_DRAM_BYTES_PER_MB = (67620096 + 8762112) / 2048
 
 
 def algorithmic_bytes(B, H, NC, cgs):
