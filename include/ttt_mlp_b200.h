@@ -37,7 +37,17 @@ enum {
 };
 
 enum {
-  TTT_B200_FLAG_SYNC = 1u /* synchronise the stream and report device-side status before returning */
+  TTT_B200_FLAG_SYNC = 1u, /* synchronise the stream and report device-side status before returning */
+  /* Test hook for the failure path (no counterpart in the reference): stream 0 never issues the loads
+   * of its second mini-batch (its only one when NC = 1), so that the kernel's bounded wait for them
+   * runs out; the kernel reports code 3 through the status word and exits normally. */
+  TTT_B200_FLAG_TEST_LOST_LOAD = 2u,
+  /* Bits 8..11: how many CTAs (a thread-block cluster) share one (batch, head) stream, each owning
+   * 256 / n hidden units; the reference fixes this at compile time (TP = 2 in kernels/ttt/ttt.cu:11-12,
+   * 4 in kernels/ttt_backward/ttt.cu:12-16).  0 = chosen per launch from B*H and the GPU's SM count
+   * (overridable with the environment variable TTT_B200_CLUSTER); 1, 2 or 4 = forced. */
+  TTT_B200_FLAG_CLUSTER_SHIFT = 8,
+  TTT_B200_FLAG_CLUSTER_MASK = 0xFu << 8
 };
 
 /* Arguments of the forward.  Replaces ttt_forward(XQ, XK, XV, last_eta, ttt_norm_weight,

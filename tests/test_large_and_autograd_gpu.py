@@ -11,19 +11,19 @@ from ttt_tk_b200.synthetic import make_inputs
 pytestmark = pytest.mark.gpu
 
 
-def _run(d, cgs):
+def _run(d, cgs, cluster=None):
     dev = "cuda"
     B, H, NC = d["XQ"].shape[:3]
     t = {k: v.to(dev) for k, v in d.items()}
     ck = alloc_checkpoints(B, H, NC, cgs, dev)
     out = torch.empty_like(t["XQ"])
     ttt_forward(t["XQ"], t["XK"], t["XV"], t["last_eta"], t["ttt_norm_weight"], t["ttt_norm_bias"],
-                t["W1"], t["b1"], t["W2"], t["b2"], *ck, out, cgs)
+                t["W1"], t["b1"], t["W2"], t["b2"], *ck, out, cgs, cluster=cluster)
     scratch, outs = alloc_backward_buffers(B, H, NC, cgs, dev, fill=float("nan"))
     ttt_backward(t["XQ"], t["XK"], t["XV"], t["last_eta"].unsqueeze(-1).contiguous(), t["ttt_norm_weight"],
                  t["ttt_norm_bias"], *ck, out, *scratch, t["grad_L_W1_last"], t["grad_L_b1_last"],
                  t["grad_L_W2_last"], t["grad_L_b2_last"], t["grad_L_XQW_mini_batch"],
-                 *[outs[k] for k in GRAD_NAMES], cgs)
+                 *[outs[k] for k in GRAD_NAMES], cgs, cluster=cluster)
     torch.cuda.synchronize()
     assert take_status() == 0
     return out, ck, outs
@@ -56,8 +56,9 @@ def test_config1_full_size_forward_and_backward():
 
 def test_config2_full_size_streams_are_independent_and_correct():
     """configs[2] (B=4, H=32, seq 8192, cgs 8) at full size.  The oracle would need minutes for all 128
-    streams, so: (a) two streams taken out and run alone must give bit-identical results (streams are
-    independent and the kernels deterministic), (b) those two streams are checked against the oracle."""
+    streams, so: (a) two streams taken out and run alone (with the same one CTA per stream the full
+    launch gets) must give bit-identical results (streams are independent and the kernels
+    deterministic), (b) those two streams are checked against the oracle."""
     B, H, NC, cgs = 4, 32, 128, 8
     d = make_inputs(B, H, NC, seed=0, backward=True)
     out, ck, outs = _run(d, cgs)
@@ -69,7 +70,7 @@ def test_config2_full_size_streams_are_independent_and_correct():
                 sub[k] = v[:, h:h + 1].contiguous()
             else:
                 sub[k] = v[b:b + 1, h:h + 1].contiguous()
-        out1, ck1, outs1 = _run(sub, cgs)
+        out1, ck1, outs1 = _run(sub, cgs, cluster=1)
         assert torch.equal(out1[0, 0], out[b, h])
         for c1, c in zip(ck1, ck):
             assert torch.equal(c1[0, 0], c[b, h])
@@ -138,7 +139,7 @@ def test_config4_full_size_forward_runs_in_waves():
         sub = {k: (v[:, h:h + 1] if v.shape[0] == 1 else v[b:b + 1, h:h + 1]).contiguous() for k, v in t.items()}
         ck1 = alloc_checkpoints(1, 1, NC, cgs, dev)
         out1 = torch.empty_like(sub["XQ"])
-        ttt_forward(*[sub[k] for k in names], *ck1, out1, cgs, sync=True)
+        ttt_forward(*[sub[k] for k in names], *ck1, out1, cgs, sync=True, cluster=1)
         assert torch.equal(out1[0, 0], out[b, h])
         for c1, c in zip(ck1, ck):
             assert torch.equal(c1[0, 0], c[b, h])

@@ -48,6 +48,7 @@ EXPORTS = ["ttt_b200_forward", "ttt_b200_backward", "ttt_b200_backward_noalloc",
            "ttt_b200_unpack_tokens"]
 
 FLAG_SYNC = 1
+FLAG_TEST_LOST_LOAD = 2
 
 
 def load():

@@ -15,8 +15,11 @@
 
 #include "ttt_internal.h"
 
-int ttt_launch_forward(const ttt_b200_fwd_args* a, cudaStream_t stream, uint32_t* status, uint64_t limit_ns);
+int ttt_launch_forward(const ttt_b200_fwd_args* a, cudaStream_t stream, uint32_t* status, uint64_t limit_ns,
+                       int drop_load);
 int ttt_launch_backward(const ttt_b200_bwd_args* a, cudaStream_t stream, uint32_t* status, uint64_t limit_ns);
+int ttt_launch_forward_cluster(const ttt_b200_fwd_args* a, int cluster, cudaStream_t stream, uint32_t* status,
+                               uint64_t limit_ns, int drop_load);
 
 namespace {
 
@@ -45,7 +48,45 @@ uint64_t wait_limit_ns() {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// SM count of the current device (cached per device index).
+int sm_count() {
+  static std::mutex mu;
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  std::lock_guard<std::mutex> lk(mu);
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 }  // namespace
+
+// How many CTAs share one stream.  The mini-batches of a stream are strictly sequential, so with fewer
+// streams than SMs the idle SMs can only help by taking a share of every stream's hidden units: the
+// largest cluster size (1, 2 or 4) whose CTAs all fit on the GPU at once is used.
+int ttt_pick_cluster(int streams, uint32_t flags, int* cluster) {
+  int forced = static_cast<int>((flags & TTT_B200_FLAG_CLUSTER_MASK) >> TTT_B200_FLAG_CLUSTER_SHIFT);
+  if (forced == 0) {
+    static const int env = [] {
+      const char* e = std::getenv("TTT_B200_CLUSTER");
+      return e ? std::atoi(e) : 0;
+    }();
+    forced = env;
+  }
+  if (forced != 0) {
+    if (forced != 1 && forced != 2 && forced != 4)
+      return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "cluster size must be 1, 2 or 4");
+    *cluster = forced;
+    return TTT_B200_OK;
+  }
+  const int sms = sm_count();
+  *cluster = 4 * streams <= sms ? 4 : (2 * streams <= sms ? 2 : 1);
+  return TTT_B200_OK;
+}
 
 int ttt_set_error(int code, const char* msg) {
   g_last_error = msg ? msg : "";
@@ -155,7 +196,12 @@ extern "C" int ttt_b200_forward(const ttt_b200_fwd_args* a, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   uint32_t* status = nullptr;
   if (int rc = pre_launch(&status)) return rc;
-  if (int rc = ttt_launch_forward(a, stream, status, wait_limit_ns())) return rc;
+  int cluster = 1;
+  if (int rc = ttt_pick_cluster(a->B * a->H, a->flags, &cluster)) return rc;
+  const int drop = (a->flags & TTT_B200_FLAG_TEST_LOST_LOAD) ? (a->NC > 1 ? 1 : 0) : -1;
+  if (int rc = cluster == 1 ? ttt_launch_forward(a, stream, status, wait_limit_ns(), drop)
+                            : ttt_launch_forward_cluster(a, cluster, stream, status, wait_limit_ns(), drop))
+    return rc;
   if (a->flags & TTT_B200_FLAG_SYNC) return ttt_check_status(stream);
   return TTT_B200_OK;
 }

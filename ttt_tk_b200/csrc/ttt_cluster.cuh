@@ -1,0 +1,194 @@
+// Thread-block-cluster layer of the cluster-sharded TTT-MLP kernels: the 256 hidden units of one
+// (batch, head) stream are split over the kC CTAs of a cluster (kC = 2 or 4), and every
+// contraction over the hidden units leaves each CTA with a partial 64 x 64 fp32 tile that is summed
+// across the cluster through distributed shared memory.
+//
+// Replaces the reference's tp_reduce / tp_reduce_arrive (kernels/ttt_backward/ttt.cu:21-69) and the
+// forward's Z2 reduction (kernels/ttt/ttt.cu:332-348, 506-522), which exchange bf16 tiles between
+// hardware cluster barriers.  Here the partial tiles travel in fp32, straight from the registers of
+// the thread that read them out of tensor memory into the peers' shared memory (plain
+// st.shared::cluster stores), followed by one remote mbarrier arrive per warp and peer (release at
+// cluster scope); the receiver polls its own mbarrier with a bounded try_wait (acquire at cluster
+// scope).  The hardware cluster barrier, which cannot time out, is used only twice per kernel: after
+// the mbarriers are initialised and before the CTAs exit.
+#pragma once
+
+#include "ttt_device.cuh"
+
+namespace tttcl {
+
+using namespace tttdev;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cta address -> shared::cluster address of the same variable in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+// arrive on an mbarrier of another CTA of the cluster; orders this thread's earlier stores (and, after
+// a __syncwarp, its warp's) before the arrival
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
+// Bounded wait of the cluster kernels.  A thread whose wait runs out raises the abort flag of its own
+// CTA and of every peer (the flag lives at the same shared-memory offset in all of them), so that the
+// whole cluster leaves its waits within a few polls and walks to the exit barrier together.
+static __device__ __noinline__ bool mbar_wait_slow_cl(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                                      uint64_t limit_ns, uint32_t cluster_size) {
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if ((++spins & 0x3f) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > limit_ns) {
+        const uint32_t a = smem_u32(const_cast<uint32_t*>(abort_flag));
+        for (uint32_t r = 0; r < cluster_size; ++r) st_cluster_u32(mapa(a, r), 1u);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ bool mbar_wait_cl(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                             uint64_t limit_ns, uint32_t cluster_size) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  return mbar_wait_slow_cl(bar, parity, abort_flag, limit_ns, cluster_size);
+}
+
+// tcgen05.st counterpart of tmem_ld_16x256b_x4 (same thread <-> element mapping)
+__device__ __forceinline__ void tmem_st_16x256b_x4(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.16x256b.x4.b32 [%16], "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};" ::"r"(r[0]),
+      "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tok_st_tmem(const TokMap& m, uint32_t tmem_acc, const float (&v)[16]) {
+  uint32_t u[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) u[i] = __float_as_uint(v[i]);
+  tmem_st_16x256b_x4(tmem_acc + m.taddr, u);
+}
+
+// ---- MMA forms of the cluster kernels.  A CTA owns R = 256 / kC hidden units, kept as NB = R / 64
+// blocks of 64 rows: every accumulator is an M = 64 tile (row r in TMEM lane r % 16 + 32 (r / 16)) read
+// back with the 16x256b fragments of TokMap, whether its rows are hidden units or tokens.
+//
+// "Hidden-major" block product: D[64 hid x 64] (+)= A * B with A one [64][64] bf16 block read K-major
+// (row = hidden unit) and B a [64][64] tile read K-major (row = N index) or MN-major (row = K index).
+template <bool kBMn>
+__device__ __forceinline__ void mma_hid64(uint32_t tmem_d, uint32_t a_smem, uint32_t b_smem, uint32_t accumulate) {
+  constexpr uint32_t idesc = umma_idesc_bf16(64, 64, false, kBMn, false);
+  const uint32_t a0 = desc_lo(a_smem, 16);
+  const uint32_t b0 = desc_lo(b_smem, kBMn ? 8192 : 16);
+  constexpr uint32_t bstep = kBMn ? (2048u >> 4) : (32u >> 4);
+  mma_issue_rt(tmem_d, a0, b0, idesc, accumulate);
+#pragma unroll
+  for (int j = 1; j < 4; ++j) mma_issue_rt(tmem_d, a0 + j * 2, b0 + j * bstep, idesc, 1u);
+}
+// Partial "token-major" product over this CTA's hidden units: D[64 tok x 64] = X[64 x R] * W[R x 64], both
+// operands [R][64] tiles read MN-major (row = hidden unit), R = 64 nblk.
+__device__ __forceinline__ void mma_tok_partial(uint32_t tmem_d, uint32_t x_smem, uint32_t w_smem, int nblk) {
+  constexpr uint32_t idesc = umma_idesc_bf16(64, 64, true, true, false);
+  const uint32_t a0 = desc_lo(x_smem, TILE);
+  const uint32_t b0 = desc_lo(w_smem, TILE);
+  mma_issue_rt(tmem_d, a0, b0, idesc, 0u);
+#pragma unroll 1
+  for (int j = 1; j < 4 * nblk; ++j) mma_issue_rt(tmem_d, a0 + j * (2048u >> 4), b0 + j * (2048u >> 4), idesc, 1u);
+}
+
+// ---- Sum of a partial 64 x 64 fp32 tile (the TokMap fragment: 16 values per thread, plus kExtra
+// further per-thread values) over the CTAs of the cluster.  Every CTA ends with the same bits: the
+// additions are arranged as a butterfly over the rank bits, (own + [rank^1]) + ([rank^2] + [rank^3]),
+// which is the same expression in every CTA up to the commutativity of each addition.
+//
+// Exchange area per CTA: 2 buffers x (kC - 1) slots x kV4 x 256 float4 (slot s holds the values of
+// rank ^ (s + 1)), with one mbarrier per buffer counting (kC - 1) x 8 arrivals (one per warp and
+// peer).  Successive reductions alternate between the buffers.  That is enough: a CTA sends reduction
+// n + 2 only after it has received reduction n + 1 from every warp of every peer, and a peer's warp
+// sends n + 1 only after it has read its part of buffer n.
+template <int kC, int kV4>
+struct ClusterSum {
+  uint8_t* bufp;         // the exchange area (this CTA's shared memory)
+  uint64_t* bars;        // [2]
+  uint32_t n;            // reductions done
+  uint32_t rank;
+  volatile uint32_t* abort_flag;
+  uint64_t limit;
+
+  static constexpr uint32_t kSlotBytes = kV4 * 4096u;
+  static constexpr uint32_t kBufBytes = (kC - 1) * kSlotBytes;
+  static constexpr uint32_t kBytes = 2 * kBufBytes;
+  static constexpr uint32_t kArrivals = (kC - 1) * 8;
+
+  // v: kV4 * 4 floats.  Returns with v summed over the cluster.
+  __device__ __forceinline__ void run(float (&v)[kV4 * 4], int tid, int lane) {
+    const uint32_t b = n & 1u, par = (n >> 1) & 1u;
+    ++n;
+    const uint32_t boff = b * kBufBytes + static_cast<uint32_t>(tid) * 16u;
+    const uint32_t base = smem_u32(bufp) + boff;
+#pragma unroll
+    for (int s = 0; s < kC - 1; ++s) {
+      const uint32_t peer = rank ^ static_cast<uint32_t>(s + 1);
+      // at the peer, this CTA is rank ^ (s + 1) as well: the slot index is the same on both sides
+      const uint32_t dst = mapa(base + s * kSlotBytes, peer);
+#pragma unroll
+      for (int j = 0; j < kV4; ++j) st_cluster_f4(dst + j * 4096u, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    }
+    __syncwarp();
+    if (lane == 0) {
+      const uint32_t ba = smem_u32(&bars[b]);
+#pragma unroll
+      for (int s = 0; s < kC - 1; ++s) mbar_arrive_cluster(mapa(ba, rank ^ static_cast<uint32_t>(s + 1)));
+    }
+    mbar_wait_cl(&bars[b], par, abort_flag, limit, kC);
+    const float4* src = reinterpret_cast<const float4*>(bufp + boff);
+    if constexpr (kC == 2) {
+#pragma unroll
+      for (int j = 0; j < kV4; ++j) {
+        const float4 p = src[j * 256];
+        v[4 * j] += p.x; v[4 * j + 1] += p.y; v[4 * j + 2] += p.z; v[4 * j + 3] += p.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < kV4; ++j) {
+        const float4 p1 = src[j * 256];
+        const float4 p2 = src[(kSlotBytes / 16) + j * 256];
+        const float4 p3 = src[2 * (kSlotBytes / 16) + j * 256];
+        v[4 * j] = (v[4 * j] + p1.x) + (p2.x + p3.x);
+        v[4 * j + 1] = (v[4 * j + 1] + p1.y) + (p2.y + p3.y);
+        v[4 * j + 2] = (v[4 * j + 2] + p1.z) + (p2.z + p3.z);
+        v[4 * j + 3] = (v[4 * j + 3] + p1.w) + (p2.w + p3.w);
+      }
+    }
+  }
+};
+
+}  // namespace tttcl

@@ -25,6 +25,8 @@
 //
 // All waits are bounded (see sm100_ptx.cuh); on expiry the CTA reports through the status
 // word, drains its own copies, frees its tensor memory and returns.
+#include <mutex>
+
 #include "ttt_device.cuh"
 #include "ttt_internal.h"
 
@@ -79,6 +81,7 @@ struct FwdParams {
   float* W2f;
   float* b2f;
   int H, NC, cgs, nck;
+  int drop_load;            // test only: mini-batch whose loads stream 0 never issues (-1: none)
   uint32_t* status;
   uint64_t wait_limit_ns;
 };
@@ -126,9 +129,11 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   float* sBeta = reinterpret_cast<float*>(smem + OFF_BETA);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + OFF_BAR);   // [kStages]
   uint64_t* mma_bar = full + kStages;
+  uint64_t* drain_bar = mma_bar + 1;        // abort path only
   float* sXch = reinterpret_cast<float*>(smem + OFF_XCH);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_MISC);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + OFF_MISC + 4);
+  volatile uint32_t* never_flag = reinterpret_cast<volatile uint32_t*>(smem + OFF_MISC + 8);   // stays 0
 
   const uint64_t limit = p.wait_limit_ns;
   const int NC = p.NC;
@@ -136,8 +141,10 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) mbar_init(&full[s], 1);
     mbar_init(mma_bar, 4);
+    mbar_init(drain_bar, 4);
     fence_mbar_init();
     *abort_flag = 0;
+    *never_flag = 0;
     prefetch_tmap(&tmQ);
     prefetch_tmap(&tmK);
     prefetch_tmap(&tmV);
@@ -158,6 +165,7 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const uint32_t tmem = *tmem_slot;
 
   auto issue_loads = [&](int i) {   // thread 0 only
+    if (i == p.drop_load && stream_id == 0) return;
     const int s = i % kStages;
     const int row0 = static_cast<int>((stream_id * NC + i) * 64);
     mbar_expect_tx(&full[s], 3 * TILE + 128);
@@ -261,8 +269,6 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const long ckc = stream_id * p.nck + it / p.cgs;
     float* ckW1 = p.W1c + ckc * (64 * 256);
     float* ckW2 = p.W2c + ckc * (256 * 64);
-    if (tid == 0) tma_wait_group_read<0>();   // previous Out tile has left shared memory
-
     mbar_wait_bounded(&full[s], (it / kStages) & 1, abort_flag, limit);
 
     // ---- MMA1: Z1^T = W1^T K^T
@@ -444,6 +450,9 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         st_chunk(sX2, hrow, half * 4 + c, g);
       }
     }
+    // the Out tile stored earlier has long left shared memory: confirmed here, off the critical path,
+    // before the barrier after which the tile is written again
+    if (tid == 0) tma_wait_group_read<0>();
     publish();
 
     // ---- MMA6: Z2b = X2b W2
@@ -496,15 +505,24 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     store_state(p.W1f + stream_id * (64 * 256), p.b1f + stream_id * 256, p.W2f + stream_id * (256 * 64),
                 p.b2f + stream_id * 64);
   }
-  if (tid == 0) {
-    tma_wait_group<0>();
-    if (aborted) {
-      // wait (bounded) for our own loads still in flight before the CTA's shared memory goes away
-      for (int j = it + 1; j < loads_issued; ++j)
-        mbar_wait_bounded(&full[j % kStages], (j / kStages) & 1, abort_flag, limit);
+  if (aborted) {
+    // everything this CTA still has in flight is waited for (bounded, not cut short by the abort flag)
+    // before its shared and tensor memory go away: the tensor-core work of the four issuers ...
+    if (warp < 4) {
+      if (elect_one()) umma_commit(drain_bar);
+      __syncwarp();
+    }
+    if (tid == 0) {
+      mbar_wait_bounded(drain_bar, 0, never_flag, limit);
+      // ... and its own loads
+      for (int j = it; j < loads_issued; ++j) {
+        if (j == p.drop_load && stream_id == 0) continue;
+        mbar_wait_bounded(&full[j % kStages], (j / kStages) & 1, never_flag, limit);
+      }
       atomicExch(p.status, static_cast<uint32_t>(TTT_B200_ERR_TIMEOUT));
     }
   }
+  if (tid == 0) tma_wait_group<0>();
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, TM_COLS);
@@ -512,7 +530,8 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
 }  // namespace
 
-int ttt_launch_forward(const ttt_b200_fwd_args* a, cudaStream_t stream, uint32_t* status, uint64_t limit_ns) {
+int ttt_launch_forward(const ttt_b200_fwd_args* a, cudaStream_t stream, uint32_t* status, uint64_t limit_ns,
+                       int drop_load) {
   const uint64_t rows = static_cast<uint64_t>(a->B) * a->H * a->NC * 64;
   CUtensorMap tmQ, tmK, tmV, tmOut;
   if (int rc = ttt_make_tile_map(&tmQ, a->XQ, rows)) return rc;
@@ -529,16 +548,18 @@ int ttt_launch_forward(const ttt_b200_fwd_args* a, cudaStream_t stream, uint32_t
   p.W1f = want_final ? a->W1_final : nullptr;
   p.b1f = a->b1_final; p.W2f = a->W2_final; p.b2f = a->b2_final;
   p.H = a->H; p.NC = a->NC; p.cgs = a->checkpoint_group_size; p.nck = a->num_checkpoints;
+  p.drop_load = drop_load;
   p.status = status;
   p.wait_limit_ns = limit_ns;
-  static bool attr_done[64] = {};
+  static std::once_flag once[64];
+  static cudaError_t attr_err[64];
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(ttt_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
-    if (dev >= 0 && dev < 64) attr_done[dev] = true;
-  }
+  if (dev < 0 || dev >= 64) return ttt_set_error(TTT_B200_ERR_LAUNCH, "device index out of range");
+  std::call_once(once[dev], [&] {
+    attr_err[dev] = cudaFuncSetAttribute(ttt_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  });
+  if (attr_err[dev] != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(attr_err[dev]));
   ttt_fwd_kernel<<<dim3(a->B * a->H), dim3(kThreads), SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmOut, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));

@@ -69,15 +69,24 @@ def _stream_ptr(device):
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
+def _flags(sync, cluster, lost_load=False):
+    """Flag word of the C ABI: bit 0 synchronise, bit 1 the failure-path test hook, bits 8..11 the number
+    of CTAs (1, 2 or 4) that share one stream (0 / None: chosen from B*H and the SM count)."""
+    cluster = 0 if cluster is None else int(cluster)
+    _check(cluster in (0, 1, 2, 4), "cluster must be None, 1, 2 or 4")
+    return (_lib.FLAG_SYNC if sync else 0) | (_lib.FLAG_TEST_LOST_LOAD if lost_load else 0) | (cluster << 8)
+
+
 def ttt_forward(XQ, XK, XV, last_eta, ttt_norm_weight, ttt_norm_bias, W1, b1, W2, b2,
                 W1_checkpoints, b1_checkpoints, W2_checkpoints, b2_checkpoints, Out,
-                checkpoint_group_size, *, final_state=None, sync=False):
+                checkpoint_group_size, *, final_state=None, sync=False, cluster=None, _lost_load=False):
     """TTT-MLP forward over the whole sequence; writes `Out` and the state checkpoints.
 
     Positional arguments: exactly the reference's (kernels/ttt/ttt.cu:594-611).
     Keyword-only extras (not in the reference): `final_state` = (W1, b1, W2, b2) fp32 tensors
     that receive the state after the last mini-batch; `sync` blocks until the result is ready
-    and raises on a device-side failure.
+    and raises on a device-side failure; `cluster` forces how many CTAs share one (batch, head)
+    stream (1, 2 or 4; default: chosen from B*H and the GPU's SM count).
     """
     lib = _lib.lib()
     B, H, NC, cgs, n = _dims(XQ, checkpoint_group_size, W1_checkpoints)
@@ -112,7 +121,7 @@ def ttt_forward(XQ, XK, XV, last_eta, ttt_norm_weight, ttt_norm_bias, W1, b1, W2
             _chk_tensor(t, name, f32, shp, dev)
             setattr(a, name, t.data_ptr())
     a.B, a.H, a.NC, a.checkpoint_group_size, a.num_checkpoints = B, H, NC, cgs, n
-    a.flags = _lib.FLAG_SYNC if sync else 0
+    a.flags = _flags(sync, cluster, _lost_load)
     with torch.cuda.device(dev):
         rc = lib.ttt_b200_forward(ctypes.byref(a), _stream_ptr(dev))
     if rc != 0:
@@ -129,7 +138,7 @@ def ttt_backward(XQ, XK, XV, last_eta, ttt_norm_weight, ttt_norm_bias,
                  grad_L_W1_last, grad_L_b1_last, grad_L_W2_last, grad_L_b2_last, grad_L_XQW_mini_batch,
                  grad_L_ttt_norm_weight, grad_L_ttt_norm_bias, grad_L_W1_init, grad_L_b1_init,
                  grad_L_W2_init, grad_L_b2_init, grad_L_last_eta, grad_L_XQ, grad_L_XK, grad_L_XV,
-                 checkpoint_group_size, *, sync=False):
+                 checkpoint_group_size, *, sync=False, cluster=None, _lost_load=False):
     """TTT-MLP backward with per-checkpoint-group rematerialisation.
 
     Positional arguments: exactly the reference's 42 tensors + int
@@ -176,7 +185,7 @@ def ttt_backward(XQ, XK, XV, last_eta, ttt_norm_weight, ttt_norm_bias,
             _chk_tensor(t, name, dt, shp, dev)
         setattr(a, name, t.data_ptr())
     a.B, a.H, a.NC, a.checkpoint_group_size, a.num_checkpoints = B, H, NC, cgs, n
-    a.flags = _lib.FLAG_SYNC if sync else 0
+    a.flags = _flags(sync, cluster, _lost_load)
     with torch.cuda.device(dev):
         rc = lib.ttt_b200_backward(ctypes.byref(a), _stream_ptr(dev))
     if rc != 0:
