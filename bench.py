@@ -1,22 +1,25 @@
 #!/usr/bin/env python
 """Benchmark of the TTT-MLP forward + backward path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1|c3|c4|c0|small|prof]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload c2|c1|c3|c4|c0|small|prof|glue] [--scaling strong|weak] [--cluster 0|1|2|4]
 
-One "step" = one forward + one backward over one batch of synthetic input of the named
-workload (default: the forward+backward configuration, B=4 H=32 seq 8192 cgs 8 per GPU).
-With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank processes its
-own batch shard of that size (weak scaling) and the per-head norm gradients are summed across
-ranks with one NCCL all-reduce, the only exchange the path has.
+One "step" = one forward + one backward over one batch of synthetic input of the named workload
+(default: the forward+backward configuration, B=4 H=32 seq 8192 cgs 8).  With N > 1 (launched by
+torch.distributed.run, one rank per GPU) the (batch x head) streams of that ONE problem are
+partitioned across the ranks (strong scaling: 128 / N streams per GPU) and the per-head norm gradients
+are summed with one NCCL all-reduce, the only exchange the path has; the same run then also times N
+replicas of the whole problem (weak scaling) and reports that number under "weak".
 
-Prints ONE JSON line (rank 0).  `value` is device-timed with the inputs resident in HBM;
-`e2e` is measured through the public operator API with pinned host buffers, host<->device
-copies inside the timed region: every step copies all of its inputs in and all of its results
-out; the independent (batch element, head range) chunks run on their own CUDA streams and are
-not joined between steps, so a step's copies overlap the neighbouring steps' kernels.  `--impl reference` times the CPU oracle (the PyTorch-eager
-restatement of the reference's own PyTorch functions; the reference's CUDA kernels are
-sm_90a-only and cannot run on this GPU) on the host cores on a bounded sample of the same
-workload.
+Prints ONE JSON line (rank 0).  `value` is device-timed with the inputs resident in HBM; `e2e` is
+measured through the public operator API with pinned host buffers, host<->device copies inside the
+timed region: every step copies all of its inputs in and all of its results out; the independent
+(batch element, head range) chunks run on their own CUDA streams and are not joined between steps, so
+a step's copies overlap the neighbouring steps' kernels.  `--impl reference` times the CPU oracle (the
+PyTorch-eager restatement of the reference's own PyTorch functions; the reference's CUDA kernels are
+sm_90a-only and cannot run on this GPU) on the host cores on a bounded sample of the same workload.
+`--workload glue` times the layer-side kernels around the operator (eta gate, token layout transforms,
+output norm) instead; they are HBM-bound.
 """
 import argparse
 import json
@@ -49,6 +52,11 @@ STATE_BYTES = 132352                  # fp32 W1 + b1 + W2 + b2 of one (b,h)
 # proportion to the number of (stream, mini-batch) pairs, so a full-size launch is scaled from it.
 NCU_BWD_DRAM_BYTES_PER_MB = (583610880 + 585072384) / 2048
 NCU_FWD_DRAM_BYTES_PER_MB = (67620096 + 8762112) / 2048
+# Scratch bytes the backward asks for per (stream, mini-batch): the recompute writes seven [256][64] bf16 images
+# (X2, Z1, dl/dZ1, gelu'(Z1_bar), X2_bar, W1^T, W2), three [64][64] bf16 tiles and two fp32[64] vectors; the sweep
+# reads the same back, X2 twice.
+SCRATCH_WRITE_PER_MB = 7 * 32768 + 3 * 8192 + 512
+SCRATCH_READ_PER_MB = 8 * 32768 + 3 * 8192 + 512
 
 
 def algorithmic_bytes(B, H, NC, cgs):
@@ -123,23 +131,25 @@ def make_host_inputs(B, H, NC, seed):
 
 
 class DeviceStep:
-    """Device-resident buffers and the fwd+bwd step through the operator API."""
+    """Device-resident buffers of one rank's streams and the fwd+bwd step through the operator API."""
 
-    def __init__(self, host, cgs, dev):
+    def __init__(self, host, cgs, dev, cluster=None, heads=None, total_heads=None):
         from ttt_tk_b200.buffers import alloc_backward_buffers, GRAD_NAMES
         self.GRADS = GRAD_NAMES
         self.cgs = cgs
         self.dev = dev
+        self.cluster = cluster
         B, H, NC = host["XQ"].shape[:3]
         self.B, self.H, self.NC = B, H, NC
+        self.heads = (0, H) if heads is None else heads          # this rank's heads within the whole problem
+        self.total_heads = H if total_heads is None else total_heads
         n = -(-NC // cgs)
         self.t = {k: v.to(dev) for k, v in host.items()}
         self.t["last_eta5"] = self.t["last_eta"].unsqueeze(-1).contiguous()
         self.ck = [torch.empty(B, H, n, *s, device=dev) for s in ((64, 256), (1, 256), (256, 64), (1, 64))]
         self.out = torch.empty_like(self.t["XQ"])
         self.scratch, self.outs = alloc_backward_buffers(B, H, NC, cgs, device=dev, fill=0.0)
-        self.norm_grads = torch.zeros(2, H, 64, device=dev)
-        self.ev = None
+        self.norm_grads = None
 
     def forward(self, sl=(slice(None), slice(None)), norm=None):
         """Forward over the streams `sl` = (batch element b:b+1 or all, head range): such a slice of a
@@ -150,7 +160,7 @@ class DeviceStep:
         nw, nb = norm if norm is not None else (t["ttt_norm_weight"][hs], t["ttt_norm_bias"][hs])
         ttt_forward(t["XQ"][sl], t["XK"][sl], t["XV"][sl], t["last_eta"][sl], nw,
                     nb, t["W1"][sl], t["b1"][sl], t["W2"][sl], t["b2"][sl],
-                    *[c[sl] for c in self.ck], self.out[sl], self.cgs)
+                    *[c[sl] for c in self.ck], self.out[sl], self.cgs, cluster=self.cluster)
 
     def backward(self, sl=(slice(None), slice(None)), norm=None):
         from ttt_tk_b200 import ttt_backward
@@ -162,23 +172,20 @@ class DeviceStep:
                      *[x[sl] for x in self.scratch],
                      t["grad_L_W1_last"][sl], t["grad_L_b1_last"][sl], t["grad_L_W2_last"][sl],
                      t["grad_L_b2_last"][sl], t["grad_L_XQW_mini_batch"][sl],
-                     *[self.outs[k][sl] for k in self.GRADS], self.cgs)
+                     *[self.outs[k][sl] for k in self.GRADS], self.cgs, cluster=self.cluster)
 
-    def reduce_norm_grads(self, world):
+    def reduce_norm_grads(self):
         # the caller-side batch sum the operator's layout asks for, then the one exchange of the path
         from ttt_tk_b200.dist import reduce_norm_grads
-        self.norm_grads = reduce_norm_grads(self.outs["grad_L_ttt_norm_weight"], self.outs["grad_L_ttt_norm_bias"])
+        self.norm_grads = reduce_norm_grads(self.outs["grad_L_ttt_norm_weight"], self.outs["grad_L_ttt_norm_bias"],
+                                            heads=self.heads, total_heads=self.total_heads)
 
 
-def run_ours(args, rank, world, local_rank):
+def timed_steps(step, K, W, world, dev):
+    """W warm-up steps, then K steps timed with CUDA events between a barrier + synchronize on both sides.
+    Returns (total ms, mean forward ms, mean backward ms), each the maximum over the ranks."""
     import torch.distributed as dist
     from ttt_tk_b200 import take_status
-    B, H, NC, cgs, desc = WORKLOADS[args.workload]
-    dev = torch.device("cuda", local_rank)
-    torch.cuda.set_device(dev)
-    host = make_host_inputs(B, H, NC, seed=rank)
-    step = DeviceStep(host, cgs, dev)
-    K, W = args.steps, args.warmup
 
     def barrier():
         if world > 1:
@@ -188,13 +195,9 @@ def run_ours(args, rank, world, local_rank):
     for _ in range(W):
         step.forward()
         step.backward()
-        step.reduce_norm_grads(world)
+        step.reduce_norm_grads()
     barrier()
     assert take_status() == 0, "device-side wait ran out during warm-up"
-
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
     t_end = torch.cuda.Event(enable_timing=True)
     barrier()
@@ -204,18 +207,57 @@ def run_ours(args, rank, world, local_rank):
         ev[k][1].record()
         step.backward()
         ev[k][2].record()
-        step.reduce_norm_grads(world)
+        step.reduce_norm_grads()
     t_end.record()
     barrier()
-    total_ms = ev[0][0].elapsed_time(t_end)
-    clocks = sampler.stop() if rank == 0 else None
     assert take_status() == 0, "device-side wait ran out during the timed region"
+    total_ms = ev[0][0].elapsed_time(t_end)
     fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
     bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
     tt = torch.tensor([total_ms, fwd_ms, bwd_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-    total_ms, fwd_ms, bwd_ms = tt.tolist()
+    return tt.tolist()
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+    from ttt_tk_b200 import _lib
+    from ttt_tk_b200.dist import shard_tensors
+    B, H, NC, cgs, desc = WORKLOADS[args.workload]
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    strong = args.scaling == "strong"
+    cluster = args.cluster or None
+    K, W = args.steps, args.warmup
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- the measured arm: ONE problem, its (batch x head) streams partitioned over the ranks (strong), or
+    # one whole problem per rank (weak)
+    if strong:
+        full = make_host_inputs(B, H, NC, seed=0)
+        host, (b0, b1, h0, h1) = shard_tensors(full, rank, world)
+        del full
+        step = DeviceStep(host, cgs, dev, cluster, heads=(h0, h1), total_heads=H)
+    else:
+        host = make_host_inputs(B, H, NC, seed=rank)
+        b0, b1, h0, h1 = 0, B, 0, H
+        step = DeviceStep(host, cgs, dev, cluster)
+    Bl, Hl = b1 - b0, h1 - h0
+    lib = _lib.lib()
+    cl_used = cluster or lib.ttt_b200_pick_cluster(Bl * Hl)
+
+    sampler = ClockSampler(local_rank)
+    # warm-up happens inside timed_steps; the sampler is started just before so that most of its samples
+    # fall into the timed region (the first one, taken at idle, is dropped)
+    if rank == 0:
+        sampler.start()
+    total_ms, fwd_ms, bwd_ms = timed_steps(step, K, W, world, dev)
+    clocks = sampler.stop() if rank == 0 else None
 
     # ---- end to end through the operator API with pinned host buffers
     e2e_steps = max(1, min(K, args.e2e_steps))
@@ -234,12 +276,15 @@ def run_ours(args, rank, world, local_rank):
     # next batch): both copy directions and the kernels stay busy.  Every step still copies all of its
     # inputs in and all of its results out, and the norm-gradient batch sum of a step is taken before
     # the next step's backward may overwrite its addends.
-    hsplit = max(1, min(args.e2e_head_chunks, H))
-    hb = [(i * H // hsplit, (i + 1) * H // hsplit) for i in range(hsplit)]
-    bpc = max(1, min(args.e2e_batch_per_chunk, B))
-    chunks = [(slice(b, min(b + bpc, B)), slice(h0, h1)) for b in range(0, B, bpc) for (h0, h1) in hb]
+    hsplit = max(1, min(args.e2e_head_chunks, Hl))
+    hb = [(i * Hl // hsplit, (i + 1) * Hl // hsplit) for i in range(hsplit)]
+    bpc = max(1, min(args.e2e_batch_per_chunk, Bl))
+    if Bl == 1 and hsplit == 1 and Hl >= 2:
+        hb = [(0, Hl // 2), (Hl // 2, Hl)]           # one batch element per rank: two head ranges keep two chunks in flight
+        hsplit = 2
     if hsplit > 1:
-        assert bpc == 1, "a head range of several batch elements is not contiguous"
+        bpc = 1                                      # a head range of several batch elements is not contiguous
+    chunks = [(slice(b, min(b + bpc, Bl)), slice(x0, x1)) for b in range(0, Bl, bpc) for (x0, x1) in hb]
     streams = [torch.cuda.Stream(device=dev) for _ in chunks]        # copies in + kernels of a chunk
     out_streams = [torch.cuda.Stream(device=dev) for _ in chunks]    # copies out of a chunk
     shared_keys = ["ttt_norm_weight", "ttt_norm_bias"]
@@ -282,70 +327,130 @@ def run_ours(args, rank, world, local_rank):
                     copied_out[i].record(so)
             for ev_c in done:
                 main.wait_event(ev_c)
-            step.reduce_norm_grads(world)
+            step.reduce_norm_grads()
             reduced = torch.cuda.Event()
             reduced.record(main)
         for so in out_streams:
             main.wait_stream(so)
 
+    def timed(fn):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        t0 = time.perf_counter()
+        fn()
+        host_ms = (time.perf_counter() - t0) * 1e3
+        e1.record()
+        barrier()
+        et = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(et, op=dist.ReduceOp.MAX)
+        return et.item(), host_ms
+
     e2e_steps_run(2)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    t_issue = time.perf_counter()
-    e2e_steps_run(e2e_steps)
-    t_issue = (time.perf_counter() - t_issue) * 1e3 / e2e_steps      # host time spent queueing one step
-    e1.record()
-    barrier()
-    et = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(et, op=dist.ReduceOp.MAX)
-    e2e_ms = et.item() / e2e_steps
+    e2e_total, issue_total = timed(lambda: e2e_steps_run(e2e_steps))
+    e2e_ms, t_issue = e2e_total / e2e_steps, issue_total / e2e_steps
+
+    # each copy direction alone, all ranks at once: what the host side gives one rank when the others copy too
+    def copy_in():
+        for k, v in pin_in.items():
+            step.t[k].copy_(v, non_blocking=True)
+
+    def copy_out():
+        for k, v in out_t.items():
+            pin_out[k].copy_(v, non_blocking=True)
+
+    copy_in(); copy_out()
+    h2d_ms, _ = timed(copy_in)
+    d2h_ms, _ = timed(copy_out)
+
+    # ---- N replicas of the whole problem (weak scaling), as an extra number of the same run
+    weak = None
+    if strong and world > 1:
+        del step, pin_in, pin_out, out_t, norm_dev
+        torch.cuda.empty_cache()
+        wstep = DeviceStep(make_host_inputs(B, H, NC, seed=rank), cgs, dev, cluster)
+        wK = max(2, K // 2)
+        w_total, w_fwd, w_bwd = timed_steps(wstep, wK, 3, world, dev)
+        weak = {"value": world * B * NC * 64 / (w_total / wK * 1e-3), "unit": "tokens/s", "ms_per_step": w_total / wK,
+                "steps": wK, "streams_per_gpu": B * H, "note": "one whole problem per GPU (replicas), same run"}
 
     if rank != 0:
         return None
     pk, pk_src = peaks()
-    tokens_per_step = world * B * NC * 64
+    tokens_per_step = (B if strong else world * B) * NC * 64
     ms_per_step = total_ms / K
-    th = B * H * NC * 64                    # token-heads per GPU per step
+    th = Bl * Hl * NC * 64                  # token-heads per GPU per step
     fwd_flop, bwd_flop = th * 32768 * FWD_U, th * 32768 * BWD_U
-    fwd_bytes, bwd_bytes = algorithmic_bytes(B, H, NC, cgs)
-    peak_tf = pk.get("bf16_tflops_sustained", pk["bf16_tflops"])
+    fwd_bytes, bwd_bytes = algorithmic_bytes(Bl, Hl, NC, cgs)
+    burst, sustained = pk["bf16_tflops"], pk.get("bf16_tflops_sustained", pk["bf16_tflops"])
+    # A kernel timed inside a short region at full clock is held against the burst figure; one that ran
+    # under the power cap (clock well below maximum) or for seconds, against the sustained one.
+    at_max = bool(clocks and clocks.get("sm_mhz") and clocks.get("sm_max_mhz")
+                  and clocks["sm_mhz"] >= 0.9 * clocks["sm_max_mhz"])
+    use_burst = at_max and total_ms < 1000.0
+    peak_tf = burst if use_burst else sustained
     bwd_tf = bwd_flop / (bwd_ms * 1e-3) / 1e12
+    both_tf = (fwd_flop + bwd_flop) / ((fwd_ms + bwd_ms) * 1e-3) / 1e12
+    n = -(-NC // cgs)
+    remat_bytes = Bl * Hl * (2 * n * STATE_BYTES + NC * (SCRATCH_WRITE_PER_MB + SCRATCH_READ_PER_MB))
+    bwd_kernel = "ttt_bwd_kernel" if cl_used == 1 else f"ttt_bwd_cluster_kernel<{cl_used}>"
     res = {
         "metric": "ttt_mlp_fwd_bwd_tokens_per_s", "value": tokens_per_step / (ms_per_step * 1e-3),
         "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_per_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": desc, "B_per_gpu": B, "H": H, "seq_len": NC * 64, "checkpoint_group_size": cgs,
-                   "parallelism": f"(batch x head) streams sharded, dp{world}",
-                   "l2": "working set per step (~1.7 GB at c2) exceeds the 126 MB L2; no explicit flush"},
+        "config": {"workload": desc, "B": B, "H": H, "seq_len": NC * 64, "checkpoint_group_size": cgs,
+                   "parallelism": (f"one problem, (batch x head) streams partitioned over {world} GPU(s): "
+                                   f"{Bl} x {Hl} = {Bl * Hl} streams per GPU" if strong else
+                                   f"one whole problem per GPU (replicas), {world} GPU(s)"),
+                   "ctas_per_stream": cl_used,
+                   "l2": "working set per step (~1.7 GB at c2 on one GPU) exceeds the 126 MB L2; no explicit flush"},
         "kernels": {"fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
                     "fwd_tflops": fwd_flop / (fwd_ms * 1e-3) / 1e12, "bwd_tflops": bwd_tf,
-                    "fwd_bwd_frac_of_bf16_peak": (fwd_flop + bwd_flop) / ((fwd_ms + bwd_ms) * 1e-3) / 1e12 / peak_tf,
+                    "fwd_bwd_tflops": both_tf,
+                    "fwd_bwd_frac_of_bf16_burst_peak": both_tf / burst,
+                    "fwd_bwd_frac_of_bf16_sustained_peak": both_tf / sustained,
                     "fwd_algorithmic_gbs": fwd_bytes / (fwd_ms * 1e-3) / 1e9,
                     "bwd_algorithmic_gbs": bwd_bytes / (bwd_ms * 1e-3) / 1e9,
-                    "streams_per_gpu": B * H},
-        "roofline": {"kernel": "ttt_bwd_kernel", "bound": "tensor", "achieved": bwd_tf, "peak": peak_tf,
+                    "streams_per_gpu": Bl * Hl, "ctas_per_stream": cl_used},
+        # checkpoint + recompute scratch traffic: checkpoints written by the forward and read by the backward,
+        # scratch slots written by the recompute and read back by the sweep (bytes the kernels ask for)
+        "remat_traffic": {"bytes_per_step": remat_bytes,
+                          "hbm_gbs_achieved": remat_bytes / ((fwd_ms + bwd_ms) * 1e-3) / 1e9,
+                          "frac_of_hbm_peak": remat_bytes / ((fwd_ms + bwd_ms) * 1e-3) / 1e9 / pk["hbm_gbs"],
+                          "dram_bytes_measured_bwd": NCU_BWD_DRAM_BYTES_PER_MB * Bl * Hl * NC,
+                          "dram_gbs_measured_bwd": NCU_BWD_DRAM_BYTES_PER_MB * Bl * Hl * NC / (bwd_ms * 1e-3) / 1e9},
+        "roofline": {"kernel": bwd_kernel, "bound": "tensor", "achieved": bwd_tf, "peak": peak_tf,
                      "unit": "TFLOP/s", "frac": bwd_tf / peak_tf,
-                     "traffic": NCU_BWD_DRAM_BYTES_PER_MB * B * H * NC,
-                     "traffic_note": "bytes per launch, scaled from an ncu capture of a smaller launch by (streams x mini-batches)",
-                     "peak_source": f"{pk_src} (sustained cuBLAS bf16: kernel timed inside a long step)"},
+                     "frac_of_burst": bwd_tf / burst, "frac_of_sustained": bwd_tf / sustained,
+                     "traffic": NCU_BWD_DRAM_BYTES_PER_MB * Bl * Hl * NC,
+                     "traffic_note": "bytes per launch, scaled from an ncu capture of a smaller launch of the "
+                                     "one-CTA kernel by (streams x mini-batches)",
+                     "peak_source": f"{pk_src}, " + ("burst cuBLAS bf16 (timed region under 1 s at full clock)" if use_burst
+                                                     else "sustained cuBLAS bf16 (clock below maximum or a long region)")},
         "e2e": {"value": tokens_per_step / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                 "host_issue_ms_per_step": t_issue,
+                "h2d_gbs_alone_per_rank": h2d / (h2d_ms * 1e-3) / 1e9,
+                "d2h_gbs_alone_per_rank": d2h / (d2h_ms * 1e-3) / 1e9,
+                "copy_note": "bytes are per rank; the *_alone figures time one direction with all ranks copying at once "
+                             "(slowest rank), i.e. what the host's PCIe / memory fabric gives each rank",
                 "pipelining": f"{len(chunks)} (batch element, head range) chunks, each with a stream for copies in + "
                               "kernels and one for copies out, not joined between steps: copies in, kernels and copies out "
                               "of neighbouring steps overlap"},
         "gpu_launches": 2 * K,
         "clocks": clocks,
     }
+    if weak is not None:
+        res["weak"] = weak
     return res
 
 
-def cpu_oracle_rate(sample_B, sample_H, NC, cgs, H_full, reps, threads):
+def cpu_oracle_rate(sample_B, sample_H, NC, cgs, H_full, reps, threads, warmup=1):
     """tokens/s of the CPU oracle (fwd + hand-derived bwd) on a slice of the workload.
-    A token spans all H_full heads, so a slice with sample_H heads counts sample_H / H_full of it."""
+    A token spans all H_full heads, so a slice with sample_H heads counts sample_H / H_full of it.
+    Returns (tokens/s from the median repetition, median seconds, mean seconds)."""
     from oracle import ttt_mlp as orc
     torch.set_num_threads(threads)
     d = orc.make_inputs(sample_B, sample_H, NC, seed=0, backward=True)
@@ -359,7 +464,8 @@ def cpu_oracle_rate(sample_B, sample_H, NC, cgs, H_full, reps, threads):
                          d["grad_L_XQW_mini_batch"], cgs)
 
     with torch.no_grad():
-        once()
+        for _ in range(warmup):
+            once()
         ts = []
         for _ in range(reps):
             t0 = time.perf_counter()
@@ -367,25 +473,33 @@ def cpu_oracle_rate(sample_B, sample_H, NC, cgs, H_full, reps, threads):
             ts.append(time.perf_counter() - t0)
     sec = statistics.median(ts)
     tokens = sample_B * NC * 64 * (sample_H / H_full)
-    return tokens / sec, sec
+    return tokens / sec, sec, statistics.mean(ts)
 
 
 def run_reference(args, rank, world):
-    """The reference arm: its own CPU statement of the path (the oracle), all host threads."""
+    """The reference arm: its own CPU statement of the path (the oracle), all host threads.  One step is
+    one forward + backward over a bounded sample of the workload (one batch element, all heads when that
+    fits the time budget, fewer heads otherwise); exactly --warmup + --steps of them are run."""
     if rank != 0:
         return None
     B, H, NC, cgs, desc = WORKLOADS[args.workload]
     threads = os.cpu_count() or 1
-    sB, sH = 1, H          # one batch element, all heads: enough parallel work for every host core
-    K, W = args.steps, args.warmup
-    rate, sec = cpu_oracle_rate(sB, sH, NC, cgs, H, reps=max(1, min(K, 5)), threads=threads)
-    sample = (f"PyTorch-eager fp32 oracle, fwd + hand-derived bwd, slice B={sB} H={sH} of the workload's "
-              f"B={B} H={H} at full sequence (NC={NC}); tokens/s = slice token-heads/s / {H}")
+    K, W = max(1, args.steps), max(0, args.warmup)
+    # size the sample so that K + W steps take about two minutes: one token-head costs about 25 us of this
+    # oracle on 16 cores (measured: 5-6 k tokens/s at H = 32)
+    budget_s = 120.0
+    est_per_head = NC * 64 * 25e-6 * (16.0 / max(1, min(threads, 16)))
+    sH = int(max(1, min(H, budget_s / ((K + W) * est_per_head))))
+    sB = 1
+    rate, sec, mean_sec = cpu_oracle_rate(sB, sH, NC, cgs, H, reps=K, threads=threads, warmup=W)
+    sample = (f"PyTorch-eager fp32 oracle, fwd + hand-derived bwd; one step = the slice B={sB} H={sH} of the "
+              f"workload's B={B} H={H} at full sequence (NC={NC}); tokens/s = slice token-heads/s / {H}")
     return {
         "impl": "reference", "metric": "ttt_mlp_fwd_bwd_tokens_per_s", "value": rate, "unit": "tokens/s",
-        "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": sec * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": desc},
+        "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": mean_sec * 1e3, "higher_is_better": True,
+        "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": desc, "B": B, "H": H, "seq_len": NC * 64, "checkpoint_group_size": cgs,
+                   "sample_per_step": f"B={sB} H={sH} of B={B} H={H}"},
         "cpu_baseline": {"value": rate, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": rate, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -414,6 +528,10 @@ def main():
     ap.add_argument("--e2e-batch-per-chunk", type=int, default=2,
                     help="end-to-end step: batch elements per chunk (with --e2e-head-chunks 1)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
+                    help="N > 1: partition the one problem's streams over the ranks (strong), or one whole problem per rank")
+    ap.add_argument("--cluster", type=int, default=0, choices=[0, 1, 2, 4],
+                    help="CTAs per (batch, head) stream; 0 = the launcher's own choice")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -436,7 +554,7 @@ def main():
             B, H, NC, cgs, _ = WORKLOADS[args.workload]
             threads = os.cpu_count() or 1
             sB, sH = 1, H      # one batch element, all heads (about 10-20 s of CPU work in total)
-            rate, sec = cpu_oracle_rate(sB, sH, NC, cgs, H, reps=3, threads=threads)
+            rate, sec, _ = cpu_oracle_rate(sB, sH, NC, cgs, H, reps=3, threads=threads)
             res["cpu_baseline"] = {
                 "value": rate, "unit": "tokens/s", "cores": threads, "kind": "port",
                 "sample": (f"PyTorch-eager fp32 oracle, fwd + hand-derived bwd, slice B={sB} H={sH} at full "

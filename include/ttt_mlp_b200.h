@@ -165,8 +165,11 @@ int ttt_b200_backward(const ttt_b200_bwd_args* args, void* stream);
  *     shared-memory limit: make that first call before any stream capture begins.
  *   - All calls on a device share the array, which keeps the previous call's contents (nothing
  *     in it needs to start at zero); calls that overlap on the GPU race on it: serialise them.
- *   - A device-side wait that ran out (code 3) is reported only by calls with
- *     TTT_B200_FLAG_SYNC set; without the flag the call returns once the kernel is launched. */
+ *   - A device-side wait that ran out (code 3) is reported by the call itself when
+ *     TTT_B200_FLAG_SYNC is set; without the flag the call returns once the kernel is launched and
+ *     the condition stays recorded (no later launch clears it) until ttt_b200_take_status() is
+ *     called after the caller has synchronised.  The wait limit is TTT_B200_WAIT_LIMIT_MS, as for
+ *     the other entry points. */
 #define TTT_B200_NOALLOC_MAX_SLOTS 128
 typedef struct ttt_b200_bwd_noalloc_args {
   const void* XQ;                    /* bf16 [B,H,NC,64,64] */
@@ -211,6 +214,12 @@ int ttt_b200_take_status(void);
 /* Library / ABI version (major * 1000 + minor). */
 int ttt_b200_version(void);
 
+/* How many CTAs (1, 2 or 4) the launchers give each (batch, head) stream of a problem with `streams` = B*H
+ * streams on the current device when the flags leave the choice to them: the largest cluster size whose
+ * CTAs all fit on the GPU at once (TTT_B200_CLUSTER overrides).  The reference fixes the split at compile
+ * time (kernels/ttt/ttt.cu:11-12, kernels/ttt_backward/ttt.cu:12-16).  Returns -1 on error. */
+int ttt_b200_pick_cluster(int streams);
+
 /* Diagnostics (no counterpart in the reference): one CTA computes
  * D[M,N] = (+/-)A[M,K] * B[N,K]^T, `repeat` times accumulated, through the same shared-memory
  * descriptors, instruction descriptors and tensor-memory mapping as the operator kernels.
@@ -237,6 +246,24 @@ int ttt_b200_pack_tokens(const void* const* src, void* const* dst, int n_tensors
                          void* stream);
 int ttt_b200_unpack_tokens(const void* const* src, void* const* dst, int n_tensors, int B, int T, int H,
                            void* stream);
+
+/* Layer-side kernels around the operator (no counterpart in the reference, whose callers compute
+ * `last_eta` and post-process `XQW_batch` themselves: README.md:22-98).  Token-major tensors are a
+ * model's [B][T][H] / [B][T][H*64] activations, head-major ones the operator's [B][H][T] / [B][H][T][64].
+ * T a multiple of 64; B*T*H < 2^31; device pointers; stream-ordered, no synchronisation; TTT_B200_* codes.
+ *
+ * eta gate: last_eta[b][h][t] = scale * sigmoid(logits[b][t][h]), bf16 -> bf16 (H <= 256).  `scale` carries
+ * the base learning rate, the 1 / 64 of the head dimension and the last row's token weight.  Its
+ * backward: grad_logits[b][t][h] = grad_last_eta[b][h][t] * scale * s (1 - s), s = sigmoid(logits[b][t][h]). */
+int ttt_b200_eta_gate(const void* logits, void* last_eta, float scale, int B, int T, int H, void* stream);
+int ttt_b200_eta_gate_backward(const void* logits, const void* grad_last_eta, void* grad_logits, float scale, int B,
+                               int T, int H, void* stream);
+/* Output norm fused with the unpack: dst[b][t][:] = gamma * LayerNorm(src[b][:][t][:]) + beta over the H*64
+ * features of a token; src = the operator's Out, bf16 [B][H][T][64]; gamma, beta fp32 [H*64]; dst bf16
+ * [B][T][H*64]; statistics in fp32 (biased variance, eps inside the square root); H <= 64; pointers 16-byte
+ * aligned; out of place. */
+int ttt_b200_unpack_layernorm(const void* src, const float* gamma, const float* beta, void* dst, float eps, int B,
+                              int T, int H, void* stream);
 
 #ifdef __cplusplus
 }

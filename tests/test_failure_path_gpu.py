@@ -2,6 +2,9 @@
 runs out, the kernel reports code 3 through the status word and exits normally, and the very next
 operator call works."""
 import ctypes
+import os
+import subprocess
+import sys
 
 import pytest
 import torch
@@ -37,3 +40,15 @@ def test_bounded_wait_expires_and_context_survives():
 def test_wait_selftest_rejects_bad_limit():
     lib = _lib.lib()
     assert lib.ttt_b200_wait_selftest(0, None, None) == 1
+
+
+def test_operator_kernels_report_a_lost_load_and_the_context_survives():
+    """The abort paths of the operator kernels themselves (one CTA per stream and cluster-sharded): a
+    child process with a 5 ms wait limit launches each kernel with the test hook that withholds one
+    mini-batch's loads; see lost_load_child.py."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, TTT_B200_WAIT_LIMIT_MS="5", PYTHONPATH=root)
+    res = subprocess.run([sys.executable, os.path.join(root, "tests", "lost_load_child.py")], env=env, cwd=root,
+                         capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
+    assert "LOST_LOAD_OK" in res.stdout

@@ -51,15 +51,16 @@ def check(res, ref, keys_tol):
 @pytest.mark.parametrize("B,H,NC,cgs", [(1, 1, 1, 1), (1, 2, 3, 2), (2, 3, 8, 4), (1, 4, 32, 4)])
 def test_forward_matches_oracle(B, H, NC, cgs):
     d = orc.make_inputs(B, H, NC, seed=0)
+    # non-zero initial biases (the recipe's zeros would leave the bias gates comparing pure update noise)
+    g = torch.Generator().manual_seed(77)
+    d["b1"] = 0.02 * torch.randn(d["b1"].shape, generator=g)
+    d["b2"] = 0.02 * torch.randn(d["b2"].shape, generator=g)
     ref = orc.ttt_forward(d["XQ"], d["XK"], d["XV"], d["last_eta"], d["ttt_norm_weight"], d["ttt_norm_bias"],
                           d["W1"], d["b1"], d["W2"], d["b2"], cgs)
     res = run_forward(d, cgs, final=True)
     assert torch.isfinite(res["Out"]).all()
     check(res, ref, [("Out", TOL_OUT)] + [(k, TOL_STATE) for k in CK]
-          + [(k, TOL_STATE) for k in ("W1_final", "W2_final")])
-    # b1/b2 start at zero in this recipe: compare the final biases absolutely scaled by their norm
-    for k in ("b1_final", "b2_final"):
-        assert orc.rel_l2(res[k], ref[k]) <= 2e-2, k
+          + [(k, TOL_STATE) for k in ("W1_final", "b1_final", "W2_final", "b2_final")])
     # checkpoint 0 is the initial state, bit for bit
     assert torch.equal(res["W1_checkpoints"][:, :, 0], d["W1"])
     assert torch.equal(res["W2_checkpoints"][:, :, 0], d["W2"])

@@ -44,8 +44,8 @@ class BwdNoAllocArgs(ctypes.Structure):
 
 
 EXPORTS = ["ttt_b200_forward", "ttt_b200_backward", "ttt_b200_backward_noalloc", "ttt_b200_last_error", "ttt_b200_take_status",
-           "ttt_b200_version", "ttt_b200_umma_selftest", "ttt_b200_wait_selftest", "ttt_b200_pack_tokens",
-           "ttt_b200_unpack_tokens"]
+           "ttt_b200_version", "ttt_b200_pick_cluster", "ttt_b200_umma_selftest", "ttt_b200_wait_selftest", "ttt_b200_pack_tokens",
+           "ttt_b200_unpack_tokens", "ttt_b200_eta_gate", "ttt_b200_eta_gate_backward", "ttt_b200_unpack_layernorm"]
 
 FLAG_SYNC = 1
 FLAG_TEST_LOST_LOAD = 2
@@ -69,6 +69,8 @@ def load():
     lib.ttt_b200_take_status.restype = ctypes.c_int
     lib.ttt_b200_version.argtypes = []
     lib.ttt_b200_version.restype = ctypes.c_int
+    lib.ttt_b200_pick_cluster.argtypes = [ctypes.c_int]
+    lib.ttt_b200_pick_cluster.restype = ctypes.c_int
     lib.ttt_b200_umma_selftest.argtypes = [c_void_p, c_void_p, c_void_p] + [ctypes.c_int] * 7 + [c_void_p]
     lib.ttt_b200_umma_selftest.restype = ctypes.c_int
     lib.ttt_b200_wait_selftest.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_ulonglong), c_void_p]
@@ -77,6 +79,13 @@ def load():
         fn = getattr(lib, name)
         fn.argtypes = [ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p)] + [ctypes.c_int] * 4 + [c_void_p]
         fn.restype = ctypes.c_int
+    lib.ttt_b200_eta_gate.argtypes = [c_void_p, c_void_p, ctypes.c_float] + [ctypes.c_int] * 3 + [c_void_p]
+    lib.ttt_b200_eta_gate.restype = ctypes.c_int
+    lib.ttt_b200_eta_gate_backward.argtypes = [c_void_p, c_void_p, c_void_p, ctypes.c_float] + [ctypes.c_int] * 3 + [c_void_p]
+    lib.ttt_b200_eta_gate_backward.restype = ctypes.c_int
+    lib.ttt_b200_unpack_layernorm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_float] + \
+        [ctypes.c_int] * 3 + [c_void_p]
+    lib.ttt_b200_unpack_layernorm.restype = ctypes.c_int
     return lib
 
 

@@ -69,28 +69,6 @@ constexpr int kThreads = 256;
     __syncwarp();                   \
   }
 
-// Optional timeline of CTA 0 (compile with -DTTT_STAMPS): one thread records the global timer
-// whenever a wait returns and when a publish step begins and returns.  Off in the shipped library.
-#ifdef TTT_STAMPS
-#ifndef TTT_STAMP_TID
-#define TTT_STAMP_TID 0      // the recording thread
-#endif
-__device__ unsigned long long g_ttt_stamps[16384];
-__device__ unsigned int g_ttt_nstamps;
-#define TTT_STAMP(id)                                                            \
-  do {                                                                           \
-    if (threadIdx.x == TTT_STAMP_TID && blockIdx.x == 0) {                                  \
-      const unsigned n_ = g_ttt_nstamps;                                         \
-      if (n_ < 16384) {                                                          \
-        g_ttt_stamps[n_] = (globaltimer_ns() << 8) | (unsigned long long)(id);   \
-        g_ttt_nstamps = n_ + 1;                                                  \
-      }                                                                          \
-    }                                                                            \
-  } while (0)
-#else
-#define TTT_STAMP(id)
-#endif
-
 // ---- shared memory map (offsets from a 1024-byte aligned base)
 constexpr uint32_t OFF_BIG = 0;                      // 5 hidden-major buffers of 32 KB
 constexpr uint32_t OFF_T = 5 * BIG;                  // 7 token tiles of 8 KB
@@ -105,8 +83,8 @@ constexpr uint32_t OFF_SIGF = OFF_SIGLN + 256;       // fp32[64]
 constexpr uint32_t OFF_GB1 = OFF_SIGF + 256;         // fp32[256] copy of the per-thread dL/db1
 constexpr uint32_t OFF_PART = OFF_GB1 + 1024;        // fp32[8][64] partial sums for d_eta (one row per warp)
 constexpr uint32_t OFF_ETA = OFF_PART + 2048;        // bf16[2][64]
-constexpr uint32_t OFF_BAR = OFF_ETA + 256;          // 16 mbarriers
-constexpr uint32_t OFF_MISC = OFF_BAR + 128;
+constexpr uint32_t OFF_BAR = OFF_ETA + 256;          // 17 mbarriers
+constexpr uint32_t OFF_MISC = OFF_BAR + 192;
 constexpr uint32_t OFF_XCH = OFF_MISC + 64;        // fp32[2][64][8] row-sum exchange between warp pairs
 constexpr uint32_t SMEM_USED = OFF_XCH + 4096;
 constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;
@@ -118,6 +96,7 @@ constexpr int BAR_T = 5;       // +tile index (0..6)
 constexpr int BAR_IN = 12;     // +stage (0..1), recompute inputs
 constexpr int BAR_MMA = 14;
 constexpr int BAR_V = 15;      // recompute: the single V tile
+constexpr int BAR_DRAIN = 16;  // abort path only
 
 constexpr uint32_t TM_S1 = 0;      // W1^T / dL/dW1^T
 constexpr uint32_t TM_S2 = 128;    // W2   / dL/dW2
@@ -143,6 +122,7 @@ struct BwdParams {
   __nv_bfloat16* d_eta;
   uint8_t* dXQ; uint8_t* dXK; uint8_t* dXV;              // bf16 [rows][64], row-major
   int H, NC, cgs, nck;
+  int drop_load;            // test only: mini-batch whose recompute inputs stream 0 never loads (-1: none)
   uint32_t* status;
   uint64_t wait_limit_ns;
 };
@@ -182,12 +162,14 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   float* sXch = reinterpret_cast<float*>(smem + OFF_XCH);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_MISC);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + OFF_MISC + 4);
+  volatile uint32_t* never_flag = reinterpret_cast<volatile uint32_t*>(smem + OFF_MISC + 8);   // stays 0
   const uint64_t limit = p.wait_limit_ns;
 
   if (tid == 0) {
-    for (int i = 0; i < 16; ++i) mbar_init(&bars[i], i == BAR_MMA ? 4 : 1);
+    for (int i = 0; i < 17; ++i) mbar_init(&bars[i], (i == BAR_MMA || i == BAR_DRAIN) ? 4 : 1);
     fence_mbar_init();
     *abort_flag = 0;
+    *never_flag = 0;
     prefetch_tmap(&tmQ);
     prefetch_tmap(&tmK);
     prefetch_tmap(&tmV);
@@ -221,7 +203,6 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       ph ^= 1u << b;
       pending &= ~(1u << b);
     }
-    TTT_STAMP(0x40 + b);
   };
   auto wait_mma = [&]() {
     wait_bar(BAR_MMA);
@@ -229,11 +210,9 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     tc_fence_after_sync();
   };
   auto publish = [&]() {
-    TTT_STAMP(0x11);
     fence_proxy_async_smem();   // generic-proxy writes to shared memory -> async proxy (MMA, bulk copies)
     tc_fence_before_sync();
     __syncthreads();
-    TTT_STAMP(0x10);
   };
   auto commit = [&]() { umma_commit(&bars[BAR_MMA]); };   // thread 0
   // thread 0: bulk-load helpers
@@ -294,6 +273,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     uint8_t* tU2 = tile(6);
 
     auto issue_inputs = [&](int j) {   // thread 0
+      if (i0 + j == p.drop_load && sid == 0) return;
       const int s = j & 1;
       const int row0 = static_cast<int>(tok_rows0 + (long)(i0 + j) * 64);
       mbar_expect_tx(&bars[BAR_IN + s], 2 * TILE + 128);
@@ -1184,10 +1164,20 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
   }
   if (tid == 0) tma_wait_group<0>();
-  if (tid == 0 && (aborted || *abort_flag)) {
-    for (int b = 0; b < 16; ++b)
-      if (pending & (1u << b)) mbar_wait_bounded(&bars[b], (ph >> b) & 1u, abort_flag, limit);
-    atomicExch(p.status, static_cast<uint32_t>(TTT_B200_ERR_TIMEOUT));
+  if (aborted) {
+    // everything this CTA still has in flight is waited for (bounded, not cut short by the abort flag)
+    // before its shared and tensor memory go away: the tensor-core work of the four issuers ...
+    if (warp < 4) {
+      if (elect_one()) umma_commit(&bars[BAR_DRAIN]);
+      __syncwarp();
+    }
+    if (tid == 0) {
+      mbar_wait_bounded(&bars[BAR_DRAIN], 0, never_flag, limit);
+      // ... and its own loads
+      for (int b = 0; b < 16; ++b)
+        if (pending & (1u << b)) mbar_wait_bounded(&bars[b], (ph >> b) & 1u, never_flag, limit);
+      atomicExch(p.status, static_cast<uint32_t>(TTT_B200_ERR_TIMEOUT));
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -1196,7 +1186,8 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
 }  // namespace
 
-int ttt_launch_backward(const ttt_b200_bwd_args* a, cudaStream_t stream, uint32_t* status, uint64_t limit_ns) {
+int ttt_launch_backward(const ttt_b200_bwd_args* a, cudaStream_t stream, uint32_t* status, uint64_t limit_ns,
+                        int drop_load) {
   const uint64_t rows = static_cast<uint64_t>(a->B) * a->H * a->NC * 64;
   CUtensorMap tmQ, tmK, tmV, tmGo, tmDQ, tmDK, tmDV;
   if (int rc = ttt_make_tile_map(&tmQ, a->XQ, rows)) return rc;
@@ -1233,16 +1224,18 @@ int ttt_launch_backward(const ttt_b200_bwd_args* a, cudaStream_t stream, uint32_
   p.dXK = static_cast<uint8_t*>(a->grad_L_XK);
   p.dXV = static_cast<uint8_t*>(a->grad_L_XV);
   p.H = a->H; p.NC = a->NC; p.cgs = a->checkpoint_group_size; p.nck = a->num_checkpoints;
+  p.drop_load = drop_load;
   p.status = status;
   p.wait_limit_ns = limit_ns;
-  static bool attr_done[64] = {};
+  static std::once_flag once[64];
+  static cudaError_t attr_err[64];
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(ttt_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
-    if (dev >= 0 && dev < 64) attr_done[dev] = true;
-  }
+  if (dev < 0 || dev >= 64) return ttt_set_error(TTT_B200_ERR_LAUNCH, "device index out of range");
+  std::call_once(once[dev], [&] {
+    attr_err[dev] = cudaFuncSetAttribute(ttt_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  });
+  if (attr_err[dev] != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(attr_err[dev]));
   ttt_bwd_kernel<<<dim3(a->B * a->H), dim3(kThreads), SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmGo, tmDQ, tmDK, tmDV, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
@@ -1392,11 +1385,12 @@ extern "C" int ttt_b200_backward_noalloc(const ttt_b200_bwd_noalloc_args* a, voi
   p.dXK = static_cast<uint8_t*>(a->grad_L_XK);
   p.dXV = static_cast<uint8_t*>(a->grad_L_XV);
   p.H = a->H; p.NC = a->NC; p.cgs = a->checkpoint_group_size; p.nck = a->num_checkpoints;
+  p.drop_load = -1;
+  // The status word of this entry point is a device word that no launch clears: a kernel that gives up
+  // on a bounded wait sets it, and it stays set until a synchronising call or ttt_b200_take_status()
+  // reads and clears it (both without allocating anything).
   p.status = d.status;
-  p.wait_limit_ns = 2000ull * 1000 * 1000;
-  // the status word is shared like the scratch: it must read zero when this launch starts
-  e = cudaMemsetAsync(d.status, 0, sizeof(uint32_t), stream);
-  if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
+  p.wait_limit_ns = ttt_wait_limit_ns();
   ttt_bwd_kernel<<<dim3(a->B * a->H), dim3(kThreads), SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmGo, tmDQ, tmDK, tmDV, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
@@ -1405,23 +1399,32 @@ extern "C" int ttt_b200_backward_noalloc(const ttt_b200_bwd_noalloc_args* a, voi
     e = cudaMemcpyAsync(&st, d.status, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
     if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
-    if (st != 0)
+    if (st != 0) {
+      cudaMemsetAsync(d.status, 0, sizeof(uint32_t), stream);
+      cudaStreamSynchronize(stream);
       return ttt_set_error(TTT_B200_ERR_TIMEOUT, "a device-side bounded wait ran out; results are invalid");
+    }
   }
   return TTT_B200_OK;
 }
 
-#ifdef TTT_STAMPS
-// Debug builds only: copy out and reset the timeline of CTA 0 (entries: time_ns << 8 | id).
-extern "C" int ttt_b200_debug_stamps(unsigned long long* out, int max_entries) {
-  unsigned int n = 0;
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(&n, g_ttt_nstamps, sizeof(n));
-  if (n > 16384) n = 16384;
-  if ((int)n > max_entries) n = max_entries;
-  cudaMemcpyFromSymbol(out, g_ttt_stamps, n * sizeof(unsigned long long));
-  const unsigned int zero = 0;
-  cudaMemcpyToSymbol(g_ttt_nstamps, &zero, sizeof(zero));
-  return (int)n;
+// Read and clear the status word of ttt_b200_backward_noalloc on every device it has run on (plain
+// synchronous copies from / to the symbol: nothing is allocated).  Called after the caller has
+// synchronised, by ttt_b200_take_status().
+uint32_t ttt_noalloc_take_status() {
+  uint32_t any = 0;
+  int cur = 0;
+  if (cudaGetDevice(&cur) != cudaSuccess) return 0;
+  for (int dev = 0; dev < 64; ++dev) {
+    if (!g_noalloc_dev[dev].ready) continue;
+    if (cudaSetDevice(dev) != cudaSuccess) continue;
+    uint32_t st = 0;
+    if (cudaMemcpyFromSymbol(&st, g_noalloc_status, sizeof(st)) == cudaSuccess && st != 0) {
+      any = st;
+      const uint32_t zero = 0;
+      cudaMemcpyToSymbol(g_noalloc_status, &zero, sizeof(zero));
+    }
+  }
+  cudaSetDevice(cur);
+  return any;
 }
-#endif

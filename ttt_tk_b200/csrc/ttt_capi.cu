@@ -17,7 +17,10 @@
 
 int ttt_launch_forward(const ttt_b200_fwd_args* a, cudaStream_t stream, uint32_t* status, uint64_t limit_ns,
                        int drop_load);
-int ttt_launch_backward(const ttt_b200_bwd_args* a, cudaStream_t stream, uint32_t* status, uint64_t limit_ns);
+int ttt_launch_backward(const ttt_b200_bwd_args* a, cudaStream_t stream, uint32_t* status, uint64_t limit_ns,
+                        int drop_load);
+int ttt_launch_backward_cluster(const ttt_b200_bwd_args* a, int cluster, cudaStream_t stream, uint32_t* status,
+                                uint64_t limit_ns, int drop_load);
 int ttt_launch_forward_cluster(const ttt_b200_fwd_args* a, int cluster, cudaStream_t stream, uint32_t* status,
                                uint64_t limit_ns, int drop_load);
 
@@ -34,9 +37,13 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
 
+uint64_t wait_limit_ns() { return ttt_wait_limit_ns(); }
+
+}  // namespace
+
 // Device-side waits give up after this long (nanoseconds).  A healthy launch never waits
 // more than microseconds; the limit only decides how fast a lost signal is reported.
-uint64_t wait_limit_ns() {
+uint64_t ttt_wait_limit_ns() {
   static uint64_t v = [] {
     const char* e = std::getenv("TTT_B200_WAIT_LIMIT_MS");
     long ms = e ? std::atol(e) : 2000;
@@ -45,6 +52,8 @@ uint64_t wait_limit_ns() {
   }();
   return v;
 }
+
+namespace {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -226,13 +235,30 @@ extern "C" int ttt_b200_backward(const ttt_b200_bwd_args* a, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   uint32_t* status = nullptr;
   if (int rc = pre_launch(&status)) return rc;
-  if (int rc = ttt_launch_backward(a, stream, status, wait_limit_ns())) return rc;
+  int cluster = 1;
+  if (int rc = ttt_pick_cluster(a->B * a->H, a->flags, &cluster)) return rc;
+  // the hook drops the recompute inputs of the last group's second mini-batch (its only one if it has one)
+  const int last0 = (a->num_checkpoints - 1) * a->checkpoint_group_size;
+  const int drop = (a->flags & TTT_B200_FLAG_TEST_LOST_LOAD) ? (last0 + 1 < a->NC ? last0 + 1 : last0) : -1;
+  if (int rc = cluster == 1 ? ttt_launch_backward(a, stream, status, wait_limit_ns(), drop)
+                            : ttt_launch_backward_cluster(a, cluster, stream, status, wait_limit_ns(), drop))
+    return rc;
   if (a->flags & TTT_B200_FLAG_SYNC) return ttt_check_status(stream);
   return TTT_B200_OK;
 }
 
 extern "C" const char* ttt_b200_last_error(void) { return g_last_error.c_str(); }
 
-extern "C" int ttt_b200_take_status(void) { return ttt_take_status() ? TTT_B200_ERR_TIMEOUT : TTT_B200_OK; }
+extern "C" int ttt_b200_take_status(void) {
+  const uint32_t a = ttt_take_status();
+  const uint32_t b = ttt_noalloc_take_status();
+  return (a | b) ? TTT_B200_ERR_TIMEOUT : TTT_B200_OK;
+}
 
-extern "C" int ttt_b200_version(void) { return 1000; }
+extern "C" int ttt_b200_version(void) { return 1001; }
+
+extern "C" int ttt_b200_pick_cluster(int streams) {
+  int c = 1;
+  if (streams < 1 || ttt_pick_cluster(streams, 0u, &c) != TTT_B200_OK) return -1;
+  return c;
+}

@@ -124,17 +124,21 @@ __device__ __forceinline__ void mma_tok_partial(uint32_t tmem_d, uint32_t x_smem
   for (int j = 1; j < 4 * nblk; ++j) mma_issue_rt(tmem_d, a0 + j * (2048u >> 4), b0 + j * (2048u >> 4), idesc, 1u);
 }
 
-// ---- Sum of a partial 64 x 64 fp32 tile (the TokMap fragment: 16 values per thread, plus kExtra
-// further per-thread values) over the CTAs of the cluster.  Every CTA ends with the same bits: the
+// ---- Sum of a partial 64 x 64 fp32 tile (the TokMap fragment: 16 values per thread, optionally with
+// two further per-thread values) over the CTAs of the cluster.  Every CTA ends with the same bits: the
 // additions are arranged as a butterfly over the rank bits, (own + [rank^1]) + ([rank^2] + [rank^3]),
 // which is the same expression in every CTA up to the commutativity of each addition.
 //
-// Exchange area per CTA: 2 buffers x (kC - 1) slots x kV4 x 256 float4 (slot s holds the values of
-// rank ^ (s + 1)), with one mbarrier per buffer counting (kC - 1) x 8 arrivals (one per warp and
-// peer).  Successive reductions alternate between the buffers.  That is enough: a CTA sends reduction
-// n + 2 only after it has received reduction n + 1 from every warp of every peer, and a peer's warp
-// sends n + 1 only after it has read its part of buffer n.
-template <int kC, int kV4>
+// Exchange area per CTA: 2 buffers x (kC - 1) slots (slot s holds the values of rank ^ (s + 1)) of
+// kSlotBytes each: 256 x 4 float4 for the tile, then 256 x float2 for the extra values when a kernel
+// uses them (kSlotBytes = 16384 or 18432); one mbarrier per buffer counting (kC - 1) x 8 arrivals (one
+// per warp and peer).  Successive reductions alternate between the buffers.  That is enough: a CTA
+// sends reduction n + 2 only after it has received reduction n + 1 from every warp of every peer, and
+// a peer's warp sends n + 1 only after it has read its part of buffer n.
+__device__ __forceinline__ void st_cluster_f2(uint32_t addr, float a, float b) {
+  asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(a), "f"(b) : "memory");
+}
+template <int kC, uint32_t kSlotBytes_>
 struct ClusterSum {
   uint8_t* bufp;         // the exchange area (this CTA's shared memory)
   uint64_t* bars;        // [2]
@@ -143,24 +147,30 @@ struct ClusterSum {
   volatile uint32_t* abort_flag;
   uint64_t limit;
 
-  static constexpr uint32_t kSlotBytes = kV4 * 4096u;
+  static constexpr uint32_t kSlotBytes = kSlotBytes_;
   static constexpr uint32_t kBufBytes = (kC - 1) * kSlotBytes;
   static constexpr uint32_t kBytes = 2 * kBufBytes;
   static constexpr uint32_t kArrivals = (kC - 1) * 8;
+  static_assert(kSlotBytes == 16384 || kSlotBytes == 18432, "slot = tile, or tile + extras");
 
-  // v: kV4 * 4 floats.  Returns with v summed over the cluster.
-  __device__ __forceinline__ void run(float (&v)[kV4 * 4], int tid, int lane) {
+  // v: the thread's 16 tile values; e0, e1: its two extra values (kExtra).  Returns with all of them
+  // summed over the cluster.
+  template <bool kExtra>
+  __device__ __forceinline__ void run_impl(float (&v)[16], float& e0, float& e1, int tid, int lane) {
+    static_assert(!kExtra || kSlotBytes == 18432, "the exchange area has no room for extra values");
     const uint32_t b = n & 1u, par = (n >> 1) & 1u;
     ++n;
     const uint32_t boff = b * kBufBytes + static_cast<uint32_t>(tid) * 16u;
-    const uint32_t base = smem_u32(bufp) + boff;
+    const uint32_t eoff = b * kBufBytes + 16384u + static_cast<uint32_t>(tid) * 8u;
+    const uint32_t base = smem_u32(bufp);
 #pragma unroll
     for (int s = 0; s < kC - 1; ++s) {
       const uint32_t peer = rank ^ static_cast<uint32_t>(s + 1);
       // at the peer, this CTA is rank ^ (s + 1) as well: the slot index is the same on both sides
-      const uint32_t dst = mapa(base + s * kSlotBytes, peer);
+      const uint32_t dst = mapa(base + boff + s * kSlotBytes, peer);
 #pragma unroll
-      for (int j = 0; j < kV4; ++j) st_cluster_f4(dst + j * 4096u, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+      for (int j = 0; j < 4; ++j) st_cluster_f4(dst + j * 4096u, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+      if constexpr (kExtra) st_cluster_f2(mapa(base + eoff + s * kSlotBytes, peer), e0, e1);
     }
     __syncwarp();
     if (lane == 0) {
@@ -170,15 +180,20 @@ struct ClusterSum {
     }
     mbar_wait_cl(&bars[b], par, abort_flag, limit, kC);
     const float4* src = reinterpret_cast<const float4*>(bufp + boff);
+    const float2* esrc = reinterpret_cast<const float2*>(bufp + eoff);
     if constexpr (kC == 2) {
 #pragma unroll
-      for (int j = 0; j < kV4; ++j) {
+      for (int j = 0; j < 4; ++j) {
         const float4 p = src[j * 256];
         v[4 * j] += p.x; v[4 * j + 1] += p.y; v[4 * j + 2] += p.z; v[4 * j + 3] += p.w;
       }
+      if constexpr (kExtra) {
+        const float2 q = esrc[0];
+        e0 += q.x; e1 += q.y;
+      }
     } else {
 #pragma unroll
-      for (int j = 0; j < kV4; ++j) {
+      for (int j = 0; j < 4; ++j) {
         const float4 p1 = src[j * 256];
         const float4 p2 = src[(kSlotBytes / 16) + j * 256];
         const float4 p3 = src[2 * (kSlotBytes / 16) + j * 256];
@@ -187,7 +202,19 @@ struct ClusterSum {
         v[4 * j + 2] = (v[4 * j + 2] + p1.z) + (p2.z + p3.z);
         v[4 * j + 3] = (v[4 * j + 3] + p1.w) + (p2.w + p3.w);
       }
+      if constexpr (kExtra) {
+        const float2 q1 = esrc[0], q2 = esrc[kSlotBytes / 8], q3 = esrc[2 * (kSlotBytes / 8)];
+        e0 = (e0 + q1.x) + (q2.x + q3.x);
+        e1 = (e1 + q1.y) + (q2.y + q3.y);
+      }
     }
+  }
+  __device__ __forceinline__ void run(float (&v)[16], int tid, int lane) {
+    float d0 = 0.f, d1 = 0.f;
+    run_impl<false>(v, d0, d1, tid, lane);
+  }
+  __device__ __forceinline__ void run_with_extras(float (&v)[16], float& e0, float& e1, int tid, int lane) {
+    run_impl<true>(v, e0, e1, tid, lane);
   }
 };
 

@@ -38,7 +38,7 @@ struct Cfg {
   static constexpr int NB = 4 / kC;                  // 64-row blocks of hidden units per CTA
   static constexpr int R = 64 * NB;                  // hidden units per CTA
   static constexpr uint32_t HB = NB * TILE;          // bytes of an [R][64] bf16 tile
-  using Sum = ClusterSum<kC, 4>;
+  using Sum = ClusterSum<kC, 16384>;
   static constexpr uint32_t OFF_K = 0;
   static constexpr uint32_t OFF_V = OFF_K + kStages * TILE;
   static constexpr uint32_t OFF_Q = OFF_V + kStages * TILE;

@@ -1,0 +1,199 @@
+// Layer-side kernels around the TTT-MLP operator: the learning-rate gate that produces `last_eta`,
+// and the output LayerNorm that follows the operator, each fused with the layout change the operator's
+// interface forces (a model's activations are token-major [B][T][H*64]; the operator wants contiguous
+// head-major [B][H][T][..] tensors: README.md:98 of the reference).  The reference leaves all of this
+// to its callers (README.md:22-98: the caller passes `last_eta` and receives `XQW_batch`); the
+// statements these kernels must match are the torch expressions in oracle/glue.py.
+//
+//   eta gate       last_eta[b][h][t] = scale * sigmoid(logit[b][t][h])             bf16 in, bf16 out
+//   its backward   d_logit[b][t][h]  = d_last_eta[b][h][t] * scale * s (1 - s)
+//   output norm    y[b][t][:] = gamma * LayerNorm_{H*64}(x[b][:][t][:]) + beta     x = Out [B][H][T][64] bf16
+//
+// All three are HBM-bound byte movers with a little fp32 arithmetic: algorithmic bytes = input + output.
+#include <cuda_bf16.h>
+
+#include <cstdio>
+
+#include "ttt_internal.h"
+
+namespace {
+
+__device__ __forceinline__ float sigmoidf_fast(float x) { return 1.f / (1.f + __expf(-x)); }
+
+// ---- eta gate.  One CTA per (b, block of 64 tokens): the [64 tok][H] block of the logits is one
+// contiguous run of 128 H bytes; it is turned through shared memory and leaves as H runs of 128 bytes
+// (64 tokens of one head).  kBackward: `other` is d_last_eta [B][H][T] and the result d_logit [B][T][H].
+template <bool kBackward>
+__global__ void __launch_bounds__(256) eta_gate_kernel(const __nv_bfloat16* __restrict__ logits,
+                                                       const __nv_bfloat16* __restrict__ other,
+                                                       __nv_bfloat16* __restrict__ out, float scale, int T, int H) {
+  extern __shared__ float tile[];                 // [64][H + 1]
+  const int nblk = T / 64;
+  const int b = blockIdx.x / nblk, t0 = (blockIdx.x % nblk) * 64;
+  const int n = 64 * H;
+  const long tm0 = (static_cast<long>(b) * T + t0) * H;             // first element of the token-major block
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int t = i / H, h = i - t * H;
+    const float s = sigmoidf_fast(__bfloat162float(logits[tm0 + i]));
+    tile[t * (H + 1) + h] = kBackward ? scale * s * (1.f - s) : scale * s;
+  }
+  __syncthreads();
+  if (!kBackward) {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const int h = i >> 6, t = i & 63;
+      out[(static_cast<long>(b) * H + h) * T + t0 + t] = __float2bfloat16(tile[t * (H + 1) + h]);
+    }
+  } else {
+    // d_last_eta is head-major: read it along t, multiply, and leave token-major
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const int h = i >> 6, t = i & 63;
+      tile[t * (H + 1) + h] *= __bfloat162float(other[(static_cast<long>(b) * H + h) * T + t0 + t]);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const int t = i / H, h = i - t * H;
+      out[tm0 + i] = __float2bfloat16(tile[t * (H + 1) + h]);
+    }
+  }
+}
+
+// ---- output LayerNorm over the H*64 features of a token, fused with the head-major -> token-major
+// turn.  One warp per token: 8 lanes take one head's 128-byte row as 16-byte pieces, so one warp-wide
+// load covers 4 heads; a token's values stay in registers (packed bf16) between the statistics and the
+// normalisation; the result leaves as whole 512-byte runs of the token's row.
+constexpr int kMaxChunks = 16;     // H <= 64
+__global__ void __launch_bounds__(256) unpack_layernorm_kernel(const uint4* __restrict__ src, const float* __restrict__ gamma,
+                                                               const float* __restrict__ beta, uint4* __restrict__ dst,
+                                                               float eps, long tokens, int T, int H) {
+  const int lane = threadIdx.x & 31;
+  const int sub = lane >> 3, piece = lane & 7;          // head within a group of 4, 16-byte piece of the row
+  const int chunks = (H + 3) >> 2;
+  const long warp0 = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long nwarps = (static_cast<long>(gridDim.x) * blockDim.x) >> 5;
+  const float inv_n = 1.f / static_cast<float>(H * 64);
+  for (long tok = warp0; tok < tokens; tok += nwarps) {
+    const long b = tok / T, t = tok - b * T;
+    uint4 raw[kMaxChunks];
+    float sum = 0.f;
+#pragma unroll
+    for (int c = 0; c < kMaxChunks; ++c) {
+      const int h = 4 * c + sub;
+      if (c < chunks && h < H) {
+        raw[c] = __ldcs(src + (((b * H + h) * T + t) << 3) + piece);
+        const __nv_bfloat162* v = reinterpret_cast<const __nv_bfloat162*>(&raw[c]);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = __bfloat1622float2(v[k]);
+          sum += f.x + f.y;
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float mean = sum * inv_n;
+    float sq = 0.f;
+#pragma unroll
+    for (int c = 0; c < kMaxChunks; ++c) {
+      const int h = 4 * c + sub;
+      if (c < chunks && h < H) {
+        const __nv_bfloat162* v = reinterpret_cast<const __nv_bfloat162*>(&raw[c]);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = __bfloat1622float2(v[k]);
+          sq = fmaf(f.x - mean, f.x - mean, fmaf(f.y - mean, f.y - mean, sq));
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    const float rstd = rsqrtf(sq * inv_n + eps);
+#pragma unroll
+    for (int c = 0; c < kMaxChunks; ++c) {
+      const int h = 4 * c + sub;
+      if (c < chunks && h < H) {
+        const __nv_bfloat162* v = reinterpret_cast<const __nv_bfloat162*>(&raw[c]);
+        const int f0 = h * 64 + piece * 8;
+        const float4 g0 = *reinterpret_cast<const float4*>(gamma + f0), g1 = *reinterpret_cast<const float4*>(gamma + f0 + 4);
+        const float4 b0 = *reinterpret_cast<const float4*>(beta + f0), b1 = *reinterpret_cast<const float4*>(beta + f0 + 4);
+        const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        uint4 o4;
+        __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = __bfloat1622float2(v[k]);
+          o[k] = __floats2bfloat162_rn(fmaf((f.x - mean) * rstd, gg[2 * k], bb[2 * k]),
+                                       fmaf((f.y - mean) * rstd, gg[2 * k + 1], bb[2 * k + 1]));
+        }
+        __stcs(dst + ((tok * H + h) << 3) + piece, o4);
+      }
+    }
+  }
+}
+
+int check_common(const char* what, int B, int T, int H) {
+  if (B < 1 || T < 1 || H < 1 || (T % TTT_CS) != 0) {
+    static thread_local char buf[128];
+    snprintf(buf, sizeof buf, "%s: B, T, H >= 1 and T a multiple of the mini-batch size 64", what);
+    return ttt_set_error(TTT_B200_ERR_BAD_ARGS, buf);
+  }
+  if (static_cast<long>(B) * T * H >= (1L << 31))
+    return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "B * T * H must stay below 2^31");
+  return TTT_B200_OK;
+}
+bool bad_ptr(const void* p, uintptr_t align) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & (align - 1)); }
+
+int launch_eta(bool backward, const void* logits, const void* other, void* out, float scale, int B, int T, int H,
+               void* stream_) {
+  if (int rc = check_common("eta gate", B, T, H)) return rc;
+  if (H > 256) return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "eta gate: H must not exceed 256");
+  if (bad_ptr(logits, 2) || bad_ptr(out, 2) || (backward && bad_ptr(other, 2)))
+    return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "eta gate: null or misaligned tensor pointer");
+  const unsigned grid = static_cast<unsigned>(B) * (T / 64);
+  const size_t smem = 64 * (H + 1) * sizeof(float);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (backward) {
+    eta_gate_kernel<true><<<grid, 256, smem, stream>>>(static_cast<const __nv_bfloat16*>(logits),
+                                                       static_cast<const __nv_bfloat16*>(other),
+                                                       static_cast<__nv_bfloat16*>(out), scale, T, H);
+  } else {
+    eta_gate_kernel<false><<<grid, 256, smem, stream>>>(static_cast<const __nv_bfloat16*>(logits), nullptr,
+                                                        static_cast<__nv_bfloat16*>(out), scale, T, H);
+  }
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
+  return TTT_B200_OK;
+}
+
+}  // namespace
+
+extern "C" int ttt_b200_eta_gate(const void* logits, void* last_eta, float scale, int B, int T, int H, void* stream) {
+  return launch_eta(false, logits, nullptr, last_eta, scale, B, T, H, stream);
+}
+
+extern "C" int ttt_b200_eta_gate_backward(const void* logits, const void* grad_last_eta, void* grad_logits, float scale,
+                                          int B, int T, int H, void* stream) {
+  return launch_eta(true, logits, grad_last_eta, grad_logits, scale, B, T, H, stream);
+}
+
+extern "C" int ttt_b200_unpack_layernorm(const void* src, const float* gamma, const float* beta, void* dst, float eps,
+                                         int B, int T, int H, void* stream_) {
+  if (int rc = check_common("output norm", B, T, H)) return rc;
+  if (H > 4 * kMaxChunks) return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "output norm: H must not exceed 64");
+  if (bad_ptr(src, 16) || bad_ptr(dst, 16) || bad_ptr(gamma, 16) || bad_ptr(beta, 16))
+    return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "output norm: null or not 16-byte aligned tensor pointer");
+  if (src == dst) return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "output norm: the transform is out of place");
+  if (!(eps >= 0.f)) return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "output norm: eps must be >= 0");
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long tokens = static_cast<long>(B) * T;
+  long blocks = (tokens + 7) / 8;                     // 8 warps = 8 tokens per CTA pass
+  const long cap = static_cast<long>(sms) * 8;        // a whole number of CTAs per SM
+  if (blocks > cap) blocks = cap;
+  unpack_layernorm_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+      static_cast<const uint4*>(src), gamma, beta, static_cast<uint4*>(dst), eps, tokens, T, H);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
+  return TTT_B200_OK;
+}

@@ -30,3 +30,9 @@ uint32_t ttt_take_status();
 // Build a 2-D tensor map over a contiguous [rows][64] bf16 array with a 64 x 64 box and the
 // 128-byte swizzle (the layout every 64 x 64 token tile of the operator has in memory).
 int ttt_make_tile_map(CUtensorMap* map, const void* base, uint64_t rows);
+
+// Limit of the device-side bounded waits in nanoseconds (TTT_B200_WAIT_LIMIT_MS, default 2000 ms).
+uint64_t ttt_wait_limit_ns();
+
+// Read and clear the device status word of ttt_b200_backward_noalloc (0 = nothing reported).
+uint32_t ttt_noalloc_take_status();
