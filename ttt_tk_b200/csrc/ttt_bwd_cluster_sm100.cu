@@ -17,13 +17,14 @@
 //   recompute; in the reverse step the hidden-unit contractions G7 (dQ), G5 / G6 / G8 (merged into
 //   one tile: A2 = -eta acc1 + acc2, plus the two d_eta row sums that are linear in acc1 and T1) and
 //   G13 (dK, together with the -eta T1 term).  Three sums per reverse step, two per recomputed
-//   mini-batch.
+//   mini-batch.  dQ and dK are outputs only: they are summed by reduce-scatter (every CTA finishes and
+//   stores the token rows it owns), which sends kC times fewer bytes than an all-reduce.
 //
 //   replicated: everything 64 x 64 (LayerNorm stages, second-order terms), b2, dL/db2, d_gamma,
 //   d_beta; every CTA computes them from the same summed tiles, bit for bit.  The token-tile scratch
 //   (x_hat_fused, dl/dZ2, x_hat_ln, 1/std) is written by every CTA with the same bytes, so that a CTA
-//   only ever reads back what it has written itself.  The CTAs take turns storing dQ / dK / dV; rank 0
-//   stores d_eta and the per-stream vectors.
+//   only ever reads back what it has written itself.  The CTAs take turns storing dV; rank 0 stores d_eta and the
+//   per-stream vectors.
 //
 // Every wait is bounded; a wait that runs out raises the abort flag of the whole cluster, the vote on
 // leaving a loop is taken CTA-wide at a barrier, and no CTA exits before its peers have reached the
@@ -100,6 +101,7 @@ struct BwdClParams {
   float* d_gamma; float* d_beta;
   float* gW1; float* gb1; float* gW2; float* gb2;
   __nv_bfloat16* d_eta;
+  __nv_bfloat16* dXQ; __nv_bfloat16* dXK;               // bf16 [rows][64], row-major
   int H, NC, cgs, nck;
   int drop_load;            // test only: mini-batch whose recompute inputs stream 0 never loads (-1: none)
   uint32_t* status;
@@ -127,6 +129,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   const int NC = p.NC, cgs = p.cgs;
   const int hid0 = static_cast<int>(rank) * C::R;
   const uint32_t img0 = rank * HB;            // this CTA's rows inside a [256][64] scratch image
+  const bool kp_owner = C::Sum::row_owner(tid) == rank;     // this thread's token rows are this CTA's to finish
   const bool row_writer = tm.colhalf == 0 && tm.l3 == 0;   // of the 8 threads that share a row, the one that stores per-row values
 
   auto big = [&](int i) -> uint8_t* { return smem + C::OFF_BIG + i * HB; };
@@ -849,20 +852,18 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           }
         }
       }
-      {   // dQ = go + sum over the cluster of gZ1b W1+^T, staged over the dL/dOut tile and stored by TMA
+      {   // dQ = go + sum over the cluster of gZ1b W1+^T: an output only, so the partial tiles are summed by
+          // reduce-scatter and every CTA stores the token rows it owns
         float acc[16], go[16];
         tok_ld(tm, tmem + C::TM_B, acc);
-        cluster_sum(acc);
-        tok_ld_tile(tm, t_go, go);
+        if (csum.reduce_scatter(acc, tid)) {
+          tok_ld_tile(tm, t_go, go);
 #pragma unroll
-        for (int q = 0; q < 16; ++q) go[q] += acc[q];
-        tok_st_tile(tm, t_go, go);
+          for (int q = 0; q < 16; ++q) go[q] += acc[q];
+          tok_st_global(tm, p.dXQ + static_cast<long>(row0) * 64, go);
+        }
       }
       publish();
-      if (tid == 0 && turn % kC == rank) {
-        tma_store_2d(&tmDQ, t_go, 0, row0);
-        tma_commit_group();
-      }
       wait_bar(BAR_BIG + ib4);
       wait_bar(BAR_T + 4);
       wait_bar(BAR_BIG + ib1);      // X2, requested two phases ago
@@ -1028,7 +1029,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
               const float gly = gm * bt;
               dga[x] = fmaf(go[x], bt, gly * xh[x]);
               dv[x] = -gly;
-              if (rank == 0) kp[x] += gly;        // added once across the cluster
+              if (kp_owner) kp[x] += gly;         // added once across the cluster: by the CTA that owns the row
               const float gxh = fmaf(gly, gm, -(go[x] * gm * ra[3] + A2[x] * ra[4]) * rs0 * (1.f / 64.f));
               sa[0] += (-gxh * xh[x] - A2[x] * gz[x]) * rs0;
               sa[1] += gxh;
@@ -1040,7 +1041,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
               const float gly = gm * bt;
               dga[x] = fmaf(go[x], bt, gly * xh[x]);
               dv[x] = -gly;
-              if (rank == 0) kp[x] += gly;
+              if (kp_owner) kp[x] += gly;
               const float gxh = fmaf(gly, gm, -(go[x] * gm * rb[3] + A2[x] * rb[4]) * rs1 * (1.f / 64.f));
               sb[0] += (-gxh * xh[x] - A2[x] * gz[x]) * rs1;
               sb[1] += gxh;
@@ -1143,21 +1144,16 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                  HID_ONE(true, C::TM_S2, big(ib3), t_q, 1u, 0),
                  if (NB > 1) HID_ONE(true, C::TM_S2, big(ib3), t_q, 1u, NB - 1))
       wait_mma();
-      // ---- E6: dK = sum over the cluster of (share of dK + gZ1in W1^T), staged over the dl/dZ2 tile (dead
-      // since G12) and stored by TMA; nothing waits for the store here: the tile's next load is issue_gz2's
+      // ---- E6: dK = sum over the cluster of (share of dK + gZ1in W1^T): an output only, summed by
+      // reduce-scatter; every CTA stores the token rows it owns
       {
         float acc[16];
         tok_ld(tm, tmem + C::TM_A, acc);
 #pragma unroll
         for (int q = 0; q < 16; ++q) kp[q] += acc[q];
-        cluster_sum(kp);
-        tok_st_tile(tm, t_gz2, kp);
+        if (csum.reduce_scatter(kp, tid)) tok_st_global(tm, p.dXK + static_cast<long>(row0) * 64, kp);
       }
       aborted = publish_vote();
-      if (tid == 0 && (turn + 2) % kC == rank) {
-        tma_store_2d(&tmDK, t_gz2, 0, row0);
-        tma_commit_group();
-      }
       // pre-update weights of this mini-batch are the post-update weights of the previous one
       {
         const int n0 = ib4, n1 = ib1, n2 = ib0, n3 = ib2, n4 = ib3;
@@ -1221,8 +1217,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   tc_fence_before_sync();
   __syncthreads();
   // no CTA leaves while a peer may still write into its shared memory (exchange area, abort flag)
-  cluster_arrive();
-  cluster_wait();
+  cluster_exit(abort_flag);
   if (warp == 0) tmem_dealloc(tmem, C::TM_COLS);
 }
 
@@ -1287,6 +1282,8 @@ int ttt_launch_backward_cluster(const ttt_b200_bwd_args* a, int cluster, cudaStr
   p.d_gamma = a->grad_L_ttt_norm_weight; p.d_beta = a->grad_L_ttt_norm_bias;
   p.gW1 = a->grad_L_W1_init; p.gb1 = a->grad_L_b1_init; p.gW2 = a->grad_L_W2_init; p.gb2 = a->grad_L_b2_init;
   p.d_eta = static_cast<__nv_bfloat16*>(a->grad_L_last_eta);
+  p.dXQ = static_cast<__nv_bfloat16*>(a->grad_L_XQ);
+  p.dXK = static_cast<__nv_bfloat16*>(a->grad_L_XK);
   p.H = a->H; p.NC = a->NC; p.cgs = a->checkpoint_group_size; p.nck = a->num_checkpoints;
   p.drop_load = drop_load;
   p.status = status;

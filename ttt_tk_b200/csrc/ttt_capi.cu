@@ -75,8 +75,10 @@ int sm_count() {
 }  // namespace
 
 // How many CTAs share one stream.  The mini-batches of a stream are strictly sequential, so with fewer
-// streams than SMs the idle SMs can only help by taking a share of every stream's hidden units: the
-// largest cluster size (1, 2 or 4) whose CTAs all fit on the GPU at once is used.
+// streams than SMs the idle SMs can only help by taking a share of every stream's hidden units.  The
+// thresholds are measured (B200, 148 SMs): four CTAs per stream win whenever they all fit on the GPU at
+// once (about 12 % per mini-batch over one CTA); two CTAs per stream win up to about 100 resident CTAs
+// and lose beyond (the backward's exchanges slow down when most SMs of a GPC take part in one).
 int ttt_pick_cluster(int streams, uint32_t flags, int* cluster) {
   int forced = static_cast<int>((flags & TTT_B200_FLAG_CLUSTER_MASK) >> TTT_B200_FLAG_CLUSTER_SHIFT);
   if (forced == 0) {
@@ -93,7 +95,7 @@ int ttt_pick_cluster(int streams, uint32_t flags, int* cluster) {
     return TTT_B200_OK;
   }
   const int sms = sm_count();
-  *cluster = 4 * streams <= sms ? 4 : (2 * streams <= sms ? 2 : 1);
+  *cluster = 4 * streams <= sms ? 4 : (10 * 2 * streams <= 7 * sms ? 2 : 1);
   return TTT_B200_OK;
 }
 

@@ -6,11 +6,13 @@
 // Replaces the reference's tp_reduce / tp_reduce_arrive (kernels/ttt_backward/ttt.cu:21-69) and the
 // forward's Z2 reduction (kernels/ttt/ttt.cu:332-348, 506-522), which exchange bf16 tiles between
 // hardware cluster barriers.  Here the partial tiles travel in fp32, straight from the registers of
-// the thread that read them out of tensor memory into the peers' shared memory (plain
-// st.shared::cluster stores), followed by one remote mbarrier arrive per warp and peer (release at
-// cluster scope); the receiver polls its own mbarrier with a bounded try_wait (acquire at cluster
-// scope).  The hardware cluster barrier, which cannot time out, is used only twice per kernel: after
-// the mbarriers are initialised and before the CTAs exit.
+// the thread that read them out of tensor memory into the peers' shared memory as asynchronous stores
+// (st.async) that complete a transaction count on the receiver's mbarrier: data and signal travel
+// together, nobody waits for an acknowledgement (plain remote stores followed by a release-arrive
+// cost a further round trip over the SM-to-SM network: measured 0.3 us per exchange).  The receiver
+// arms its mbarrier with the byte count it expects and polls it with a bounded try_wait.  The hardware
+// cluster barrier, which cannot time out, is used only after the mbarriers are initialised and before
+// the CTAs exit.
 #pragma once
 
 #include "ttt_device.cuh"
@@ -124,6 +126,18 @@ __device__ __forceinline__ void mma_tok_partial(uint32_t tmem_d, uint32_t x_smem
   for (int j = 1; j < 4 * nblk; ++j) mma_issue_rt(tmem_d, a0 + j * (2048u >> 4), b0 + j * (2048u >> 4), idesc, 1u);
 }
 
+// the thread's 16 values of a token-major fragment, rounded to bf16, straight to a row-major [64][64] bf16
+// tile in global memory (`tile` = its first element): used by the CTA that owns the rows after a
+// reduce-scatter, where only a quarter or half of the tile is this CTA's to store
+__device__ __forceinline__ void tok_st_global(const TokMap& m, __nv_bfloat16* tile, const float (&v)[16]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int c = m.col(j);
+    *reinterpret_cast<uint32_t*>(tile + m.r0 * 64 + c) = pack_bf16(v[4 * j], v[4 * j + 1]);
+    *reinterpret_cast<uint32_t*>(tile + m.r1 * 64 + c) = pack_bf16(v[4 * j + 2], v[4 * j + 3]);
+  }
+}
+
 // ---- Sum of a partial 64 x 64 fp32 tile (the TokMap fragment: 16 values per thread, optionally with
 // two further per-thread values) over the CTAs of the cluster.  Every CTA ends with the same bits: the
 // additions are arranged as a butterfly over the rank bits, (own + [rank^1]) + ([rank^2] + [rank^3]),
@@ -135,13 +149,22 @@ __device__ __forceinline__ void mma_tok_partial(uint32_t tmem_d, uint32_t x_smem
 // per warp and peer).  Successive reductions alternate between the buffers.  That is enough: a CTA
 // sends reduction n + 2 only after it has received reduction n + 1 from every warp of every peer, and
 // a peer's warp sends n + 1 only after it has read its part of buffer n.
-__device__ __forceinline__ void st_cluster_f2(uint32_t addr, float a, float b) {
-  asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(a), "f"(b) : "memory");
+// asynchronous remote stores: the bytes are counted on the mbarrier `bar` (a shared::cluster address in
+// the same CTA as `addr`) when they have landed
+__device__ __forceinline__ void st_async_f4(uint32_t addr, uint32_t bar, float a, float b, float c, float d) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%2, %3, %4, %5}, [%1];" ::"r"(addr),
+               "r"(bar), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+__device__ __forceinline__ void st_async_f2(uint32_t addr, uint32_t bar, float a, float b) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.f32 [%0], {%2, %3}, [%1];" ::"r"(addr),
+               "r"(bar), "f"(a), "f"(b)
+               : "memory");
 }
 template <int kC, uint32_t kSlotBytes_>
 struct ClusterSum {
   uint8_t* bufp;         // the exchange area (this CTA's shared memory)
-  uint64_t* bars;        // [2]
+  uint64_t* bars;        // [2], initialised with count 1 (the arming arrival of this CTA's thread 0)
   uint32_t n;            // reductions done
   uint32_t rank;
   volatile uint32_t* abort_flag;
@@ -150,11 +173,17 @@ struct ClusterSum {
   static constexpr uint32_t kSlotBytes = kSlotBytes_;
   static constexpr uint32_t kBufBytes = (kC - 1) * kSlotBytes;
   static constexpr uint32_t kBytes = 2 * kBufBytes;
-  static constexpr uint32_t kArrivals = (kC - 1) * 8;
+  static constexpr uint32_t kArrivals = 1;
   static_assert(kSlotBytes == 16384 || kSlotBytes == 18432, "slot = tile, or tile + extras");
 
   // v: the thread's 16 tile values; e0, e1: its two extra values (kExtra).  Returns with all of them
   // summed over the cluster.
+  //
+  // Order on one buffer: this CTA arms phase k of barrier b (reduction n = 2 k + b) after it has left
+  // the wait of reduction n - 2 in program order, and a peer's bytes for reduction n can only be sent
+  // after that peer has received this CTA's reduction n - 1, which every thread sends after its own wait
+  // of n - 2: no byte of phase k is counted on phase k - 1.  Bytes that arrive before the arming only
+  // take the transaction count below zero for a moment.
   template <bool kExtra>
   __device__ __forceinline__ void run_impl(float (&v)[16], float& e0, float& e1, int tid, int lane) {
     static_assert(!kExtra || kSlotBytes == 18432, "the exchange area has no room for extra values");
@@ -163,20 +192,18 @@ struct ClusterSum {
     const uint32_t boff = b * kBufBytes + static_cast<uint32_t>(tid) * 16u;
     const uint32_t eoff = b * kBufBytes + 16384u + static_cast<uint32_t>(tid) * 8u;
     const uint32_t base = smem_u32(bufp);
+    const uint32_t ba = smem_u32(&bars[b]);
+    if (tid == 0) mbar_expect_tx(&bars[b], (kC - 1) * (kExtra ? 18432u : 16384u));
 #pragma unroll
     for (int s = 0; s < kC - 1; ++s) {
       const uint32_t peer = rank ^ static_cast<uint32_t>(s + 1);
       // at the peer, this CTA is rank ^ (s + 1) as well: the slot index is the same on both sides
       const uint32_t dst = mapa(base + boff + s * kSlotBytes, peer);
+      const uint32_t rbar = mapa(ba, peer);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) st_cluster_f4(dst + j * 4096u, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-      if constexpr (kExtra) st_cluster_f2(mapa(base + eoff + s * kSlotBytes, peer), e0, e1);
-    }
-    __syncwarp();
-    if (lane == 0) {
-      const uint32_t ba = smem_u32(&bars[b]);
-#pragma unroll
-      for (int s = 0; s < kC - 1; ++s) mbar_arrive_cluster(mapa(ba, rank ^ static_cast<uint32_t>(s + 1)));
+      for (int j = 0; j < 4; ++j)
+        st_async_f4(dst + j * 4096u, rbar, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+      if constexpr (kExtra) st_async_f2(mapa(base + eoff + s * kSlotBytes, peer), rbar, e0, e1);
     }
     mbar_wait_cl(&bars[b], par, abort_flag, limit, kC);
     const float4* src = reinterpret_cast<const float4*>(bufp + boff);
@@ -213,9 +240,74 @@ struct ClusterSum {
     float d0 = 0.f, d1 = 0.f;
     run_impl<false>(v, d0, d1, tid, lane);
   }
+
+  // The same sum, delivered only where it is needed when a tile is an output and not an operand of
+  // later steps: the token rows of the tile are dealt out to the CTAs of the cluster (the rows of
+  // fragment quadrant q = warp % 4, i.e. tokens 16 q .. 16 q + 15, belong to CTA q kC / 4), every thread
+  // sends its 16 values to the owner of its rows only, and the owner's threads add what arrives.  A CTA
+  // sends (kC - 1) / kC of a tile instead of kC - 1 tiles: the exchange is bound by the bytes that cross
+  // the SM-to-SM network.  Uses the same buffers, barriers and reduction counter as run().
+  // Returns true in the threads that now hold finished rows.
+  static __device__ __forceinline__ uint32_t row_owner(int tid) { return (static_cast<uint32_t>(tid >> 5) & 3u) * kC / 4u; }
+  __device__ __forceinline__ bool reduce_scatter(float (&v)[16], int tid) {
+    const uint32_t b = n & 1u, par = (n >> 1) & 1u;
+    ++n;
+    const uint32_t boff = b * kBufBytes + static_cast<uint32_t>(tid) * 16u;
+    const uint32_t owner = row_owner(tid);
+    if (tid == 0) mbar_expect_tx(&bars[b], (kC - 1) * (16384u / kC));
+    if (owner != rank) {
+      const uint32_t s = (rank ^ owner) - 1u;
+      const uint32_t dst = mapa(smem_u32(bufp) + boff + s * kSlotBytes, owner);
+      const uint32_t rbar = mapa(smem_u32(&bars[b]), owner);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        st_async_f4(dst + j * 4096u, rbar, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    }
+    mbar_wait_cl(&bars[b], par, abort_flag, limit, kC);
+    if (owner != rank) return false;
+    const float4* src = reinterpret_cast<const float4*>(bufp + boff);
+    if constexpr (kC == 2) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float4 p = src[j * 256];
+        v[4 * j] += p.x; v[4 * j + 1] += p.y; v[4 * j + 2] += p.z; v[4 * j + 3] += p.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float4 p1 = src[j * 256];
+        const float4 p2 = src[(kSlotBytes / 16) + j * 256];
+        const float4 p3 = src[2 * (kSlotBytes / 16) + j * 256];
+        v[4 * j] = (v[4 * j] + p1.x) + (p2.x + p3.x);
+        v[4 * j + 1] = (v[4 * j + 1] + p1.y) + (p2.y + p3.y);
+        v[4 * j + 2] = (v[4 * j + 2] + p1.z) + (p2.z + p3.z);
+        v[4 * j + 3] = (v[4 * j + 3] + p1.w) + (p2.w + p3.w);
+      }
+    }
+    return true;
+  }
   __device__ __forceinline__ void run_with_extras(float (&v)[16], float& e0, float& e1, int tid, int lane) {
     run_impl<true>(v, e0, e1, tid, lane);
   }
 };
+
+// Exit of a cluster kernel (all threads of all CTAs call it).  On the ordinary path every byte a peer
+// has sent to this CTA has been waited for, so one cluster barrier is enough before the shared memory
+// goes away.  After an abort the CTAs may have skipped waits: all of them first meet (nobody sends any
+// more), then let the asynchronous stores already under way land (they take well under a microsecond;
+// 50 us are allowed), then meet again.  Whether the cluster aborted is read after the first barrier: a
+// CTA raises the flag in every CTA of the cluster before it arrives there, so all of them read the same
+// answer and run the same number of barriers.
+__device__ __forceinline__ void cluster_exit(volatile uint32_t* abort_flag) {
+  cluster_arrive();
+  cluster_wait();
+  if (__syncthreads_or(*abort_flag != 0)) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 50000ull) {
+    }
+    cluster_arrive();
+    cluster_wait();
+  }
+}
 
 }  // namespace tttcl

@@ -15,7 +15,7 @@
 // distributed shared memory (ttt_cluster.cuh), after which every CTA holds the same Z2 and runs the
 // 64 x 64 LayerNorm stages redundantly (they are small).  Every CTA loads its own copy of the K, V, Q
 // tiles (plain TMA loads; after the first CTA they hit in L2).  b2 is kept, identically, by every CTA.
-// The CTAs of a cluster take turns storing the Out tile.
+// Z2b is needed only for the output: it is summed by reduce-scatter and every CTA stores the Out rows it owns.
 //
 // All accumulators are M = 64 tiles read with the 16x256b fragments (TokMap): a CTA's hidden units are
 // NB = 4 / kC blocks of 64 rows.  Per mini-batch the steps are those of the one-CTA kernel
@@ -84,6 +84,7 @@ struct FwdClParams {
   float* b1f;
   float* W2f;
   float* b2f;
+  __nv_bfloat16* out;
   int H, NC, cgs, nck;
   int drop_load;            // test only: mini-batch whose loads stream 0 never issues (-1: none)
   uint32_t* status;
@@ -473,9 +474,6 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       }
       tok_st_tile(tm, sX2 + b * TILE, z);
     }
-    // the Out tile stored earlier has long left shared memory: confirmed here, off the critical path,
-    // before the barrier after which the tile is written again
-    if (tid == 0) tma_wait_group_read<0>();
     publish();
 
     // ---- MMA6: partial Z2b = X2b W2
@@ -484,13 +482,13 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                ,
                )
     wait_mma();
-    // ---- OUT: Q + gamma * LN(Z2b + b2) + beta.  The CTAs of the cluster take turns storing the tile.
+    // ---- OUT: Q + gamma * LN(Z2b + b2) + beta.  Z2b is an output only: its partial tiles are summed by
+    // reduce-scatter, and every CTA normalises and stores the token rows it owns.
     {
       float z[16], b2c[8], gam[8], bet[8], q[16];
       tok_ld(tm, tmem + C::TM_Z, z);
-      csum.run(z, tid, lane);
-      const bool mine = static_cast<uint32_t>(it % kC) == rank;
-      if (mine) {
+      const bool mine = csum.reduce_scatter(z, tid);
+      if (mine) {       // whole warp pairs (the two warps of a fragment quadrant) take this branch together
         tok_ld_cols(tm, sB2, b2c);
         tok_ld_cols(tm, sGamma, gam);
         tok_ld_cols(tm, sBeta, bet);
@@ -511,7 +509,7 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             q[i1] += fmaf(gam[c], z[i1] * rs1, bet[c]);
           }
         }
-        tok_st_tile(tm, sOut, q);
+        tok_st_global(tm, p.out + (stream_id * NC + it) * 4096, q);
       }
       // the last CTA barrier of the mini-batch also takes the vote on leaving the loop: a peer can raise
       // this CTA's abort flag at any moment, and all 256 threads must see the same answer
@@ -519,10 +517,6 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       tc_fence_before_sync();
       aborted = __syncthreads_or(*abort_flag != 0) != 0;
       if (tid == 0) {
-        if (mine) {
-          tma_store_2d(&tmOut, sOut, 0, static_cast<int>((stream_id * NC + it) * 64));
-          tma_commit_group();
-        }
         if (!aborted && loads_issued < NC && loads_issued == it + kStages) {
           issue_loads(loads_issued);
           ++loads_issued;
@@ -564,8 +558,7 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   tc_fence_before_sync();
   __syncthreads();
   // no CTA leaves while a peer may still write into its shared memory (exchange area, abort flag)
-  cluster_arrive();
-  cluster_wait();
+  cluster_exit(abort_flag);
   if (warp == 0) tmem_dealloc(tmem, C::TM_COLS);
 }
 
@@ -619,6 +612,7 @@ int ttt_launch_forward_cluster(const ttt_b200_fwd_args* a, int cluster, cudaStre
   const bool want_final = a->W1_final && a->b1_final && a->W2_final && a->b2_final;
   p.W1f = want_final ? a->W1_final : nullptr;
   p.b1f = a->b1_final; p.W2f = a->W2_final; p.b2f = a->b2_final;
+  p.out = static_cast<__nv_bfloat16*>(a->Out);
   p.H = a->H; p.NC = a->NC; p.cgs = a->checkpoint_group_size; p.nck = a->num_checkpoints;
   p.drop_load = drop_load;
   p.status = status;
