@@ -249,7 +249,8 @@ def run_ours(args, rank, world, local_rank):
         step = DeviceStep(host, cgs, dev, cluster)
     Bl, Hl = b1 - b0, h1 - h0
     lib = _lib.lib()
-    cl_used = cluster or lib.ttt_b200_pick_cluster(Bl * Hl)
+    cl_used = cluster or lib.ttt_b200_pick_cluster(Bl * Hl, 1)
+    cl_fwd = cluster or lib.ttt_b200_pick_cluster(Bl * Hl, 0)
 
     sampler = ClockSampler(local_rank)
     # warm-up happens inside timed_steps; the sampler is started just before so that most of its samples
@@ -404,7 +405,7 @@ def run_ours(args, rank, world, local_rank):
                    "parallelism": (f"one problem, (batch x head) streams partitioned over {world} GPU(s): "
                                    f"{Bl} x {Hl} = {Bl * Hl} streams per GPU" if strong else
                                    f"one whole problem per GPU (replicas), {world} GPU(s)"),
-                   "ctas_per_stream": cl_used,
+                   "ctas_per_stream": {"forward": cl_fwd, "backward": cl_used},
                    "l2": "working set per step (~1.7 GB at c2 on one GPU) exceeds the 126 MB L2; no explicit flush"},
         "kernels": {"fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
                     "fwd_tflops": fwd_flop / (fwd_ms * 1e-3) / 1e12, "bwd_tflops": bwd_tf,
@@ -413,7 +414,7 @@ def run_ours(args, rank, world, local_rank):
                     "fwd_bwd_frac_of_bf16_sustained_peak": both_tf / sustained,
                     "fwd_algorithmic_gbs": fwd_bytes / (fwd_ms * 1e-3) / 1e9,
                     "bwd_algorithmic_gbs": bwd_bytes / (bwd_ms * 1e-3) / 1e9,
-                    "streams_per_gpu": Bl * Hl, "ctas_per_stream": cl_used},
+                    "streams_per_gpu": Bl * Hl, "ctas_per_stream_fwd": cl_fwd, "ctas_per_stream_bwd": cl_used},
         # checkpoint + recompute scratch traffic: checkpoints written by the forward and read by the backward,
         # scratch slots written by the recompute and read back by the sweep (bytes the kernels ask for)
         "remat_traffic": {"bytes_per_step": remat_bytes,

@@ -69,7 +69,7 @@ def load():
     lib.ttt_b200_take_status.restype = ctypes.c_int
     lib.ttt_b200_version.argtypes = []
     lib.ttt_b200_version.restype = ctypes.c_int
-    lib.ttt_b200_pick_cluster.argtypes = [ctypes.c_int]
+    lib.ttt_b200_pick_cluster.argtypes = [ctypes.c_int, ctypes.c_int]
     lib.ttt_b200_pick_cluster.restype = ctypes.c_int
     lib.ttt_b200_umma_selftest.argtypes = [c_void_p, c_void_p, c_void_p] + [ctypes.c_int] * 7 + [c_void_p]
     lib.ttt_b200_umma_selftest.restype = ctypes.c_int

@@ -721,6 +721,9 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     tmem_wait_st();
     tc_fence_before_sync();   // the state columns are read by the MMAs of the first step
 
+    float dk_pend[16];          // a step's share of dK between its send and its receive
+    uint32_t dk_tag = 0;
+    int dk_row0 = -1;
     for (int j = gsz - 1; j >= 0; --j) {
       const long slot = slot0 + j;
       const int row0 = static_cast<int>(tok_rows0 + (long)(i0 + j) * 64);
@@ -784,6 +787,10 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           sDG[tid] += part_sum(1);
           sGb2[tid] += part_sum(2);
         }
+      }
+      if (dk_row0 >= 0) {     // the previous step's dK
+        if (csum.reduce_scatter_recv(dk_pend, tid, dk_tag)) tok_st_global(tm, p.dXK + static_cast<long>(dk_row0) * 64, dk_pend);
+        dk_row0 = -1;
       }
       wait_mma();
       if (tid == 0) load_big(ib1, p.sc_X2 + slot * BIG);   // W2+ is consumed (G1 was its only use): X2 for G5
@@ -852,17 +859,12 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           }
         }
       }
-      {   // dQ = go + sum over the cluster of gZ1b W1+^T: an output only, so the partial tiles are summed by
-          // reduce-scatter and every CTA stores the token rows it owns
-        float acc[16], go[16];
-        tok_ld(tm, tmem + C::TM_B, acc);
-        if (csum.reduce_scatter(acc, tid)) {
-          tok_ld_tile(tm, t_go, go);
-#pragma unroll
-          for (int q = 0; q < 16; ++q) go[q] += acc[q];
-          tok_st_global(tm, p.dXQ + static_cast<long>(row0) * 64, go);
-        }
-      }
+      // dQ = go + sum over the cluster of gZ1b W1+^T: an output only, so the partial tiles are summed by
+      // reduce-scatter and every CTA stores the token rows it owns.  The partial tile is sent now and
+      // received inside the next MMA window: nobody waits for the exchange.
+      float dq[16];
+      tok_ld(tm, tmem + C::TM_B, dq);
+      const uint32_t dq_tag = csum.reduce_scatter_send(dq, tid);
       publish();
       wait_bar(BAR_BIG + ib4);
       wait_bar(BAR_T + 4);
@@ -893,6 +895,13 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           c0 = fmaf(bf16_lo(w3), g.w, c0); c1 = fmaf(bf16_hi(w3), g.w, c1);
         }
         *reinterpret_cast<float2*>(sPart + warp * 64 + 2 * lane) = make_float2(a0 + c0, a1 + c1);
+      }
+      if (csum.reduce_scatter_recv(dq, tid, dq_tag)) {
+        float go[16];
+        tok_ld_tile(tm, t_go, go);
+#pragma unroll
+        for (int q = 0; q < 16; ++q) go[q] += dq[q];
+        tok_st_global(tm, p.dXQ + static_cast<long>(row0) * 64, go);
       }
       wait_mma();
       if (tid == 0) {
@@ -1145,13 +1154,15 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                  if (NB > 1) HID_ONE(true, C::TM_S2, big(ib3), t_q, 1u, NB - 1))
       wait_mma();
       // ---- E6: dK = sum over the cluster of (share of dK + gZ1in W1^T): an output only, summed by
-      // reduce-scatter; every CTA stores the token rows it owns
+      // reduce-scatter; every CTA stores the token rows it owns.  Sent now, received inside the first MMA
+      // window of the next step (or right after the group's last step).
       {
         float acc[16];
         tok_ld(tm, tmem + C::TM_A, acc);
 #pragma unroll
-        for (int q = 0; q < 16; ++q) kp[q] += acc[q];
-        if (csum.reduce_scatter(kp, tid)) tok_st_global(tm, p.dXK + static_cast<long>(row0) * 64, kp);
+        for (int q = 0; q < 16; ++q) dk_pend[q] = kp[q] + acc[q];
+        dk_tag = csum.reduce_scatter_send(dk_pend, tid);
+        dk_row0 = row0;
       }
       aborted = publish_vote();
       // pre-update weights of this mini-batch are the post-update weights of the previous one
@@ -1163,7 +1174,9 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       if (aborted) break;
     }
     if (aborted) break;
-    if (tid == 0) tma_wait_group_read<0>();   // the last dK has left its tile (the recompute writes it again)
+    if (dk_row0 >= 0 && csum.reduce_scatter_recv(dk_pend, tid, dk_tag))      // the group's last dK
+      tok_st_global(tm, p.dXK + static_cast<long>(dk_row0) * 64, dk_pend);
+    if (tid == 0) tma_wait_group_read<0>();   // the last dV has left its tile (the recompute writes it again)
 
     // ---- park the gradient state (tensor memory -> grad_L_W*_init); the last group leaves the result
     __syncwarp();

@@ -77,9 +77,10 @@ int sm_count() {
 // How many CTAs share one stream.  The mini-batches of a stream are strictly sequential, so with fewer
 // streams than SMs the idle SMs can only help by taking a share of every stream's hidden units.  The
 // thresholds are measured (B200, 148 SMs): four CTAs per stream win whenever they all fit on the GPU at
-// once (about 12 % per mini-batch over one CTA); two CTAs per stream win up to about 100 resident CTAs
-// and lose beyond (the backward's exchanges slow down when most SMs of a GPC take part in one).
-int ttt_pick_cluster(int streams, uint32_t flags, int* cluster) {
+// once (about 12 % per mini-batch over one CTA); two CTAs per stream win in the forward whenever they fit
+// (12 %), in the backward up to about 100 resident CTAs (10 %; beyond, with both SMs of nearly every TPC
+// running the large backward, every phase of it slows down by about 15 % and the gain is gone).
+int ttt_pick_cluster(int streams, uint32_t flags, bool backward, int* cluster) {
   int forced = static_cast<int>((flags & TTT_B200_FLAG_CLUSTER_MASK) >> TTT_B200_FLAG_CLUSTER_SHIFT);
   if (forced == 0) {
     static const int env = [] {
@@ -95,7 +96,8 @@ int ttt_pick_cluster(int streams, uint32_t flags, int* cluster) {
     return TTT_B200_OK;
   }
   const int sms = sm_count();
-  *cluster = 4 * streams <= sms ? 4 : (10 * 2 * streams <= 7 * sms ? 2 : 1);
+  const int two_limit = backward ? 7 * sms / 10 : sms;
+  *cluster = 4 * streams <= sms ? 4 : (2 * streams <= two_limit ? 2 : 1);
   return TTT_B200_OK;
 }
 
@@ -208,7 +210,7 @@ extern "C" int ttt_b200_forward(const ttt_b200_fwd_args* a, void* stream_) {
   uint32_t* status = nullptr;
   if (int rc = pre_launch(&status)) return rc;
   int cluster = 1;
-  if (int rc = ttt_pick_cluster(a->B * a->H, a->flags, &cluster)) return rc;
+  if (int rc = ttt_pick_cluster(a->B * a->H, a->flags, false, &cluster)) return rc;
   const int drop = (a->flags & TTT_B200_FLAG_TEST_LOST_LOAD) ? (a->NC > 1 ? 1 : 0) : -1;
   if (int rc = cluster == 1 ? ttt_launch_forward(a, stream, status, wait_limit_ns(), drop)
                             : ttt_launch_forward_cluster(a, cluster, stream, status, wait_limit_ns(), drop))
@@ -238,7 +240,7 @@ extern "C" int ttt_b200_backward(const ttt_b200_bwd_args* a, void* stream_) {
   uint32_t* status = nullptr;
   if (int rc = pre_launch(&status)) return rc;
   int cluster = 1;
-  if (int rc = ttt_pick_cluster(a->B * a->H, a->flags, &cluster)) return rc;
+  if (int rc = ttt_pick_cluster(a->B * a->H, a->flags, true, &cluster)) return rc;
   // the hook drops the recompute inputs of the last group's second mini-batch (its only one if it has one)
   const int last0 = (a->num_checkpoints - 1) * a->checkpoint_group_size;
   const int drop = (a->flags & TTT_B200_FLAG_TEST_LOST_LOAD) ? (last0 + 1 < a->NC ? last0 + 1 : last0) : -1;
@@ -259,8 +261,8 @@ extern "C" int ttt_b200_take_status(void) {
 
 extern "C" int ttt_b200_version(void) { return 1001; }
 
-extern "C" int ttt_b200_pick_cluster(int streams) {
+extern "C" int ttt_b200_pick_cluster(int streams, int backward) {
   int c = 1;
-  if (streams < 1 || ttt_pick_cluster(streams, 0u, &c) != TTT_B200_OK) return -1;
+  if (streams < 1 || ttt_pick_cluster(streams, 0u, backward != 0, &c) != TTT_B200_OK) return -1;
   return c;
 }

@@ -249,7 +249,11 @@ struct ClusterSum {
   // the SM-to-SM network.  Uses the same buffers, barriers and reduction counter as run().
   // Returns true in the threads that now hold finished rows.
   static __device__ __forceinline__ uint32_t row_owner(int tid) { return (static_cast<uint32_t>(tid >> 5) & 3u) * kC / 4u; }
-  __device__ __forceinline__ bool reduce_scatter(float (&v)[16], int tid) {
+  // The two halves may be separated by other work (the result of such a sum is only stored): the send
+  // right after the partial tile has been read, the receive inside a later MMA window.  `tag` carries
+  // the buffer and parity from one to the other.  No other reduction may start in between (the buffers
+  // alternate per reduction).
+  __device__ __forceinline__ uint32_t reduce_scatter_send(const float (&v)[16], int tid) {
     const uint32_t b = n & 1u, par = (n >> 1) & 1u;
     ++n;
     const uint32_t boff = b * kBufBytes + static_cast<uint32_t>(tid) * 16u;
@@ -263,8 +267,13 @@ struct ClusterSum {
       for (int j = 0; j < 4; ++j)
         st_async_f4(dst + j * 4096u, rbar, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
     }
+    return b | (par << 1);
+  }
+  __device__ __forceinline__ bool reduce_scatter_recv(float (&v)[16], int tid, uint32_t tag) {
+    const uint32_t b = tag & 1u, par = tag >> 1;
+    const uint32_t boff = b * kBufBytes + static_cast<uint32_t>(tid) * 16u;
     mbar_wait_cl(&bars[b], par, abort_flag, limit, kC);
-    if (owner != rank) return false;
+    if (row_owner(tid) != rank) return false;
     const float4* src = reinterpret_cast<const float4*>(bufp + boff);
     if constexpr (kC == 2) {
 #pragma unroll
@@ -285,6 +294,10 @@ struct ClusterSum {
       }
     }
     return true;
+  }
+  __device__ __forceinline__ bool reduce_scatter(float (&v)[16], int tid) {
+    const uint32_t tag = reduce_scatter_send(v, tid);
+    return reduce_scatter_recv(v, tid, tag);
   }
   __device__ __forceinline__ void run_with_extras(float (&v)[16], float& e0, float& e1, int tid, int lane) {
     run_impl<true>(v, e0, e1, tid, lane);

@@ -284,6 +284,40 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     __syncwarp();                     \
   }
 
+  // the output tile of a mini-batch between the send and the receive of its reduce-scatter
+  float zo[16];
+  uint32_t zo_tag = 0;
+  int zo_it = -1;
+  auto finish_out = [&]() {
+    const bool mine = csum.reduce_scatter_recv(zo, tid, zo_tag);
+    if (mine) {       // whole warp pairs (the two warps of a fragment quadrant) take this branch together
+      const uint8_t* sQp = smem + C::OFF_Q + (zo_it % kStages) * TILE;
+      float b2c[8], gam[8], bet[8], q[16];
+      tok_ld_cols(tm, sB2, b2c);
+      tok_ld_cols(tm, sGamma, gam);
+      tok_ld_cols(tm, sBeta, bet);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        zo[4 * j] += b2c[2 * j]; zo[4 * j + 1] += b2c[2 * j + 1];
+        zo[4 * j + 2] += b2c[2 * j]; zo[4 * j + 3] += b2c[2 * j + 1];
+      }
+      float rs0, rs1;
+      tok_ld_tile(tm, sQp, q);
+      tok_layernorm(tm, zo, TTT_LN_EPS, sXch, rs0, rs1);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int i0 = 4 * j + e, i1 = 4 * j + 2 + e, c = 2 * j + e;
+          q[i0] += fmaf(gam[c], zo[i0] * rs0, bet[c]);
+          q[i1] += fmaf(gam[c], zo[i1] * rs1, bet[c]);
+        }
+      }
+      tok_st_global(tm, p.out + (stream_id * NC + zo_it) * 4096, q);
+    }
+    zo_it = -1;
+  };
+
   int it = 0;
   bool aborted = false;
   for (; it < NC; ++it) {
@@ -312,6 +346,7 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       store_b1(p.b1c + ckc * 256);
       if (rank == 0 && tid < 64) p.b2c[ckc * 64 + tid] = sB2[tid];   // before this mini-batch's column sums reach b2
     }
+    if (zo_it >= 0) finish_out();          // the previous mini-batch's output, with the b2 it saw
     wait_mma();
     // ---- EPI1: X2^T = gelu(Z1^T + b1), G' = gelu'(Z1^T + b1)
 #pragma unroll
@@ -330,6 +365,12 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       tok_st_tile(tm, sGP + b * TILE, gp);
     }
     publish();
+    // the previous mini-batch's Q tile has been read by every warp (its output is finished): its stage takes
+    // the loads of the mini-batch two ahead
+    if (tid == 0 && it >= 1 && loads_issued < NC && loads_issued == it - 1 + kStages) {
+      issue_loads(loads_issued);
+      ++loads_issued;
+    }
 
     // ---- MMA2: partial Z2 = X2 W2 over this CTA's hidden units
     TTT_ISSUE4(mma_tok_partial(tmem + C::TM_Z, smem_u32(sX2), smem_u32(sW2), NB),
@@ -483,49 +524,20 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                )
     wait_mma();
     // ---- OUT: Q + gamma * LN(Z2b + b2) + beta.  Z2b is an output only: its partial tiles are summed by
-    // reduce-scatter, and every CTA normalises and stores the token rows it owns.
-    {
-      float z[16], b2c[8], gam[8], bet[8], q[16];
-      tok_ld(tm, tmem + C::TM_Z, z);
-      const bool mine = csum.reduce_scatter(z, tid);
-      if (mine) {       // whole warp pairs (the two warps of a fragment quadrant) take this branch together
-        tok_ld_cols(tm, sB2, b2c);
-        tok_ld_cols(tm, sGamma, gam);
-        tok_ld_cols(tm, sBeta, bet);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          z[4 * j] += b2c[2 * j]; z[4 * j + 1] += b2c[2 * j + 1];
-          z[4 * j + 2] += b2c[2 * j]; z[4 * j + 3] += b2c[2 * j + 1];
-        }
-        float rs0, rs1;
-        tok_ld_tile(tm, sQ, q);
-        tok_layernorm(tm, z, TTT_LN_EPS, sXch, rs0, rs1);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int i0 = 4 * j + e, i1 = 4 * j + 2 + e, c = 2 * j + e;
-            q[i0] += fmaf(gam[c], z[i0] * rs0, bet[c]);
-            q[i1] += fmaf(gam[c], z[i1] * rs1, bet[c]);
-          }
-        }
-        tok_st_global(tm, p.out + (stream_id * NC + it) * 4096, q);
-      }
-      // the last CTA barrier of the mini-batch also takes the vote on leaving the loop: a peer can raise
-      // this CTA's abort flag at any moment, and all 256 threads must see the same answer
-      fence_proxy_async_smem();
-      tc_fence_before_sync();
-      aborted = __syncthreads_or(*abort_flag != 0) != 0;
-      if (tid == 0) {
-        if (!aborted && loads_issued < NC && loads_issued == it + kStages) {
-          issue_loads(loads_issued);
-          ++loads_issued;
-        }
-      }
-    }
+    // reduce-scatter, and every CTA normalises and stores the token rows it owns.  The partial tile is
+    // sent now; it is received, normalised and stored inside the first MMA window of the next mini-batch.
+    tok_ld(tm, tmem + C::TM_Z, zo);
+    zo_tag = csum.reduce_scatter_send(zo, tid);
+    zo_it = it;
+    // the last CTA barrier of the mini-batch also takes the vote on leaving the loop: a peer can raise
+    // this CTA's abort flag at any moment, and all 256 threads must see the same answer
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    aborted = __syncthreads_or(*abort_flag != 0) != 0;
     if (aborted) break;
   }
 #undef TTT_ISSUE4
+  if (!aborted && zo_it >= 0) finish_out();      // the last mini-batch's output
 
   // ---- epilogue: optional final state, then teardown
   if (!aborted && p.W1f != nullptr) {
