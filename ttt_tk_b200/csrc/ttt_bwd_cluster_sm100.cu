@@ -57,8 +57,8 @@ struct Cfg {
   static constexpr uint32_t HB = NB * TILE;            // bytes of an [R][64] bf16 tile
   using Sum = ClusterSum<kC, 18432>;                   // a 64 x 64 tile, optionally with two extra values per thread
   static constexpr uint32_t OFF_BIG = 0;               // 5 hidden-major buffers
-  static constexpr uint32_t OFF_T = 5 * HB;            // 7 token tiles of 8 KB
-  static constexpr uint32_t OFF_SUM = OFF_T + 7 * TILE;
+  static constexpr uint32_t OFF_T = 5 * HB;            // 8 token tiles of 8 KB
+  static constexpr uint32_t OFF_SUM = OFF_T + 8 * TILE;
   static constexpr uint32_t OFF_B2 = OFF_SUM + Sum::kBytes;
   static constexpr uint32_t OFF_GB2 = OFF_B2 + 256;
   static constexpr uint32_t OFF_GAMMA = OFF_GB2 + 256;
@@ -398,6 +398,32 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     }
 
     // ================================================================== recompute the group
+    float zb[16];             // a mini-batch's partial Z2b between the send and the receive of its sum
+    uint32_t zb_tag = 0;
+    long zb_slot = -1;
+    uint8_t* tXln = tile(7);  // x_hat_ln on its way to the scratch slot
+    auto finish_xhln = [&]() {
+      csum.allreduce_recv(zb, tid, zb_tag);
+      float b2c[8];
+      tok_ld_cols(tm, sB2, b2c);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        zb[4 * q] += b2c[2 * q]; zb[4 * q + 1] += b2c[2 * q + 1];
+        zb[4 * q + 2] += b2c[2 * q]; zb[4 * q + 3] += b2c[2 * q + 1];
+      }
+      float rs0, rs1;
+      tok_layernorm(tm, zb, TTT_LN_EPS, sXch, rs0, rs1);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        zb[4 * q] *= rs0; zb[4 * q + 1] *= rs0;
+        zb[4 * q + 2] *= rs1; zb[4 * q + 3] *= rs1;
+      }
+      tok_st_tile(tm, tXln, zb);
+      if (row_writer) {
+        p.sc_sigln[zb_slot * 64 + tm.r0] = rs0;
+        p.sc_sigln[zb_slot * 64 + tm.r1] = rs1;
+      }
+    };
     for (int j = 0; j < gsz; ++j) {
       const int s = j & 1;
       const long slot = slot0 + j;
@@ -412,6 +438,11 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                  if (NB > 1) HID_ONE(false, C::TM_A, bW1, sK, 0u, NB - 1),
                  ,
                  )
+      const long xhln_slot = zb_slot;          // the previous mini-batch's x_hat_ln, with the b2 it saw
+      if (zb_slot >= 0) {
+        finish_xhln();
+        zb_slot = -1;
+      }
       wait_mma();
 #pragma unroll
       for (int b = 0; b < NB; ++b) {
@@ -433,7 +464,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       }
       publish();
       if (tid == 0) {
-        tma_wait_group_read<0>();     // the previous mini-batch's x_hat_ln has left the U2 tile (rewritten after MMA2)
+        if (xhln_slot >= 0) bulk_store_1d(p.sc_xhln + xhln_slot * TILE, tXln, TILE);
         store_big(p.sc_X2 + slot * BIG, bX2);
         store_big(p.sc_Z1 + slot * BIG, bZ1);
         tma_commit_group();
@@ -624,39 +655,26 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                  ,
                  )
       wait_mma();
-      {
-        float z[16], b2c[8];
-        tok_ld(tm, tmem + C::TM_B, z);
-        cluster_sum(z);
-        tok_ld_cols(tm, sB2, b2c);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          z[4 * q] += b2c[2 * q]; z[4 * q + 1] += b2c[2 * q + 1];
-          z[4 * q + 2] += b2c[2 * q]; z[4 * q + 3] += b2c[2 * q + 1];
-        }
-        float rs0, rs1;
-        tok_layernorm(tm, z, TTT_LN_EPS, sXch, rs0, rs1);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          z[4 * q] *= rs0; z[4 * q + 1] *= rs0;
-          z[4 * q + 2] *= rs1; z[4 * q + 3] *= rs1;
-        }
-        tok_st_tile(tm, tU2, z);      // the U2 tile is dead since MMA4; x_hat_ln leaves through it
-        if (row_writer) {
-          p.sc_sigln[slot * 64 + tm.r0] = rs0;
-          p.sc_sigln[slot * 64 + tm.r1] = rs1;
-        }
-      }
+      // Z2b only feeds the output LayerNorm statistics the sweep will read back from scratch: nothing in the
+      // recompute waits for it.  Its partial tile is sent now; the sum is received and normalised inside the
+      // first MMA window of the next mini-batch (or right after the group's last one).
+      tok_ld(tm, tmem + C::TM_B, zb);
+      zb_tag = csum.allreduce_send(zb, tid);
+      zb_slot = slot;
       if (tid == 0) tma_wait_group_read<0>();   // every big image of this mini-batch has left shared memory
       aborted = publish_vote();
-      if (tid == 0) {
-        bulk_store_1d(p.sc_xhln + slot * TILE, tU2, TILE);
-        tma_commit_group();
-        if (j + 2 < gsz && !aborted) issue_inputs(j + 2);
-      }
+      if (tid == 0 && j + 2 < gsz && !aborted) issue_inputs(j + 2);
       if (aborted) break;
     }
     if (aborted) break;
+    {   // the group's last x_hat_ln
+      finish_xhln();
+      publish();
+      if (tid == 0) {
+        bulk_store_1d(p.sc_xhln + zb_slot * TILE, tXln, TILE);
+        tma_commit_group();
+      }
+    }
 
     // ================================================================== reverse sweep
     // buffer roles: ib0 = W1+ (bf16), ib1 = W2+, the other three free

@@ -302,6 +302,48 @@ struct ClusterSum {
   __device__ __forceinline__ void run_with_extras(float (&v)[16], float& e0, float& e1, int tid, int lane) {
     run_impl<true>(v, e0, e1, tid, lane);
   }
+  // run() in two halves, for a sum whose result nothing on the critical path waits for (same rules as
+  // the halves of reduce_scatter)
+  __device__ __forceinline__ uint32_t allreduce_send(const float (&v)[16], int tid) {
+    const uint32_t b = n & 1u, par = (n >> 1) & 1u;
+    ++n;
+    const uint32_t boff = b * kBufBytes + static_cast<uint32_t>(tid) * 16u;
+    if (tid == 0) mbar_expect_tx(&bars[b], (kC - 1) * 16384u);
+#pragma unroll
+    for (int s = 0; s < kC - 1; ++s) {
+      const uint32_t peer = rank ^ static_cast<uint32_t>(s + 1);
+      const uint32_t dst = mapa(smem_u32(bufp) + boff + s * kSlotBytes, peer);
+      const uint32_t rbar = mapa(smem_u32(&bars[b]), peer);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        st_async_f4(dst + j * 4096u, rbar, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    }
+    return b | (par << 1);
+  }
+  __device__ __forceinline__ void allreduce_recv(float (&v)[16], int tid, uint32_t tag) {
+    const uint32_t b = tag & 1u, par = tag >> 1;
+    const uint32_t boff = b * kBufBytes + static_cast<uint32_t>(tid) * 16u;
+    mbar_wait_cl(&bars[b], par, abort_flag, limit, kC);
+    const float4* src = reinterpret_cast<const float4*>(bufp + boff);
+    if constexpr (kC == 2) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float4 p = src[j * 256];
+        v[4 * j] += p.x; v[4 * j + 1] += p.y; v[4 * j + 2] += p.z; v[4 * j + 3] += p.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float4 p1 = src[j * 256];
+        const float4 p2 = src[(kSlotBytes / 16) + j * 256];
+        const float4 p3 = src[2 * (kSlotBytes / 16) + j * 256];
+        v[4 * j] = (v[4 * j] + p1.x) + (p2.x + p3.x);
+        v[4 * j + 1] = (v[4 * j + 1] + p1.y) + (p2.y + p3.y);
+        v[4 * j + 2] = (v[4 * j + 2] + p1.z) + (p2.z + p3.z);
+        v[4 * j + 3] = (v[4 * j + 3] + p1.w) + (p2.w + p3.w);
+      }
+    }
+  }
 };
 
 // Exit of a cluster kernel (all threads of all CTAs call it).  On the ordinary path every byte a peer
