@@ -39,6 +39,9 @@ using namespace tttcl;
 namespace {
 
 constexpr int kThreads = 256;
+// The thread that issues the bulk copies and waits for their completion is not one of the four MMA issuers
+// (lane 0 of warps 0..3): its bookkeeping between a barrier and the next MMA group stays off the issue path.
+constexpr int kProd = 128;
 
 // barrier indices
 constexpr int BAR_BIG = 0;     // +buffer index (0..4)
@@ -153,7 +156,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   volatile uint32_t* never_flag = reinterpret_cast<volatile uint32_t*>(smem + C::OFF_MISC + 8);   // stays 0
   const uint64_t limit = p.wait_limit_ns;
 
-  if (tid == 0) {
+  if (tid == kProd) {
     for (int i = 0; i < NUM_BARS; ++i) {
       uint32_t cnt = 1;
       if (i == BAR_MMA || i == BAR_DRAIN) cnt = 4;
@@ -361,7 +364,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       tma_load_2d(tV, &tmV, &bars[BAR_V], 0, static_cast<int>(tok_rows0 + (long)(i0 + j) * 64));
       pending |= 1u << BAR_V;
     };
-    if (tid == 0) {
+    if (tid == kProd) {
       issue_inputs(0);
       issue_v(0);
       if (gsz > 1) issue_inputs(1);
@@ -391,7 +394,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       tmem_wait_st();
     }
     publish();
-    if (tid == 0) {   // bf16 images of the checkpoint = pre-update weights of the group's first mini-batch
+    if (tid == kProd) {   // bf16 images of the checkpoint = pre-update weights of the group's first mini-batch
       store_big(p.sc_W1 + slot0 * 65536, bW1);
       store_big(p.sc_W2 + slot0 * 65536, bW2);
       tma_commit_group();
@@ -463,7 +466,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         tok_st_tile(tm, bZ1 + b * TILE, z);
       }
       publish();
-      if (tid == 0) {
+      if (tid == kProd) {
         if (xhln_slot >= 0) bulk_store_1d(p.sc_xhln + xhln_slot * TILE, tXln, TILE);
         store_big(p.sc_X2 + slot * BIG, bX2);
         store_big(p.sc_Z1 + slot * BIG, bZ1);
@@ -538,11 +541,11 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           p.sc_sigf[slot * 64 + tm.r1] = rs1;
         }
       }
-      if (tid == 0) tma_wait_group_read<0>();   // Z1 / X2 images have left shared memory
+      if (tid == kProd) tma_wait_group_read<0>();   // Z1 / X2 images have left shared memory
       publish();
 
       // MMA3: R^T = W2 gZ2^T
-      if (tid == 0) {
+      if (tid == kProd) {
         bulk_store_1d(p.sc_xhf + slot * TILE, tV, TILE);
         bulk_store_1d(p.sc_gZ2 + slot * TILE, tGZ2, TILE);
         tma_commit_group();
@@ -592,7 +595,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       publish();
 
       // MMA4: W1^T += U1^T K ; W2 += X2^T U2
-      if (tid == 0) {
+      if (tid == kProd) {
         tma_wait_group_read<0>();               // x_hat_fused has left the V tile
         if (j + 1 < gsz) issue_v(j + 1);
         store_big(p.sc_gZ1 + slot * BIG, bGP);
@@ -614,7 +617,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       publish();
 
       // MMA5: Z1b^T = W1+^T Q^T
-      if (tid == 0) {
+      if (tid == kProd) {
         if (j + 1 < gsz) {   // the new weights are the next mini-batch's pre-update weights
           store_big(p.sc_W1 + (slot + 1) * 65536, bW1);
           store_big(p.sc_W2 + (slot + 1) * 65536, bW2);
@@ -645,7 +648,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       publish();
 
       // MMA6: partial Z2b = X2b W2+ ; output LayerNorm statistics
-      if (tid == 0) {
+      if (tid == kProd) {
         store_big(p.sc_X2b + slot * BIG, bX2);
         store_big(p.sc_Z1b + slot * BIG, bZ1);
         tma_commit_group();
@@ -661,16 +664,16 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       tok_ld(tm, tmem + C::TM_B, zb);
       zb_tag = csum.allreduce_send(zb, tid);
       zb_slot = slot;
-      if (tid == 0) tma_wait_group_read<0>();   // every big image of this mini-batch has left shared memory
+      if (tid == kProd) tma_wait_group_read<0>();   // every big image of this mini-batch has left shared memory
       aborted = publish_vote();
-      if (tid == 0 && j + 2 < gsz && !aborted) issue_inputs(j + 2);
+      if (tid == kProd && j + 2 < gsz && !aborted) issue_inputs(j + 2);
       if (aborted) break;
     }
     if (aborted) break;
     {   // the group's last x_hat_ln
       finish_xhln();
       publish();
-      if (tid == 0) {
+      if (tid == kProd) {
         bulk_store_1d(p.sc_xhln + zb_slot * TILE, tXln, TILE);
         tma_commit_group();
       }
@@ -720,9 +723,9 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     // scratch was written partly with generic-proxy stores by all threads, partly with bulk
     // stores by thread 0: order both before the bulk (async-proxy) copies that read it back
     asm volatile("fence.proxy.async;" ::: "memory");
-    if (tid == 0) tma_wait_group<0>();
+    if (tid == kProd) tma_wait_group<0>();
     publish();
-    if (tid == 0) {
+    if (tid == kProd) {
       issue_tiles_a(gsz - 1);
       load_big(ib2, p.sc_Z1b + (slot0 + gsz - 1) * BIG);
       issue_rest(gsz - 1);
@@ -811,7 +814,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         dk_row0 = -1;
       }
       wait_mma();
-      if (tid == 0) load_big(ib1, p.sc_X2 + slot * BIG);   // W2+ is consumed (G1 was its only use): X2 for G5
+      if (tid == kProd) load_big(ib1, p.sc_X2 + slot * BIG);   // W2+ is consumed (G1 was its only use): X2 for G5
       wait_bar(BAR_BIG + ib2);
       // ---- E1: gZ1b^T = gX2b^T * gelu'(Z1b^T), in place over the gelu'(Z1_bar) tile
       {
@@ -843,7 +846,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         }
       }
       publish();
-      if (tid == 0) {   // x_hat_ln and its column sums are consumed: bring V into that tile (E4 rebuilds
+      if (tid == kProd) {   // x_hat_ln and its column sums are consumed: bring V into that tile (E4 rebuilds
                         // grad_output_fused = gamma x_hat_fused + beta - (V - K) from it)
         mbar_expect_tx(&bars[BAR_T + 1], TILE);
         tma_load_2d(t_a, &tmV, &bars[BAR_T + 1], 0, row0);
@@ -859,7 +862,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                  if (NB > 1) HID_ONE(true, C::TM_S1, big(ib2), t_q, 1u, NB - 1))
       wait_mma();
       // gZ1b is consumed: Z1 of this step comes in while E2 runs (X2_bar's buffer takes the W2 snapshot)
-      if (tid == 0) load_big(ib2, p.sc_Z1 + slot * BIG);
+      if (tid == kProd) load_big(ib2, p.sc_Z1 + slot * BIG);
       // ---- E2: bf16 snapshots of the gradient state; dQ
       {
         uint8_t* s1b = big(ib0);
@@ -922,7 +925,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         tok_st_global(tm, p.dXQ + static_cast<long>(row0) * 64, go);
       }
       wait_mma();
-      if (tid == 0) {
+      if (tid == kProd) {
         load_big(ib1, p.sc_W2 + slot * 65536);      // X2 is consumed until G14: W2 takes its buffer
         tma_wait_group_read<0>();     // dQ has left the dL/dOut tile (E4 reuses it for dV)
       }
@@ -969,7 +972,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                  if (NB > 1) HID_ONE(true, C::TM_S2, big(ib4), t_gz2, 1u, NB - 1),
                  )
       wait_mma();
-      if (tid == 0) load_big(ib4, p.sc_W1 + slot * 65536);
+      if (tid == kProd) load_big(ib4, p.sc_W1 + slot * 65536);
       wait_bar(BAR_T + 6);
       wait_bar(BAR_T + 1);   // V
       // ---- E4: second order through the fused LayerNorm + L2 gradient (token-major, all 8 warps)
@@ -1099,7 +1102,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       }
       publish();
       // G11 (+ G_W2snap U2^T) // G12
-      if (tid == 0 && (turn + 1) % kC == rank) {
+      if (tid == kProd && (turn + 1) % kC == rank) {
         tma_store_2d(&tmDV, t_go, 0, row0);
         tma_commit_group();
       }
@@ -1119,7 +1122,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         }
       }
       wait_mma();
-      if (tid == 0) {
+      if (tid == kProd) {
         // the W2 state-gradient snapshot is consumed: X2 comes back into its buffer for G14; dV has left
         // its tile, the d_gamma addends and x_hat_fused are consumed: the next step's first tiles are
         // requested now, two phases before they are needed
@@ -1162,7 +1165,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       }
       publish();
       // gelu'(Z1) is consumed: the next step's gelu'(Z1_bar) comes into its buffer
-      if (tid == 0 && j > 0) load_big(ib0, p.sc_Z1b + (slot - 1) * BIG);
+      if (tid == kProd && j > 0) load_big(ib0, p.sc_Z1b + (slot - 1) * BIG);
       wait_bar(BAR_BIG + ib4);
       wait_bar(BAR_BIG + ib3);
       // G13 (partial dK) // G15 // G14
@@ -1188,13 +1191,13 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         const int n0 = ib4, n1 = ib1, n2 = ib0, n3 = ib2, n4 = ib3;
         ib0 = n0; ib1 = n1; ib2 = n2; ib3 = n3; ib4 = n4;
       }
-      if (tid == 0 && j > 0 && !aborted) issue_rest(j - 1);
+      if (tid == kProd && j > 0 && !aborted) issue_rest(j - 1);
       if (aborted) break;
     }
     if (aborted) break;
     if (dk_row0 >= 0 && csum.reduce_scatter_recv(dk_pend, tid, dk_tag))      // the group's last dK
       tok_st_global(tm, p.dXK + static_cast<long>(dk_row0) * 64, dk_pend);
-    if (tid == 0) tma_wait_group_read<0>();   // the last dV has left its tile (the recompute writes it again)
+    if (tid == kProd) tma_wait_group_read<0>();   // the last dV has left its tile (the recompute writes it again)
 
     // ---- park the gradient state (tensor memory -> grad_L_W*_init); the last group leaves the result
     __syncwarp();
@@ -1229,7 +1232,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       p.d_beta[sid * 64 + tid] = sDB[tid];
     }
   }
-  if (tid == 0) tma_wait_group<0>();
+  if (tid == kProd) tma_wait_group<0>();
   if (aborted) {
     // everything this CTA still has in flight is waited for (bounded, not cut short by the abort flag)
     // before its shared and tensor memory go away: the tensor-core work of the four issuers ...
@@ -1237,7 +1240,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       if (elect_one()) umma_commit(&bars[BAR_DRAIN]);
       __syncwarp();
     }
-    if (tid == 0) {
+    if (tid == kProd) {
       mbar_wait_bounded(&bars[BAR_DRAIN], 0, never_flag, limit);
       // ... and its own loads
       for (int b = 0; b < 16; ++b)

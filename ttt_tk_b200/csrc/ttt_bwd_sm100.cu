@@ -52,6 +52,9 @@ using namespace tttdev;
 namespace {
 
 constexpr int kThreads = 256;
+// The thread that issues the bulk copies and waits for their completion is not one of the four MMA issuers
+// (lane 0 of warps 0..3): its bookkeeping between a barrier and the next MMA group stays off the issue path.
+constexpr int kProd = 128;
 
 // The MMAs of one phase are issued by lane 0 of warps 0..3: four instruction streams on four
 // schedulers instead of one.  Every issuer commits (an issuer without work too), so the MMA
@@ -165,7 +168,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   volatile uint32_t* never_flag = reinterpret_cast<volatile uint32_t*>(smem + OFF_MISC + 8);   // stays 0
   const uint64_t limit = p.wait_limit_ns;
 
-  if (tid == 0) {
+  if (tid == kProd) {
     for (int i = 0; i < 17; ++i) mbar_init(&bars[i], (i == BAR_MMA || i == BAR_DRAIN) ? 4 : 1);
     fence_mbar_init();
     *abort_flag = 0;
@@ -287,7 +290,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       tma_load_2d(tV, &tmV, &bars[BAR_V], 0, static_cast<int>(tok_rows0 + (long)(i0 + j) * 64));
       pending |= 1u << BAR_V;
     };
-    if (tid == 0) {
+    if (tid == kProd) {
       issue_inputs(0);
       issue_v(0);
       if (gsz > 1) issue_inputs(1);
@@ -335,7 +338,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       tmem_wait_st();
     }
     publish();
-    if (tid == 0) {   // bf16 images of the checkpoint = pre-update weights of the group's first mini-batch
+    if (tid == kProd) {   // bf16 images of the checkpoint = pre-update weights of the group's first mini-batch
       bulk_store_1d(p.sc_W1 + slot0 * 65536, bW1, BIG);
       bulk_store_1d(p.sc_W2 + slot0 * 65536, bW2, BIG);
       tma_commit_group();
@@ -380,7 +383,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
       publish();
-      if (tid == 0) {
+      if (tid == kProd) {
         tma_wait_group_read<0>();     // the previous mini-batch's x_hat_ln has left the U2 tile (rewritten after MMA2)
         bulk_store_1d(p.sc_X2 + slot * BIG, bX2, BIG);
         bulk_store_1d(p.sc_Z1 + slot * BIG, bZ1, BIG);
@@ -454,11 +457,11 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           p.sc_sigf[slot * 64 + tm.r1] = rs1;
         }
       }
-      if (tid == 0) tma_wait_group_read<0>();   // Z1 / X2 images have left shared memory
+      if (tid == kProd) tma_wait_group_read<0>();   // Z1 / X2 images have left shared memory
       publish();
 
       // MMA3: R^T = W2 gZ2^T
-      if (tid == 0) {
+      if (tid == kProd) {
         bulk_store_1d(p.sc_xhf + slot * TILE, tV, TILE);
         bulk_store_1d(p.sc_gZ2 + slot * TILE, tGZ2, TILE);
         tma_commit_group();
@@ -504,7 +507,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
 
       // MMA4: W1^T += U1^T K ; W2 += X2^T U2
-      if (tid == 0) {
+      if (tid == kProd) {
         tma_wait_group_read<0>();               // x_hat_fused has left the V tile
         if (j + 1 < gsz) issue_v(j + 1);
         bulk_store_1d(p.sc_gZ1 + slot * BIG, bGP, BIG);
@@ -545,7 +548,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
 
       // MMA5: Z1b^T = W1+^T Q^T
-      if (tid == 0) {
+      if (tid == kProd) {
         if (j + 1 < gsz) {   // the new weights are the next mini-batch's pre-update weights
           bulk_store_1d(p.sc_W1 + (slot + 1) * 65536, bW1, BIG);
           bulk_store_1d(p.sc_W2 + (slot + 1) * 65536, bW2, BIG);
@@ -580,7 +583,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       publish();
 
       // MMA6: Z2b = X2b W2+ ; output LayerNorm statistics
-      if (tid == 0) {
+      if (tid == kProd) {
         bulk_store_1d(p.sc_X2b + slot * BIG, bX2, BIG);
         bulk_store_1d(p.sc_Z1b + slot * BIG, bZ1, BIG);
         tma_commit_group();
@@ -612,9 +615,9 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           p.sc_sigln[slot * 64 + tm.r1] = rs1;
         }
       }
-      if (tid == 0) tma_wait_group_read<0>();   // every big image of this mini-batch has left shared memory
+      if (tid == kProd) tma_wait_group_read<0>();   // every big image of this mini-batch has left shared memory
       publish();
-      if (tid == 0) {
+      if (tid == kProd) {
         bulk_store_1d(p.sc_xhln + slot * TILE, tU2, TILE);
         tma_commit_group();
         if (j + 2 < gsz && !*abort_flag) issue_inputs(j + 2);
@@ -671,9 +674,9 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // scratch was written partly with generic-proxy stores by all threads, partly with bulk
     // stores by thread 0: order both before the bulk (async-proxy) copies that read it back
     asm volatile("fence.proxy.async;" ::: "memory");
-    if (tid == 0) tma_wait_group<0>();
+    if (tid == kProd) tma_wait_group<0>();
     publish();
-    if (tid == 0) {
+    if (tid == kProd) {
       issue_tiles_a(gsz - 1);
       load_big(ib2, p.sc_Z1b + (slot0 + gsz - 1) * BIG);
       issue_rest(gsz - 1);
@@ -768,7 +771,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
       wait_mma();
-      if (tid == 0) load_big(ib1, p.sc_X2 + slot * BIG);   // W2+ is consumed (G1 was its only use): X2 for G5
+      if (tid == kProd) load_big(ib1, p.sc_X2 + slot * BIG);   // W2+ is consumed (G1 was its only use): X2 for G5
       wait_bar(BAR_BIG + ib2);
       // ---- E1: gZ1b^T = gX2b^T * gelu'(Z1b^T), in place over Z1b^T
       {
@@ -795,7 +798,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         Gb1 += bsum;
       }
       publish();
-      if (tid == 0) {   // x_hat_ln and its column sums are consumed: bring V into that tile (E4 rebuilds
+      if (tid == kProd) {   // x_hat_ln and its column sums are consumed: bring V into that tile (E4 rebuilds
                         // grad_output_fused = gamma x_hat_fused + beta - (V - K) from it)
         mbar_expect_tx(&bars[BAR_T + 1], TILE);
         tma_load_2d(t_a, &tmV, &bars[BAR_T + 1], 0, row0);
@@ -811,7 +814,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 mma_hidden_half(tmem + TM_S1, smem_u32(big(ib2)), smem_u32(t_q), true, true, 1))
       wait_mma();
       // gZ1b is consumed: Z1 of this step comes in while E2 runs (X2_bar's buffer takes the W2 snapshot)
-      if (tid == 0) load_big(ib2, p.sc_Z1 + slot * BIG);
+      if (tid == kProd) load_big(ib2, p.sc_Z1 + slot * BIG);
       // ---- E2: bf16 snapshots of the gradient state; dQ
       {
         uint8_t* s1b = big(ib0);
@@ -844,7 +847,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tok_st_tile(tm, t_go, go);
       }
       publish();
-      if (tid == 0) {
+      if (tid == kProd) {
         tma_store_2d(&tmDQ, t_go, 0, row0);
         tma_commit_group();
       }
@@ -879,7 +882,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         *reinterpret_cast<float2*>(sPart + warp * 64 + 2 * lane) = make_float2(a0 + c0, a1 + c1);
       }
       wait_mma();
-      if (tid == 0) {
+      if (tid == kProd) {
         load_big(ib1, p.sc_W2 + slot * 65536);      // X2 is consumed until G14: W2 takes its buffer
         tma_wait_group_read<0>();     // dQ has left the dL/dOut tile (E4 reuses it for dV)
       }
@@ -926,7 +929,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 mma_hidden_half(tmem + TM_S2, smem_u32(big(ib4)), smem_u32(t_gz2), true, true, 1),
                 )
       wait_mma();
-      if (tid == 0) load_big(ib4, p.sc_W1 + slot * 65536);
+      if (tid == kProd) load_big(ib4, p.sc_W1 + slot * 65536);
       wait_bar(BAR_T + 6);
       wait_bar(BAR_T + 1);   // grad_output_fused
       // ---- E4: second order through the fused LayerNorm + L2 gradient (token-major, all 8 warps)
@@ -1040,7 +1043,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       // G11
       // + G_W2snap U2^T
       // G12
-      if (tid == 0) {
+      if (tid == kProd) {
         tma_store_2d(&tmDV, t_go, 0, row0);
         tma_commit_group();
       }
@@ -1060,7 +1063,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
       wait_mma();
-      if (tid == 0) {
+      if (tid == kProd) {
         // the W2 state-gradient snapshot is consumed: X2 comes back into its buffer for G14 (it lands while
         // E5 runs); dV has left its tile, the d_gamma addends and x_hat_fused are consumed: the next step's
         // first tiles are requested now, two phases before they are needed
@@ -1098,7 +1101,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       publish();
       // gelu'(Z1) is consumed: the next step's gelu'(Z1_bar) comes into its buffer
-      if (tid == 0 && j > 0) load_big(ib0, p.sc_Z1b + (slot - 1) * BIG);
+      if (tid == kProd && j > 0) load_big(ib0, p.sc_Z1b + (slot - 1) * BIG);
       wait_bar(BAR_BIG + ib4);
       wait_bar(BAR_BIG + ib3);
       // G13 // G15 // G14
@@ -1117,7 +1120,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tok_st_tile(tm, t_gz2, kp);
       }
       publish();
-      if (tid == 0) {
+      if (tid == kProd) {
         tma_store_2d(&tmDK, t_gz2, 0, row0);
         tma_commit_group();
       }
@@ -1126,11 +1129,11 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const int n0 = ib4, n1 = ib1, n2 = ib0, n3 = ib2, n4 = ib3;
         ib0 = n0; ib1 = n1; ib2 = n2; ib3 = n3; ib4 = n4;
       }
-      if (tid == 0 && j > 0 && !*abort_flag) issue_rest(j - 1);
+      if (tid == kProd && j > 0 && !*abort_flag) issue_rest(j - 1);
       if (*abort_flag) { aborted = true; break; }
     }
     if (aborted) break;
-    if (tid == 0) tma_wait_group_read<0>();   // the last dK has left its tile (the recompute writes it again)
+    if (tid == kProd) tma_wait_group_read<0>();   // the last dK has left its tile (the recompute writes it again)
 
     // ---- park the gradient state (tensor memory -> grad_L_W*_init); the last group leaves the result
     {
@@ -1163,7 +1166,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       p.d_beta[sid * 64 + tid] = sDB[tid];
     }
   }
-  if (tid == 0) tma_wait_group<0>();
+  if (tid == kProd) tma_wait_group<0>();
   if (aborted) {
     // everything this CTA still has in flight is waited for (bounded, not cut short by the abort flag)
     // before its shared and tensor memory go away: the tensor-core work of the four issuers ...
@@ -1171,7 +1174,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       if (elect_one()) umma_commit(&bars[BAR_DRAIN]);
       __syncwarp();
     }
-    if (tid == 0) {
+    if (tid == kProd) {
       mbar_wait_bounded(&bars[BAR_DRAIN], 0, never_flag, limit);
       // ... and its own loads
       for (int b = 0; b < 16; ++b)

@@ -32,6 +32,9 @@ namespace {
 
 constexpr int kStages = 3;
 constexpr int kThreads = 256;
+// The thread that issues the bulk copies and waits for their completion is not one of the four MMA issuers
+// (lane 0 of warps 0..3): its bookkeeping between a barrier and the next MMA group stays off the issue path.
+constexpr int kProd = 128;
 
 template <int kC>
 struct Cfg {
@@ -131,7 +134,7 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   const uint64_t limit = p.wait_limit_ns;
   const int NC = p.NC;
 
-  if (tid == 0) {
+  if (tid == kProd) {
     for (int s = 0; s < kStages; ++s) mbar_init(&full[s], 1);
     mbar_init(mma_bar, 4);
     mbar_init(&sum_bars[0], C::Sum::kArrivals);
@@ -181,7 +184,7 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     bulk_load_1d(smem + C::OFF_ETA + s * 128, p.eta + (stream_id * NC + i) * 64, 128, &full[s]);
   };
   int loads_issued = 0;
-  if (tid == 0) {
+  if (tid == kProd) {
     for (; loads_issued < kStages && loads_issued < NC; ++loads_issued) issue_loads(loads_issued);
   }
 
@@ -367,7 +370,7 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     publish();
     // the previous mini-batch's Q tile has been read by every warp (its output is finished): its stage takes
     // the loads of the mini-batch two ahead
-    if (tid == 0 && it >= 1 && loads_issued < NC && loads_issued == it - 1 + kStages) {
+    if (tid == kProd && it >= 1 && loads_issued < NC && loads_issued == it - 1 + kStages) {
       issue_loads(loads_issued);
       ++loads_issued;
     }
@@ -556,7 +559,7 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       if (elect_one()) umma_commit(drain_bar);
       __syncwarp();
     }
-    if (tid == 0) {
+    if (tid == kProd) {
       mbar_wait_bounded(drain_bar, 0, never_flag, limit);
       // ... and its own loads
       for (int j = it; j < loads_issued; ++j) {
@@ -566,7 +569,7 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       atomicExch(p.status, static_cast<uint32_t>(TTT_B200_ERR_TIMEOUT));
     }
   }
-  if (tid == 0) tma_wait_group<0>();
+  if (tid == kProd) tma_wait_group<0>();
   tc_fence_before_sync();
   __syncthreads();
   // no CTA leaves while a peer may still write into its shared memory (exchange area, abort flag)

@@ -36,6 +36,9 @@ namespace {
 
 constexpr int kStages = 3;
 constexpr int kThreads = 256;
+// The thread that issues the bulk copies and waits for their completion is not one of the four MMA issuers
+// (lane 0 of warps 0..3): its bookkeeping between a barrier and the next MMA group stays off the issue path.
+constexpr int kProd = 128;
 
 constexpr uint32_t OFF_K = 0;
 constexpr uint32_t OFF_V = OFF_K + kStages * TILE;
@@ -138,7 +141,7 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const uint64_t limit = p.wait_limit_ns;
   const int NC = p.NC;
 
-  if (tid == 0) {
+  if (tid == kProd) {
     for (int s = 0; s < kStages; ++s) mbar_init(&full[s], 1);
     mbar_init(mma_bar, 4);
     mbar_init(drain_bar, 4);
@@ -175,7 +178,7 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     bulk_load_1d(smem + OFF_ETA + s * 128, p.eta + (stream_id * NC + i) * 64, 128, &full[s]);
   };
   int loads_issued = 0;
-  if (tid == 0) {
+  if (tid == kProd) {
     for (; loads_issued < kStages && loads_issued < NC; ++loads_issued) issue_loads(loads_issued);
   }
 
@@ -452,7 +455,7 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
     // the Out tile stored earlier has long left shared memory: confirmed here, off the critical path,
     // before the barrier after which the tile is written again
-    if (tid == 0) tma_wait_group_read<0>();
+    if (tid == kProd) tma_wait_group_read<0>();
     publish();
 
     // ---- MMA6: Z2b = X2b W2
@@ -488,7 +491,7 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       tok_st_tile(tm, sOut, q);
     }
     publish();
-    if (tid == 0) {
+    if (tid == kProd) {
       tma_store_2d(&tmOut, sOut, 0, static_cast<int>((stream_id * NC + it) * 64));
       tma_commit_group();
       if (!*abort_flag && loads_issued < NC && loads_issued == it + kStages) {
@@ -512,7 +515,7 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       if (elect_one()) umma_commit(drain_bar);
       __syncwarp();
     }
-    if (tid == 0) {
+    if (tid == kProd) {
       mbar_wait_bounded(drain_bar, 0, never_flag, limit);
       // ... and its own loads
       for (int j = it; j < loads_issued; ++j) {
@@ -522,7 +525,7 @@ ttt_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       atomicExch(p.status, static_cast<uint32_t>(TTT_B200_ERR_TIMEOUT));
     }
   }
-  if (tid == 0) tma_wait_group<0>();
+  if (tid == kProd) tma_wait_group<0>();
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, TM_COLS);
