@@ -43,11 +43,13 @@ WORKLOADS = {
     "c4": (64, 24, 64, 16, "configs[4] shape run fwd+bwd on one GPU, B=64 H=24 seq=4096 (NC=64) cgs=16"),
     "small": (1, 8, 16, 4, "small case, B=1 H=8 seq=1024 cgs=4"),
     "prof": (4, 32, 16, 8, "profiling case: configs[2] streams (B=4 H=32) at seq=1024 (NC=16) cgs=8"),
+    "profc": (1, 32, 16, 8, "profiling case of the cluster kernels: 32 streams (B=1 H=32) at seq=1024 (NC=16) cgs=8"),
+    "glue": (4, 32, 128, 8, "layer-side kernels at the configs[2] shape: B=4 T=8192 H=32"),
 }
 U_FLOP = 2 * 64 * 64 * 256            # one GEMM unit per mini-batch per (b,h)
 FWD_U, BWD_U = 7, 22                  # algorithmic GEMM units: forward; backward (7 recompute + 15 sweep)
 STATE_BYTES = 132352                  # fp32 W1 + b1 + W2 + b2 of one (b,h)
-# DRAM bytes per (stream, mini-batch) from the ncu capture summarised in profiles/ttt_fwd_bwd_kernels_current.md
+# DRAM bytes per (stream, mini-batch) of the one-CTA kernels from an ncu capture of the `prof` workload
 # (dram__bytes_read.sum + dram__bytes_write.sum over 128 streams x 16 mini-batches); the traffic grows in
 # proportion to the number of (stream, mini-batch) pairs, so a full-size launch is scaled from it.
 NCU_BWD_DRAM_BYTES_PER_MB = (583610880 + 585072384) / 2048
@@ -507,6 +509,67 @@ def run_reference(args, rank, world):
     }
 
 
+def run_glue(args):
+    """The layer-side kernels around the operator at the forward+backward configuration's shape: token
+    layout transforms (four tensors per launch), eta gate and its backward, output norm fused with the
+    unpack.  HBM-bound byte movers: achieved = algorithmic bytes (input + output) / device time, against
+    the measured copy bandwidth.  One step = all five launches."""
+    from ttt_tk_b200 import glue, layout
+    B, H, NC, _, desc = WORKLOADS["glue"]
+    T = NC * 64
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device=dev).manual_seed(0)
+    xs = [torch.randn(B, T, H * 64, device=dev, generator=g).bfloat16() for _ in range(4)]
+    ys = layout.pack_tokens(*xs)
+    logits = torch.randn(B, T, H, device=dev, generator=g).bfloat16()
+    d_eta = torch.randn(B, H, NC, 64, device=dev, generator=g).bfloat16()
+    gamma = 1 + 0.1 * torch.randn(H * 64, device=dev, generator=g)
+    beta = 0.1 * torch.randn(H * 64, device=dev, generator=g)
+    tok = xs[0].numel() * 2
+    cases = [("pack_tokens x4", lambda: layout.pack_tokens(*xs), 2 * 4 * tok),
+             ("unpack_tokens x4", lambda: layout.unpack_tokens(*ys), 2 * 4 * tok),
+             ("eta_gate", lambda: glue.eta_gate(logits, 0.1 / 64), 2 * logits.numel() * 2),
+             ("eta_gate_backward", lambda: glue.eta_gate_backward(logits, d_eta, 0.1 / 64), 3 * logits.numel() * 2),
+             ("unpack_layernorm", lambda: glue.unpack_layernorm(ys[0], gamma, beta, 1e-6), 2 * tok + 2 * H * 64 * 4)]
+    K, W = args.steps, max(args.warmup, 3)
+    sampler = ClockSampler(0)
+    out = {}
+    total_ms = 0.0
+    sampler.start()
+    for name, fn, nbytes in cases:
+        for _ in range(W):
+            fn()
+        torch.cuda.synchronize()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(K + 1)]
+        ev[0].record()
+        for i in range(K):
+            fn()
+            ev[i + 1].record()
+        torch.cuda.synchronize()
+        ms = statistics.median(ev[i].elapsed_time(ev[i + 1]) for i in range(K))
+        out[name] = {"us": ms * 1e3, "bytes": nbytes, "gbs": nbytes / ms / 1e6}
+        total_ms += ms
+    clocks = sampler.stop()
+    pk, pk_src = peaks()
+    for v in out.values():
+        v["frac_of_hbm_peak"] = v["gbs"] / pk["hbm_gbs"]
+    dom = out["pack_tokens x4"]
+    total_bytes = sum(v["bytes"] for v in out.values())
+    return {
+        "metric": "ttt_layer_glue_gb_per_s", "value": total_bytes / total_ms / 1e6, "unit": "GB/s", "n_gpus": 1,
+        "steps": K, "warmup": W, "ms_per_step": total_ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": desc, "B": B, "T": T, "H": H,
+                   "l2": "every tensor (268 MB) exceeds the 126 MB L2 except the eta tensors (2 MB each)"},
+        "kernels": out,
+        "roofline": {"kernel": "layout_kernel<pack>", "bound": "hbm", "achieved": dom["gbs"], "peak": pk["hbm_gbs"],
+                     "unit": "GB/s", "frac": dom["gbs"] / pk["hbm_gbs"], "traffic": None,
+                     "peak_source": f"{pk_src} copy bandwidth"},
+        "gpu_launches": len(cases) * K, "clocks": clocks,
+    }
+
+
 def _emit(res, out_fd):
     os.write(out_fd, (json.dumps(res) + "\n").encode())
 
@@ -544,6 +607,11 @@ def main():
         res = run_reference(args, rank, world)
         if res is not None:
             _emit(res, out_fd)
+        return
+
+    if args.workload == "glue":
+        if rank == 0:
+            _emit(run_glue(args), out_fd)
         return
 
     if world > 1:

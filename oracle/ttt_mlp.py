@@ -14,7 +14,7 @@ the algorithm of the reference's own PyTorch statement of the path:
   * GELU' / GELU''          kernels/ttt_backward/matching.py:42-55
   * LayerNorm eps = 1e-8    kernels/ttt/matching.py:75
 
-Parity pin: tests/test_oracle_vs_reference.py imports the reference's two
+Parity pin: tests/test_oracle_golden.py imports the reference's two
 `matching.py` files (when the reference tree is present) and checks every function
 here against them; tests/golden/ holds outputs of the *reference's* functions on
 seeded inputs, produced by tests/golden/make_golden.py, so the pin also holds on

@@ -10,11 +10,14 @@ import torch
 from .buffers import GRAD_NAMES, alloc_backward_buffers, alloc_checkpoints
 from .ops import ttt_backward, ttt_forward
 
+# One scratch set per (shape, device, CUDA stream): backward passes on the same stream are ordered and may
+# share it (its contents mean nothing between calls); passes on different streams could overlap on the
+# GPU and get their own.
 _scratch_cache = {}
 
 
 def _scratch(B, H, NC, cgs, device):
-    key = (B, H, cgs, str(device))
+    key = (B, H, cgs, str(device), torch.cuda.current_stream(device).cuda_stream)
     if key not in _scratch_cache:
         _scratch_cache[key] = alloc_backward_buffers(B, H, 1, cgs, device)[0]
     return _scratch_cache[key]

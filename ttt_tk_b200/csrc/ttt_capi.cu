@@ -137,17 +137,29 @@ int ttt_check_status(cudaStream_t stream) {
   return TTT_B200_OK;
 }
 
+// Encoded maps are kept in a small cache keyed on (base pointer, rows): a training loop calls the
+// operator with the same buffers step after step, and an encode costs about a hundred microseconds of
+// host time per map (the reference re-encodes 15 / 44 maps on every call: kernels/ttt/ttt.cu:655-673).
+// A map depends on nothing but its key, so a stale entry cannot exist; the cache is bounded and simply
+// overwrites its oldest entry.
 int ttt_make_tile_map(CUtensorMap* map, const void* base, uint64_t rows) {
-  {
-    std::lock_guard<std::mutex> lk(g_mu);
-    if (!g_encode) {
-      void* fn = nullptr;
-      cudaDriverEntryPointQueryResult qres;
-      cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
-      if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn)
-        return ttt_set_error(TTT_B200_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from the driver");
-      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  struct Entry { const void* base; uint64_t rows; CUtensorMap map; };
+  constexpr int kEntries = 64;
+  static Entry cache[kEntries];
+  static int used = 0, next = 0;
+  std::lock_guard<std::mutex> lk(g_mu);
+  for (int i = 0; i < used; ++i)
+    if (cache[i].base == base && cache[i].rows == rows) {
+      *map = cache[i].map;
+      return TTT_B200_OK;
     }
+  if (!g_encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn)
+      return ttt_set_error(TTT_B200_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from the driver");
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
   }
   const cuuint64_t dims[2] = {64, rows};
   const cuuint64_t strides[1] = {128};           // bytes between rows
@@ -161,6 +173,10 @@ int ttt_make_tile_map(CUtensorMap* map, const void* base, uint64_t rows) {
     std::snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
     return ttt_set_error(TTT_B200_ERR_LAUNCH, buf);
   }
+  Entry& e = cache[next];
+  e.base = base; e.rows = rows; e.map = *map;
+  next = (next + 1) % kEntries;
+  if (used < kEntries) ++used;
   return TTT_B200_OK;
 }
 

@@ -143,8 +143,8 @@ __device__ __forceinline__ float ld_elem(const uint8_t* tile, uint32_t row, uint
 #define TTT_MMA_OUTER _Pragma("unroll")
 #endif
 
-// ---- MMA issue.  One thread issues every MMA of the kernels, so the instruction stream
-// around each tcgen05.mma is kept to two integer adds: the descriptors' high words are the
+// ---- MMA issue.  Four threads (lane 0 of warps 0..3) issue the MMAs of a phase; the instruction
+// stream around each tcgen05.mma is kept to two integer adds: the descriptors' high words are the
 // same constant for every operand (stride byte offset 1024, version 1, 128-byte swizzle) and
 // the low words (start address | leading byte offset) advance by a constant per K step.
 constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);

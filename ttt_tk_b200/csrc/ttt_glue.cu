@@ -61,56 +61,58 @@ __global__ void __launch_bounds__(256) eta_gate_kernel(const __nv_bfloat16* __re
 // turn.  One warp per token: 8 lanes take one head's 128-byte row as 16-byte pieces, so one warp-wide
 // load covers 4 heads; a token's values stay in registers (packed bf16) between the statistics and the
 // normalisation; the result leaves as whole 512-byte runs of the token's row.
+// kChunks = groups of 4 heads (compile time: a token's values must stay in registers, and the kernel is
+// latency-bound unless enough warps are resident, so the register count follows the head count).
 constexpr int kMaxChunks = 16;     // H <= 64
-__global__ void __launch_bounds__(256) unpack_layernorm_kernel(const uint4* __restrict__ src, const float* __restrict__ gamma,
+template <int kChunks>
+__global__ void __launch_bounds__(256, (kChunks <= 8 ? 4 : 2)) unpack_layernorm_kernel(const uint4* __restrict__ src, const float* __restrict__ gamma,
                                                                const float* __restrict__ beta, uint4* __restrict__ dst,
                                                                float eps, long tokens, int T, int H) {
   const int lane = threadIdx.x & 31;
   const int sub = lane >> 3, piece = lane & 7;          // head within a group of 4, 16-byte piece of the row
-  const int chunks = (H + 3) >> 2;
   const long warp0 = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const long nwarps = (static_cast<long>(gridDim.x) * blockDim.x) >> 5;
   const float inv_n = 1.f / static_cast<float>(H * 64);
   for (long tok = warp0; tok < tokens; tok += nwarps) {
     const long b = tok / T, t = tok - b * T;
-    uint4 raw[kMaxChunks];
-    float sum = 0.f;
+    uint4 raw[kChunks];
 #pragma unroll
-    for (int c = 0; c < kMaxChunks; ++c) {
+    for (int c = 0; c < kChunks; ++c) {
       const int h = 4 * c + sub;
-      if (c < chunks && h < H) {
-        raw[c] = __ldcs(src + (((b * H + h) * T + t) << 3) + piece);
+      if (h < H) raw[c] = __ldcs(src + (((b * H + h) * T + t) << 3) + piece);
+    }
+    // One pass over the values for both moments, taken about a pivot (the token's first value) so that
+    // the variance does not come out of the difference of two large numbers: with d = x - pivot,
+    // mean = pivot + sum(d) / n and var = sum(d^2) / n - (sum(d) / n)^2.
+    const float pivot = __shfl_sync(0xffffffffu, __uint_as_float(raw[0].x << 16), 0);
+    float sum = 0.f, sq = 0.f;
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+      const int h = 4 * c + sub;
+      if (h < H) {
         const __nv_bfloat162* v = reinterpret_cast<const __nv_bfloat162*>(&raw[c]);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const float2 f = __bfloat1622float2(v[k]);
-          sum += f.x + f.y;
+          const float d0 = f.x - pivot, d1 = f.y - pivot;
+          sum += d0 + d1;
+          sq = fmaf(d0, d0, fmaf(d1, d1, sq));
         }
       }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    const float mean = sum * inv_n;
-    float sq = 0.f;
-#pragma unroll
-    for (int c = 0; c < kMaxChunks; ++c) {
-      const int h = 4 * c + sub;
-      if (c < chunks && h < H) {
-        const __nv_bfloat162* v = reinterpret_cast<const __nv_bfloat162*>(&raw[c]);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const float2 f = __bfloat1622float2(v[k]);
-          sq = fmaf(f.x - mean, f.x - mean, fmaf(f.y - mean, f.y - mean, sq));
-        }
-      }
+    for (int o = 16; o > 0; o >>= 1) {
+      sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      sq += __shfl_xor_sync(0xffffffffu, sq, o);
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    const float dm = sum * inv_n;
+    const float mean = pivot + dm;
+    sq = fmaxf(sq - sum * dm, 0.f);           // n * variance
     const float rstd = rsqrtf(sq * inv_n + eps);
 #pragma unroll
-    for (int c = 0; c < kMaxChunks; ++c) {
+    for (int c = 0; c < kChunks; ++c) {
       const int h = 4 * c + sub;
-      if (c < chunks && h < H) {
+      if (h < H) {
         const __nv_bfloat162* v = reinterpret_cast<const __nv_bfloat162*>(&raw[c]);
         const int f0 = h * 64 + piece * 8;
         const float4 g0 = *reinterpret_cast<const float4*>(gamma + f0), g1 = *reinterpret_cast<const float4*>(gamma + f0 + 4);
@@ -191,8 +193,20 @@ extern "C" int ttt_b200_unpack_layernorm(const void* src, const float* gamma, co
   long blocks = (tokens + 7) / 8;                     // 8 warps = 8 tokens per CTA pass
   const long cap = static_cast<long>(sms) * 8;        // a whole number of CTAs per SM
   if (blocks > cap) blocks = cap;
-  unpack_layernorm_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
-      static_cast<const uint4*>(src), gamma, beta, static_cast<uint4*>(dst), eps, tokens, T, H);
+  const int chunks = (H + 3) / 4;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+#define TTT_LN_LAUNCH(CH)                                                                                  \
+  unpack_layernorm_kernel<CH><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(                          \
+      static_cast<const uint4*>(src), gamma, beta, static_cast<uint4*>(dst), eps, tokens, T, H)
+  if (chunks <= 1) TTT_LN_LAUNCH(1);
+  else if (chunks <= 2) TTT_LN_LAUNCH(2);
+  else if (chunks <= 3) TTT_LN_LAUNCH(3);
+  else if (chunks <= 4) TTT_LN_LAUNCH(4);
+  else if (chunks <= 6) TTT_LN_LAUNCH(6);
+  else if (chunks <= 8) TTT_LN_LAUNCH(8);
+  else if (chunks <= 12) TTT_LN_LAUNCH(12);
+  else TTT_LN_LAUNCH(16);
+#undef TTT_LN_LAUNCH
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
   return TTT_B200_OK;

@@ -64,27 +64,3 @@ def unpack_tokens(*ys):
         raise ValueError("expected [B, H, NC, 64, 64]")
     outs = [torch.empty(B, NC * 64, H * 64, dtype=y.dtype, device=y.device) for _ in ys]
     return _run("ttt_b200_unpack_tokens", ys, outs, B, NC * 64, H)
-
-
-def _self_benchmark(B=4, T=8192, H=32, iters=10):
-    """Time pack / unpack of four tensors of the forward+backward configuration's shape (537 MB each way,
-    larger than L2) with CUDA events; prints GB/s of algorithmic traffic (read + write)."""
-    xs = [torch.randn(B, T, H * 64, device="cuda").bfloat16() for _ in range(4)]
-    ys = pack_tokens(*xs)
-    nbytes = 2 * 4 * xs[0].numel() * 2
-    for name, fn in (("pack_tokens x4", lambda: pack_tokens(*xs)), ("unpack_tokens x4", lambda: unpack_tokens(*ys))):
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(iters + 1)]
-        ev[0].record()
-        for i in range(iters):
-            fn()
-            ev[i + 1].record()
-        torch.cuda.synchronize()
-        ms = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(iters))[iters // 2]
-        print(f"{name}: B={B} T={T} H={H}  {ms * 1e3:.1f} us  {nbytes / ms / 1e6:.0f} GB/s")
-
-
-if __name__ == "__main__":
-    _self_benchmark()
