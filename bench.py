@@ -44,6 +44,7 @@ WORKLOADS = {
     "small": (1, 8, 16, 4, "small case, B=1 H=8 seq=1024 cgs=4"),
     "prof": (4, 32, 16, 8, "profiling case: configs[2] streams (B=4 H=32) at seq=1024 (NC=16) cgs=8"),
     "profc": (1, 32, 16, 8, "profiling case of the cluster kernels: 32 streams (B=1 H=32) at seq=1024 (NC=16) cgs=8"),
+    "profc2": (2, 32, 16, 8, "profiling case with 64 streams (B=2 H=32) at seq=1024 (NC=16) cgs=8"),
     "glue": (4, 32, 128, 8, "layer-side kernels at the configs[2] shape: B=4 T=8192 H=32"),
 }
 U_FLOP = 2 * 64 * 64 * 256            # one GEMM unit per mini-batch per (b,h)
@@ -512,8 +513,8 @@ def run_reference(args, rank, world):
 def run_glue(args):
     """The layer-side kernels around the operator at the forward+backward configuration's shape: token
     layout transforms (four tensors per launch), eta gate and its backward, output norm fused with the
-    unpack.  HBM-bound byte movers: achieved = algorithmic bytes (input + output) / device time, against
-    the measured copy bandwidth.  One step = all five launches."""
+    unpack and its backward fused with the pack.  HBM-bound byte movers: achieved = algorithmic bytes (input + output) / device time, against
+    the measured copy bandwidth.  One step = all six calls."""
     from ttt_tk_b200 import glue, layout
     B, H, NC, _, desc = WORKLOADS["glue"]
     T = NC * 64
@@ -527,11 +528,14 @@ def run_glue(args):
     gamma = 1 + 0.1 * torch.randn(H * 64, device=dev, generator=g)
     beta = 0.1 * torch.randn(H * 64, device=dev, generator=g)
     tok = xs[0].numel() * 2
+    _, stats = glue.unpack_layernorm(ys[0], gamma, beta, 1e-6, return_stats=True)
     cases = [("pack_tokens x4", lambda: layout.pack_tokens(*xs), 2 * 4 * tok),
              ("unpack_tokens x4", lambda: layout.unpack_tokens(*ys), 2 * 4 * tok),
              ("eta_gate", lambda: glue.eta_gate(logits, 0.1 / 64), 2 * logits.numel() * 2),
              ("eta_gate_backward", lambda: glue.eta_gate_backward(logits, d_eta, 0.1 / 64), 3 * logits.numel() * 2),
-             ("unpack_layernorm", lambda: glue.unpack_layernorm(ys[0], gamma, beta, 1e-6), 2 * tok + 2 * H * 64 * 4)]
+             ("unpack_layernorm", lambda: glue.unpack_layernorm(ys[0], gamma, beta, 1e-6), 2 * tok + 2 * H * 64 * 4),
+             # backward: kernel 1 reads x and dy and writes dx; kernel 2 reads x and dy again for the parameter gradients
+             ("pack_layernorm_backward", lambda: glue.pack_layernorm_backward(xs[1], ys[0], gamma, stats), 5 * tok)]
     K, W = args.steps, max(args.warmup, 3)
     sampler = ClockSampler(0)
     out = {}

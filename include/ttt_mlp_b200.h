@@ -155,7 +155,7 @@ int ttt_b200_backward(const ttt_b200_bwd_args* args, void* stream);
  * cudaMalloc fails or fragments the pool), or that cannot afford the implicit device
  * synchronisation of an allocation inside a latency-critical loop, cannot provide the sixteen
  * `*_group` scratch tensors on demand; for them the scratch is a fixed array inside the library
- * (about 40 MiB, held by every GPU that loads the library's kernels until the process exits).
+ * (about 32 MiB, held by every GPU that loads the library's kernels until the process exits).
  * Inputs, checkpoints, upstream gradients and outputs are passed as for ttt_b200_backward and
  * the results are the same.
  *   - Limit: B * H * checkpoint_group_size <= TTT_B200_NOALLOC_MAX_SLOTS; larger problems
@@ -262,9 +262,17 @@ int ttt_b200_eta_gate_backward(const void* logits, const void* grad_last_eta, vo
 /* Output norm fused with the unpack: dst[b][t][:] = gamma * LayerNorm(src[b][:][t][:]) + beta over the H*64
  * features of a token; src = the operator's Out, bf16 [B][H][T][64]; gamma, beta fp32 [H*64]; dst bf16
  * [B][T][H*64]; statistics in fp32 (biased variance, eps inside the square root); H <= 64; pointers 16-byte
- * aligned; out of place. */
-int ttt_b200_unpack_layernorm(const void* src, const float* gamma, const float* beta, void* dst, float eps, int B,
-                              int T, int H, void* stream);
+ * aligned; out of place.  `stats` (may be NULL): fp32 [B][T][2] receives (mean, 1 / std) per token for the
+ * backward. */
+int ttt_b200_unpack_layernorm(const void* src, const float* gamma, const float* beta, void* dst, float* stats,
+                              float eps, int B, int T, int H, void* stream);
+/* Its backward, fused with the pack of the gradient: from grad_y (bf16 [B][T][H*64]), x = the operator's Out
+ * (bf16 [B][H][T][64]), gamma and the forward's `stats`, writes grad_x (bf16 [B][H][T][64]: the operator's
+ * grad_L_XQW_mini_batch) and ADDS the parameter gradients into grad_gamma / grad_beta (fp32 [H*64]; the caller
+ * zero-fills them; blocks add with atomics, so their last bits can differ from run to run). */
+int ttt_b200_pack_layernorm_backward(const void* grad_y, const void* x, const float* gamma, const float* stats,
+                                     void* grad_x, float* grad_gamma, float* grad_beta, int B, int T, int H,
+                                     void* stream);
 
 #ifdef __cplusplus
 }

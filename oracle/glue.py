@@ -30,3 +30,16 @@ def unpack_layernorm(out, gamma, beta, eps=1e-6):
     B, H, NC = out.shape[:3]
     x = out.float().reshape(B, H, NC * 64, 64).permute(0, 2, 1, 3).reshape(B, NC * 64, H * 64)
     return F.layer_norm(x, (H * 64,), gamma.float().reshape(-1), beta.float().reshape(-1), eps).bfloat16()
+
+
+def pack_layernorm_backward(grad_y, out, gamma, beta, eps=1e-6):
+    """(grad_out [B, H, NC, 64, 64] bf16, grad_gamma, grad_beta fp32 [H * 64]) by autograd through the statement
+    above (in fp32, without the final bf16 rounding of y)."""
+    B, H, NC = out.shape[:3]
+    x = out.float().clone().requires_grad_(True)
+    g = gamma.float().reshape(-1).clone().requires_grad_(True)
+    bb = beta.float().reshape(-1).clone().requires_grad_(True)
+    xt = x.reshape(B, H, NC * 64, 64).permute(0, 2, 1, 3).reshape(B, NC * 64, H * 64)
+    y = F.layer_norm(xt, (H * 64,), g, bb, eps)
+    y.backward(grad_y.float())
+    return x.grad.bfloat16(), g.grad, bb.grad

@@ -48,6 +48,25 @@ def test_unpack_layernorm(B, NC, H):
     close(got, og.unpack_layernorm(out, gamma, beta, 1e-6), 2e-2)
 
 
+@pytest.mark.parametrize("B,NC,H", [(1, 1, 1), (2, 2, 3), (1, 5, 32), (2, 1, 12)])
+def test_pack_layernorm_backward(B, NC, H):
+    g = torch.Generator().manual_seed(B * 100 + NC * 10 + H + 7)
+    out = (torch.randn(B, H, NC, 64, 64, generator=g) * 1.5 + 0.3).bfloat16()
+    gamma = 1 + 0.1 * torch.randn(H * 64, generator=g)
+    beta = 0.1 * torch.randn(H * 64, generator=g)
+    dy = torch.randn(B, NC * 64, H * 64, generator=g).bfloat16()
+    y, stats = glue.unpack_layernorm(out.cuda(), gamma.cuda(), beta.cuda(), 1e-6, return_stats=True)
+    close(y, og.unpack_layernorm(out, gamma, beta, 1e-6), 2e-2)
+    d_out, d_gamma, d_beta = glue.pack_layernorm_backward(dy.cuda(), out.cuda(), gamma.cuda(), stats)
+    r_out, r_gamma, r_beta = og.pack_layernorm_backward(dy, out, gamma, beta, 1e-6)
+    assert d_out.shape == out.shape
+    # the gradient has small entries next to O(1) ones: bf16 rounding of both sides, 2 ulps + a small absolute term
+    close(d_out, r_out, 2e-3)
+    # fp32 sums over B * T tokens in a different order (and with atomics): relative L2
+    assert rel_l2(d_gamma.cpu(), r_gamma) <= 1e-4
+    assert rel_l2(d_beta.cpu(), r_beta) <= 1e-4
+
+
 def test_glue_rejects_bad_arguments():
     x = torch.zeros(1, 64, 2, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(ValueError):

@@ -45,7 +45,8 @@ class BwdNoAllocArgs(ctypes.Structure):
 
 EXPORTS = ["ttt_b200_forward", "ttt_b200_backward", "ttt_b200_backward_noalloc", "ttt_b200_last_error", "ttt_b200_take_status",
            "ttt_b200_version", "ttt_b200_pick_cluster", "ttt_b200_umma_selftest", "ttt_b200_wait_selftest", "ttt_b200_pack_tokens",
-           "ttt_b200_unpack_tokens", "ttt_b200_eta_gate", "ttt_b200_eta_gate_backward", "ttt_b200_unpack_layernorm"]
+           "ttt_b200_unpack_tokens", "ttt_b200_eta_gate", "ttt_b200_eta_gate_backward", "ttt_b200_unpack_layernorm",
+           "ttt_b200_pack_layernorm_backward"]
 
 FLAG_SYNC = 1
 FLAG_TEST_LOST_LOAD = 2
@@ -83,9 +84,11 @@ def load():
     lib.ttt_b200_eta_gate.restype = ctypes.c_int
     lib.ttt_b200_eta_gate_backward.argtypes = [c_void_p, c_void_p, c_void_p, ctypes.c_float] + [ctypes.c_int] * 3 + [c_void_p]
     lib.ttt_b200_eta_gate_backward.restype = ctypes.c_int
-    lib.ttt_b200_unpack_layernorm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_float] + \
+    lib.ttt_b200_unpack_layernorm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_float] + \
         [ctypes.c_int] * 3 + [c_void_p]
     lib.ttt_b200_unpack_layernorm.restype = ctypes.c_int
+    lib.ttt_b200_pack_layernorm_backward.argtypes = [c_void_p] * 7 + [ctypes.c_int] * 3 + [c_void_p]
+    lib.ttt_b200_pack_layernorm_backward.restype = ctypes.c_int
     return lib
 
 

@@ -113,7 +113,8 @@ struct BwdParams {
   const float* beta;
   const float* W1c; const float* b1c; const float* W2c; const float* b2c;
   // scratch
-  uint8_t* sc_W1; uint8_t* sc_W2;                       // 64 KB per slot, first 32 KB used
+  uint8_t* sc_W1; uint8_t* sc_W2;                       // w_stride bytes per slot, first 32 KB used
+  long w_stride;                                        // 64 KB in the caller's fp32-shaped tensors, 32 KB in the built-in scratch
   uint8_t* sc_Z1; uint8_t* sc_X2; uint8_t* sc_gZ1; uint8_t* sc_Z1b; uint8_t* sc_X2b;   // 32 KB per slot
   uint8_t* sc_xhf; uint8_t* sc_gof; uint8_t* sc_gZ2; uint8_t* sc_xhln;                 // 8 KB per slot
   float* sc_sigf; float* sc_sigln;                      // 64 floats per slot
@@ -339,8 +340,8 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
     publish();
     if (tid == kProd) {   // bf16 images of the checkpoint = pre-update weights of the group's first mini-batch
-      bulk_store_1d(p.sc_W1 + slot0 * 65536, bW1, BIG);
-      bulk_store_1d(p.sc_W2 + slot0 * 65536, bW2, BIG);
+      bulk_store_1d(p.sc_W1 + slot0 * p.w_stride, bW1, BIG);
+      bulk_store_1d(p.sc_W2 + slot0 * p.w_stride, bW2, BIG);
       tma_commit_group();
     }
 
@@ -550,8 +551,8 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       // MMA5: Z1b^T = W1+^T Q^T
       if (tid == kProd) {
         if (j + 1 < gsz) {   // the new weights are the next mini-batch's pre-update weights
-          bulk_store_1d(p.sc_W1 + (slot + 1) * 65536, bW1, BIG);
-          bulk_store_1d(p.sc_W2 + (slot + 1) * 65536, bW2, BIG);
+          bulk_store_1d(p.sc_W1 + (slot + 1) * p.w_stride, bW1, BIG);
+          bulk_store_1d(p.sc_W2 + (slot + 1) * p.w_stride, bW2, BIG);
           tma_commit_group();
         }
       }
@@ -883,7 +884,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
       wait_mma();
       if (tid == kProd) {
-        load_big(ib1, p.sc_W2 + slot * 65536);      // X2 is consumed until G14: W2 takes its buffer
+        load_big(ib1, p.sc_W2 + slot * p.w_stride);      // X2 is consumed until G14: W2 takes its buffer
         tma_wait_group_read<0>();     // dQ has left the dL/dOut tile (E4 reuses it for dV)
       }
       wait_bar(BAR_BIG + ib2);
@@ -929,7 +930,7 @@ ttt_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 mma_hidden_half(tmem + TM_S2, smem_u32(big(ib4)), smem_u32(t_gz2), true, true, 1),
                 )
       wait_mma();
-      if (tid == kProd) load_big(ib4, p.sc_W1 + slot * 65536);
+      if (tid == kProd) load_big(ib4, p.sc_W1 + slot * p.w_stride);
       wait_bar(BAR_T + 6);
       wait_bar(BAR_T + 1);   // grad_output_fused
       // ---- E4: second order through the fused LayerNorm + L2 gradient (token-major, all 8 warps)
@@ -1207,6 +1208,7 @@ int ttt_launch_backward(const ttt_b200_bwd_args* a, cudaStream_t stream, uint32_
   p.W1c = a->W1_checkpoints; p.b1c = a->b1_checkpoints; p.W2c = a->W2_checkpoints; p.b2c = a->b2_checkpoints;
   p.sc_W1 = reinterpret_cast<uint8_t*>(a->W1_init_group);
   p.sc_W2 = reinterpret_cast<uint8_t*>(a->W2_init_group);
+  p.w_stride = 65536;
   p.sc_Z1 = static_cast<uint8_t*>(a->Z1_group);
   p.sc_X2 = static_cast<uint8_t*>(a->X2_group);
   p.sc_gZ1 = static_cast<uint8_t*>(a->grad_l_wrt_Z1_group);
@@ -1257,7 +1259,7 @@ int ttt_launch_backward(const ttt_b200_bwd_args* a, cudaStream_t stream, uint32_
 // GPU on which the library's kernels are loaded holds it until the process exits.
 //
 // Capacity: B * H * checkpoint_group_size <= TTT_B200_NOALLOC_MAX_SLOTS scratch slots of
-// 328 192 bytes (about 40 MiB in total).  Larger problems are rejected with code 1.
+// 262 656 bytes (about 32 MiB in total).  Larger problems are rejected with code 1.
 //
 // All calls on a device share the array.  Nothing in it has to start at zero (each slot is
 // written before it is read within one call) and it keeps the previous call's contents; two
@@ -1269,8 +1271,8 @@ namespace {
 
 constexpr size_t NA_SLOTS = TTT_B200_NOALLOC_MAX_SLOTS;
 constexpr size_t NA_OFF_W1 = 0;
-constexpr size_t NA_OFF_W2 = NA_OFF_W1 + NA_SLOTS * 65536;
-constexpr size_t NA_OFF_Z1 = NA_OFF_W2 + NA_SLOTS * 65536;
+constexpr size_t NA_OFF_W2 = NA_OFF_W1 + NA_SLOTS * BIG;
+constexpr size_t NA_OFF_Z1 = NA_OFF_W2 + NA_SLOTS * BIG;
 constexpr size_t NA_OFF_X2 = NA_OFF_Z1 + NA_SLOTS * BIG;
 constexpr size_t NA_OFF_GZ1 = NA_OFF_X2 + NA_SLOTS * BIG;
 constexpr size_t NA_OFF_Z1B = NA_OFF_GZ1 + NA_SLOTS * BIG;
@@ -1282,7 +1284,7 @@ constexpr size_t NA_OFF_XHLN = NA_OFF_GZ2 + NA_SLOTS * TILE;
 constexpr size_t NA_OFF_SIGF = NA_OFF_XHLN + NA_SLOTS * TILE;
 constexpr size_t NA_OFF_SIGLN = NA_OFF_SIGF + NA_SLOTS * 256;
 constexpr size_t NA_BYTES = NA_OFF_SIGLN + NA_SLOTS * 256;
-static_assert(NA_BYTES == NA_SLOTS * 328192, "scratch slot size changed: update the header comment");
+static_assert(NA_BYTES == NA_SLOTS * 262656, "scratch slot size changed: update the header comment");
 
 static __device__ __align__(256) unsigned char g_noalloc_scratch[NA_BYTES];
 static __device__ __align__(16) uint32_t g_noalloc_status;
@@ -1368,6 +1370,7 @@ extern "C" int ttt_b200_backward_noalloc(const ttt_b200_bwd_noalloc_args* a, voi
   p.W1c = a->W1_checkpoints; p.b1c = a->b1_checkpoints; p.W2c = a->W2_checkpoints; p.b2c = a->b2_checkpoints;
   p.sc_W1 = d.scratch + NA_OFF_W1;
   p.sc_W2 = d.scratch + NA_OFF_W2;
+  p.w_stride = BIG;
   p.sc_Z1 = d.scratch + NA_OFF_Z1;
   p.sc_X2 = d.scratch + NA_OFF_X2;
   p.sc_gZ1 = d.scratch + NA_OFF_GZ1;

@@ -8,8 +8,9 @@
 //   eta gate       last_eta[b][h][t] = scale * sigmoid(logit[b][t][h])             bf16 in, bf16 out
 //   its backward   d_logit[b][t][h]  = d_last_eta[b][h][t] * scale * s (1 - s)
 //   output norm    y[b][t][:] = gamma * LayerNorm_{H*64}(x[b][:][t][:]) + beta     x = Out [B][H][T][64] bf16
+//   its backward   dx (head-major: the operator's grad_L_XQW_mini_batch), d_gamma, d_beta from dy (token-major)
 //
-// All three are HBM-bound byte movers with a little fp32 arithmetic: algorithmic bytes = input + output.
+// All of them are HBM-bound byte movers with a little fp32 arithmetic: algorithmic bytes = input + output.
 #include <cuda_bf16.h>
 
 #include <cstdio>
@@ -67,7 +68,7 @@ constexpr int kMaxChunks = 16;     // H <= 64
 template <int kChunks>
 __global__ void __launch_bounds__(256, (kChunks <= 8 ? 4 : 2)) unpack_layernorm_kernel(const uint4* __restrict__ src, const float* __restrict__ gamma,
                                                                const float* __restrict__ beta, uint4* __restrict__ dst,
-                                                               float eps, long tokens, int T, int H) {
+                                                               float2* __restrict__ stats, float eps, long tokens, int T, int H) {
   const int lane = threadIdx.x & 31;
   const int sub = lane >> 3, piece = lane & 7;          // head within a group of 4, 16-byte piece of the row
   const long warp0 = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -109,6 +110,7 @@ __global__ void __launch_bounds__(256, (kChunks <= 8 ? 4 : 2)) unpack_layernorm_
     const float mean = pivot + dm;
     sq = fmaxf(sq - sum * dm, 0.f);           // n * variance
     const float rstd = rsqrtf(sq * inv_n + eps);
+    if (stats != nullptr && lane == 0) stats[tok] = make_float2(mean, rstd);
 #pragma unroll
     for (int c = 0; c < kChunks; ++c) {
       const int h = 4 * c + sub;
@@ -130,6 +132,118 @@ __global__ void __launch_bounds__(256, (kChunks <= 8 ? 4 : 2)) unpack_layernorm_
         __stcs(dst + ((tok * H + h) << 3) + piece, o4);
       }
     }
+  }
+}
+
+// ---- backward of the output norm, fused with the token-major -> head-major turn of the gradient: the
+// result is the operator's grad_L_XQW_mini_batch.  With xhat = (x - mean) rstd and g = dy gamma:
+//   dx = rstd (g - mean(g) - xhat mean(g xhat)).
+// Same work split as the forward: one warp per token, the token's x and dy in registers (packed bf16).
+template <int kChunks>
+__global__ void __launch_bounds__(256, (kChunks <= 4 ? 4 : 2))
+pack_layernorm_backward_kernel(const uint4* __restrict__ dy, const uint4* __restrict__ x, const float* __restrict__ gamma,
+                               const float2* __restrict__ stats, uint4* __restrict__ dx, long tokens, int T, int H) {
+  const int lane = threadIdx.x & 31;
+  const int sub = lane >> 3, piece = lane & 7;
+  const long warp0 = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long nwarps = (static_cast<long>(gridDim.x) * blockDim.x) >> 5;
+  const float inv_n = 1.f / static_cast<float>(H * 64);
+  for (long tok = warp0; tok < tokens; tok += nwarps) {
+    const long b = tok / T, t = tok - b * T;
+    uint4 rx[kChunks], rg[kChunks];
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+      const int h = 4 * c + sub;
+      if (h < H) {
+        rx[c] = __ldcs(x + (((b * H + h) * T + t) << 3) + piece);
+        rg[c] = __ldcs(dy + ((tok * H + h) << 3) + piece);
+      }
+    }
+    const float2 st = stats[tok];
+    const float mean = st.x, rstd = st.y;
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+      const int h = 4 * c + sub;
+      if (h < H) {
+        const __nv_bfloat162* vx = reinterpret_cast<const __nv_bfloat162*>(&rx[c]);
+        const __nv_bfloat162* vg = reinterpret_cast<const __nv_bfloat162*>(&rg[c]);
+        const int f0 = h * 64 + piece * 8;
+        const float4 g0 = *reinterpret_cast<const float4*>(gamma + f0), g1 = *reinterpret_cast<const float4*>(gamma + f0 + 4);
+        const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 fx = __bfloat1622float2(vx[k]), fg = __bfloat1622float2(vg[k]);
+          const float a0 = fg.x * gg[2 * k], a1 = fg.y * gg[2 * k + 1];
+          s1 += a0 + a1;
+          s2 = fmaf(a0, (fx.x - mean) * rstd, fmaf(a1, (fx.y - mean) * rstd, s2));
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+      s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+    }
+    s1 *= inv_n;
+    s2 *= inv_n;
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+      const int h = 4 * c + sub;
+      if (h < H) {
+        const __nv_bfloat162* vx = reinterpret_cast<const __nv_bfloat162*>(&rx[c]);
+        const __nv_bfloat162* vg = reinterpret_cast<const __nv_bfloat162*>(&rg[c]);
+        const int f0 = h * 64 + piece * 8;
+        const float4 g0 = *reinterpret_cast<const float4*>(gamma + f0), g1 = *reinterpret_cast<const float4*>(gamma + f0 + 4);
+        const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        uint4 o4;
+        __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 fx = __bfloat1622float2(vx[k]), fg = __bfloat1622float2(vg[k]);
+          const float x0 = (fx.x - mean) * rstd, x1 = (fx.y - mean) * rstd;
+          o[k] = __floats2bfloat162_rn(rstd * (fmaf(fg.x, gg[2 * k], -s1) - x0 * s2),
+                                       rstd * (fmaf(fg.y, gg[2 * k + 1], -s1) - x1 * s2));
+        }
+        __stcs(dx + (((b * H + h) * T + t) << 3) + piece, o4);
+      }
+    }
+  }
+}
+
+// d_gamma[f] += sum over tokens of dy xhat, d_beta[f] += sum of dy.  One CTA per (batch element, head, block of
+// kTokBlock tokens): thread = (feature of the head, one of four token phases); x is read along its head-major
+// rows, dy along the token-major ones (128 bytes per token either way); the four phases are added in shared
+// memory and the block's 2 x 64 sums leave as fp32 atomic adds (the order of the blocks is not fixed: the last
+// bits of the result can differ from run to run).
+constexpr int kTokBlock = 256;
+__global__ void __launch_bounds__(256) layernorm_param_grad_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                                   const __nv_bfloat16* __restrict__ x,
+                                                                   const float2* __restrict__ stats,
+                                                                   float* __restrict__ d_gamma, float* __restrict__ d_beta,
+                                                                   int T, int H) {
+  __shared__ float red[2][4][64];
+  const int f = threadIdx.x & 63, ph = threadIdx.x >> 6;
+  const int nblk = (T + kTokBlock - 1) / kTokBlock;
+  const int blk = blockIdx.x % nblk;
+  const long bh = blockIdx.x / nblk;
+  const long b = bh / H, h = bh - b * H;
+  const int t0 = blk * kTokBlock, t1 = min(T, t0 + kTokBlock);
+  float ag = 0.f, ab = 0.f;
+  for (int t = t0 + ph; t < t1; t += 4) {
+    const float2 st = stats[b * T + t];
+    const float xv = __bfloat162float(x[(bh * T + t) * 64 + f]);
+    const float gv = __bfloat162float(dy[((b * T + t) * H + h) * 64 + f]);
+    ag = fmaf(gv, (xv - st.x) * st.y, ag);
+    ab += gv;
+  }
+  red[0][ph][f] = ag;
+  red[1][ph][f] = ab;
+  __syncthreads();
+  if (threadIdx.x < 128) {
+    const int k = threadIdx.x >> 6;
+    const float v = (red[k][0][f] + red[k][1][f]) + (red[k][2][f] + red[k][3][f]);
+    atomicAdd((k == 0 ? d_gamma : d_beta) + h * 64 + f, v);
   }
 }
 
@@ -178,13 +292,15 @@ extern "C" int ttt_b200_eta_gate_backward(const void* logits, const void* grad_l
   return launch_eta(true, logits, grad_last_eta, grad_logits, scale, B, T, H, stream);
 }
 
-extern "C" int ttt_b200_unpack_layernorm(const void* src, const float* gamma, const float* beta, void* dst, float eps,
-                                         int B, int T, int H, void* stream_) {
+extern "C" int ttt_b200_unpack_layernorm(const void* src, const float* gamma, const float* beta, void* dst, float* stats,
+                                         float eps, int B, int T, int H, void* stream_) {
   if (int rc = check_common("output norm", B, T, H)) return rc;
   if (H > 4 * kMaxChunks) return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "output norm: H must not exceed 64");
   if (bad_ptr(src, 16) || bad_ptr(dst, 16) || bad_ptr(gamma, 16) || bad_ptr(beta, 16))
     return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "output norm: null or not 16-byte aligned tensor pointer");
   if (src == dst) return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "output norm: the transform is out of place");
+  if (stats != nullptr && (reinterpret_cast<uintptr_t>(stats) & 7))
+    return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "output norm: stats must be 8-byte aligned");
   if (!(eps >= 0.f)) return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "output norm: eps must be >= 0");
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -197,7 +313,8 @@ extern "C" int ttt_b200_unpack_layernorm(const void* src, const float* gamma, co
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
 #define TTT_LN_LAUNCH(CH)                                                                                  \
   unpack_layernorm_kernel<CH><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(                          \
-      static_cast<const uint4*>(src), gamma, beta, static_cast<uint4*>(dst), eps, tokens, T, H)
+      static_cast<const uint4*>(src), gamma, beta, static_cast<uint4*>(dst), reinterpret_cast<float2*>(stats), eps, \
+      tokens, T, H)
   if (chunks <= 1) TTT_LN_LAUNCH(1);
   else if (chunks <= 2) TTT_LN_LAUNCH(2);
   else if (chunks <= 3) TTT_LN_LAUNCH(3);
@@ -208,6 +325,49 @@ extern "C" int ttt_b200_unpack_layernorm(const void* src, const float* gamma, co
   else TTT_LN_LAUNCH(16);
 #undef TTT_LN_LAUNCH
   const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
+  return TTT_B200_OK;
+}
+
+extern "C" int ttt_b200_pack_layernorm_backward(const void* grad_y, const void* x, const float* gamma, const float* stats,
+                                                void* grad_x, float* grad_gamma, float* grad_beta, int B, int T, int H,
+                                                void* stream_) {
+  if (int rc = check_common("output norm backward", B, T, H)) return rc;
+  if (H > 4 * kMaxChunks) return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "output norm backward: H must not exceed 64");
+  if (bad_ptr(grad_y, 16) || bad_ptr(x, 16) || bad_ptr(grad_x, 16) || bad_ptr(gamma, 16) || bad_ptr(stats, 8) ||
+      bad_ptr(grad_gamma, 4) || bad_ptr(grad_beta, 4))
+    return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "output norm backward: null or misaligned tensor pointer");
+  if (grad_x == x || grad_x == grad_y)
+    return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "output norm backward: the transform is out of place");
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long tokens = static_cast<long>(B) * T;
+  long blocks = (tokens + 7) / 8;
+  const long cap = static_cast<long>(sms) * 8;
+  if (blocks > cap) blocks = cap;
+  const int chunks = (H + 3) / 4;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+#define TTT_LNB_LAUNCH(CH)                                                                                       \
+  pack_layernorm_backward_kernel<CH><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(                         \
+      static_cast<const uint4*>(grad_y), static_cast<const uint4*>(x), gamma, reinterpret_cast<const float2*>(stats), \
+      static_cast<uint4*>(grad_x), tokens, T, H)
+  if (chunks <= 1) TTT_LNB_LAUNCH(1);
+  else if (chunks <= 2) TTT_LNB_LAUNCH(2);
+  else if (chunks <= 3) TTT_LNB_LAUNCH(3);
+  else if (chunks <= 4) TTT_LNB_LAUNCH(4);
+  else if (chunks <= 6) TTT_LNB_LAUNCH(6);
+  else if (chunks <= 8) TTT_LNB_LAUNCH(8);
+  else if (chunks <= 12) TTT_LNB_LAUNCH(12);
+  else TTT_LNB_LAUNCH(16);
+#undef TTT_LNB_LAUNCH
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
+  const long grid2 = static_cast<long>(B) * H * ((T + kTokBlock - 1) / kTokBlock);
+  layernorm_param_grad_kernel<<<static_cast<unsigned>(grid2), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(grad_y), static_cast<const __nv_bfloat16*>(x),
+      reinterpret_cast<const float2*>(stats), grad_gamma, grad_beta, T, H);
+  e = cudaGetLastError();
   if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
   return TTT_B200_OK;
 }
