@@ -44,6 +44,7 @@ WORKLOADS = {
     "small": (1, 8, 16, 4, "small case, B=1 H=8 seq=1024 cgs=4"),
     "prof": (4, 32, 16, 8, "profiling case: configs[2] streams (B=4 H=32) at seq=1024 (NC=16) cgs=8"),
     "profc": (1, 32, 16, 8, "profiling case of the cluster kernels: 32 streams (B=1 H=32) at seq=1024 (NC=16) cgs=8"),
+    "c2half": (2, 32, 128, 8, "half of configs[2] (what each of two GPUs gets): B=2 H=32 seq=8192 (NC=128) cgs=8"),
     "profc2": (2, 32, 16, 8, "profiling case with 64 streams (B=2 H=32) at seq=1024 (NC=16) cgs=8"),
     "glue": (4, 32, 128, 8, "layer-side kernels at the configs[2] shape: B=4 T=8192 H=32"),
 }

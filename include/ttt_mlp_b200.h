@@ -216,8 +216,8 @@ int ttt_b200_version(void);
 
 /* How many CTAs (1, 2 or 4) the forward (backward = 0) or backward (backward != 0) launcher gives each
  * (batch, head) stream of a problem with `streams` = B*H streams on the current device when the flags leave
- * the choice to it: four when all CTAs fit on the GPU at once, else two while that pays (measured
- * thresholds), else one; TTT_B200_CLUSTER overrides.  The reference fixes the split at compile time
+ * the choice to it: four when all CTAs fit on the GPU at once, else (forward only) two when those fit, else
+ * one (measured thresholds); TTT_B200_CLUSTER overrides.  The reference fixes the split at compile time
  * (kernels/ttt/ttt.cu:11-12, kernels/ttt_backward/ttt.cu:12-16).  Returns -1 on error. */
 int ttt_b200_pick_cluster(int streams, int backward);
 

@@ -77,9 +77,11 @@ int sm_count() {
 // How many CTAs share one stream.  The mini-batches of a stream are strictly sequential, so with fewer
 // streams than SMs the idle SMs can only help by taking a share of every stream's hidden units.  The
 // thresholds are measured (B200, 148 SMs): four CTAs per stream win whenever they all fit on the GPU at
-// once (about 12 % per mini-batch over one CTA); two CTAs per stream win in the forward whenever they fit
-// (12 %), in the backward up to about 100 resident CTAs (10 %; beyond, with both SMs of nearly every TPC
-// running the large backward, every phase of it slows down by about 15 % and the gain is gone).
+// once (forward 18 %, backward 17-20 % per mini-batch over one CTA).  Two CTAs per stream win in the
+// forward whenever they fit (12-17 %).  In the backward they gain 6-11 % up to 32 streams, where four CTAs
+// are the better choice anyway, and nothing beyond 37 streams (more than 74 CTAs: both SMs of a TPC are
+// then busy, and the backward, whose scratch traffic goes through the port the two share, slows down by
+// as much as the split gained), so the backward is never given two.
 int ttt_pick_cluster(int streams, uint32_t flags, bool backward, int* cluster) {
   int forced = static_cast<int>((flags & TTT_B200_FLAG_CLUSTER_MASK) >> TTT_B200_FLAG_CLUSTER_SHIFT);
   if (forced == 0) {
@@ -96,8 +98,7 @@ int ttt_pick_cluster(int streams, uint32_t flags, bool backward, int* cluster) {
     return TTT_B200_OK;
   }
   const int sms = sm_count();
-  const int two_limit = backward ? 7 * sms / 10 : sms;
-  *cluster = 4 * streams <= sms ? 4 : (2 * streams <= two_limit ? 2 : 1);
+  *cluster = 4 * streams <= sms ? 4 : (!backward && 2 * streams <= sms ? 2 : 1);
   return TTT_B200_OK;
 }
 
