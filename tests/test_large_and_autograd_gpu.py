@@ -82,12 +82,14 @@ def test_config2_full_size_streams_are_independent_and_correct():
             assert orc.rel_l2(outs1[k].float().cpu(), g[k]) <= 3e-2, k
 
 
-def test_long_sequence_error_stays_inside_the_gate():
-    """Long-context shape of configs[3] (seq 65536, NC = 1024, cgs 32) on two heads: the error of the
-    bf16-operand recurrence grows with the mini-batch index and must still meet the gates at the end."""
+@pytest.mark.parametrize("cluster", [1, 4])
+def test_long_sequence_error_stays_inside_the_gate(cluster):
+    """Long-context shape of configs[3] (seq 65536, NC = 1024, cgs 32) on two heads, with one CTA per stream
+    and with the cluster of four the launcher gives such a shape: the error of the bf16-operand recurrence
+    grows with the mini-batch index and must still meet the gates at the end."""
     B, H, NC, cgs = 1, 2, 1024, 32
     d = make_inputs(B, H, NC, seed=0, backward=True)
-    out, ck, outs = _run(d, cgs)
+    out, ck, outs = _run(d, cgs, cluster=cluster)
     f, g = _oracle(d, cgs, {k: c.cpu() for k, c in zip(CHECKPOINT_NAMES, ck)})
     o = out.float().cpu()
     assert orc.rel_l2(o, f["Out"]) <= 1e-2

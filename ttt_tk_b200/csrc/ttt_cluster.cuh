@@ -346,6 +346,139 @@ struct ClusterSum {
   }
 };
 
+// ---- Row-split stages.  A 64 x 64 stage that follows a contraction over the hidden units (the fused
+// LayerNorm, the output LayerNorm) does not have to be repeated by every CTA of the cluster on the whole
+// tile: the token rows are dealt out (CTA r owns the rows of fragment quadrants QPC r .. QPC r + QPC - 1,
+// QPC = 4 / kC, i.e. rows 64 r / kC .. 64 (r + 1) / kC - 1), the partial tiles are summed by reduce-scatter,
+// every CTA runs the stage on its own rows with ALL of its 256 threads, and the bf16 results that the
+// other CTAs need as MMA operands are written into the peers' shared memories as well (all-gather).
+// Against an all-reduce followed by the stage on the whole tile in every CTA this sends (kC - 1) / kC of a
+// tile in fp32 plus the bf16 rows instead of kC - 1 tiles, and does 1 / kC of the arithmetic per CTA.
+//
+// Reduce-scatter buffers: kBufs = 4 (taken in turn per use) x kC slots (slot s = the partial of rank s, this
+// CTA's own included).  A slot holds the owner's rows as [quadrant lq][row pair w = 0..7][column pair
+// 0..31] float4 = {(r, c), (r, c+1), (r+8, c), (r+8, c+1)}, r = 16 (QPC rank + lq) + w, c = 2 x column pair:
+// the float4 a fragment thread holds for j = 0..3, so the sender stores 16 bytes at a time, and one row
+// pair is 512 contiguous bytes, so the 32 lanes of the warp that works on it read them without bank
+// conflicts (an earlier layout indexed by sending thread cost 0.5 us per receive in 8-way conflicts).
+// One mbarrier per buffer: the arming arrival of thread 0 (expect_tx of the peers' bytes) plus one arrival
+// per warp that wrote this CTA's own partial with plain stores.  Four buffers, because a kernel may send
+// use n + 1 before it receives use n (it receives a deferred sum while it waits for the next one): a peer
+// writes use n + 4 into the buffer of use n only after it has received n + 3 from this CTA, which this CTA
+// sends after its receive of n in program order.
+//
+// Row layout of the stage: warp w works on row pair w of each of the CTA's QPC quadrants, lane l on the
+// column pair l: NR = 2 QPC rows x 2 columns per thread; a row lives in one warp, so row sums are five
+// xor-shuffles.
+template <int kC>
+struct RowSplit {
+  static constexpr int QPC = 4 / kC;                          // fragment quadrants per CTA
+  static constexpr int ROWS = 16 * QPC;
+  static constexpr int NR = 2 * QPC;                          // rows per thread in the row layout
+  static constexpr uint32_t kSlotBytes = QPC * 4096u;
+  static constexpr uint32_t kBufBytes = kC * kSlotBytes;      // 16 KB
+  static constexpr int kBufs = 4;
+  static constexpr uint32_t kBytes = kBufs * kBufBytes;
+  static constexpr uint32_t kBarCount = 1 + 2 * QPC;          // arming thread + the warps of the own quadrants
+
+  uint8_t* bufp;
+  uint64_t* bars;        // [kBufs]
+  uint32_t n;
+  uint32_t rank;
+  volatile uint32_t* abort_flag;
+  uint64_t limit;
+
+  // ---- fragment side (TokMap layout)
+  static __device__ __forceinline__ uint32_t owner_of(int warp) { return static_cast<uint32_t>(warp & 3) / QPC; }
+  // Send this thread's 16 partial values to the owner of its rows (or file them in this CTA's own slot).
+  // Returns the tag for recv().
+  __device__ __forceinline__ uint32_t send(const float (&v)[16], int tid, int warp, int lane) {
+    const uint32_t b = n & 3u, par = (n >> 2) & 1u;
+    ++n;
+    const uint32_t owner = owner_of(warp);
+    const uint32_t lq = static_cast<uint32_t>(warp & 3) % QPC, colhalf = static_cast<uint32_t>(warp >> 2);
+    const uint32_t off = b * kBufBytes + rank * kSlotBytes + lq * 4096u + static_cast<uint32_t>(lane >> 2) * 512u +
+                         (colhalf * 16u + static_cast<uint32_t>(lane & 3)) * 16u;
+    if (tid == 0) mbar_expect_tx(&bars[b], (kC - 1) * kSlotBytes);
+    if (owner != rank) {
+      const uint32_t dst = mapa(smem_u32(bufp) + off, owner);
+      const uint32_t rbar = mapa(smem_u32(&bars[b]), owner);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        st_async_f4(dst + j * 64u, rbar, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    } else {
+      float4* dst = reinterpret_cast<float4*>(bufp + off);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) dst[j * 4] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[b]);
+    }
+    return b | (par << 2);
+  }
+
+  // ---- row side: row i of the thread (i = 2 lq + h) is token row 16 (QPC rank + lq) + warp + 8 h of the tile
+  __device__ __forceinline__ int row(int i, int warp) const {
+    return 16 * (QPC * static_cast<int>(rank) + (i >> 1)) + warp + 8 * (i & 1);
+  }
+  // Wait for the partial tiles and return their sums (rank order): z[i][0..1] = row i, columns 2 lane, 2 lane + 1.
+  __device__ __forceinline__ void recv(float (&z)[NR][2], int warp, int lane, uint32_t tag) {
+    const uint32_t b = tag & 3u, par = tag >> 2;
+    mbar_wait_cl(&bars[b], par, abort_flag, limit, kC);
+    const uint8_t* base = bufp + b * kBufBytes + static_cast<uint32_t>(warp) * 512u + static_cast<uint32_t>(lane) * 16u;
+#pragma unroll
+    for (int lq = 0; lq < QPC; ++lq) {
+      float4 acc = *reinterpret_cast<const float4*>(base + lq * 4096u);
+#pragma unroll
+      for (int s = 1; s < kC; ++s) {
+        const float4 f = *reinterpret_cast<const float4*>(base + s * kSlotBytes + lq * 4096u);
+        acc.x += f.x; acc.y += f.y; acc.z += f.z; acc.w += f.w;
+      }
+      z[2 * lq][0] = acc.x; z[2 * lq][1] = acc.y;
+      z[2 * lq + 1][0] = acc.z; z[2 * lq + 1][1] = acc.w;
+    }
+  }
+  static __device__ __forceinline__ float row_sum(float x) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+    return x;
+  }
+  // the thread's column pair of row r of a swizzled bf16 tile
+  static __device__ __forceinline__ float2 ld_pair(const uint8_t* tile, int r, int lane) {
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(tile + sw128_off(r, lane >> 2) + (lane & 3) * 4);
+    return make_float2(bf16_lo(w), bf16_hi(w));
+  }
+  static __device__ __forceinline__ void st_pair_global(__nv_bfloat16* tile, int r, int lane, float a, float b) {
+    *reinterpret_cast<uint32_t*>(tile + r * 64 + 2 * lane) = pack_bf16(a, b);
+  }
+
+  // ---- all-gather of a stage's bf16 result: row r of `tile`, of which this thread holds the column pair
+  // (a, b), is written into this CTA's tile and, as 16-byte asynchronous stores counted on the peers'
+  // `ag_bar`, into the same place of every peer's tile (four neighbouring lanes make up one 16-byte chunk;
+  // all 32 lanes call this).  The receiver waits on its `ag_bar` (armed by arm_all_gather) and runs the usual
+  // proxy fence + CTA barrier before an MMA reads the tile.
+  __device__ __forceinline__ void arm_all_gather(uint64_t* ag_bar, int ntiles) const {
+    mbar_expect_tx(ag_bar, (kC - 1) * ROWS * 128u * static_cast<uint32_t>(ntiles));
+  }
+  __device__ __forceinline__ void all_gather_store(uint8_t* tile, uint64_t* ag_bar, int r, int lane, float a, float b) const {
+    const uint32_t w0 = pack_bf16(a, b);
+    const uint32_t w1 = __shfl_down_sync(0xffffffffu, w0, 1), w2 = __shfl_down_sync(0xffffffffu, w0, 2),
+                   w3 = __shfl_down_sync(0xffffffffu, w0, 3);
+    if ((lane & 3) == 0) {
+      const uint32_t off = sw128_off(r, lane >> 2);
+      *reinterpret_cast<uint4*>(tile + off) = make_uint4(w0, w1, w2, w3);
+      const uint32_t adr = smem_u32(tile) + off, ba = smem_u32(ag_bar);
+#pragma unroll
+      for (int s = 1; s < kC; ++s) {
+        const uint32_t peer = rank ^ static_cast<uint32_t>(s);
+        asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%2, %3, %4, %5}, [%1];" ::"r"(
+                         mapa(adr, peer)),
+                     "r"(mapa(ba, peer)), "r"(w0), "r"(w1), "r"(w2), "r"(w3)
+                     : "memory");
+      }
+    }
+  }
+};
+
 // Exit of a cluster kernel (all threads of all CTAs call it).  On the ordinary path every byte a peer
 // has sent to this CTA has been waited for, so one cluster barrier is enough before the shared memory
 // goes away.  After an abort the CTAs may have skipped waits: all of them first meet (nobody sends any

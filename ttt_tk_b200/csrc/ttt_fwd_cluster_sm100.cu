@@ -7,15 +7,17 @@
 // has fewer streams than SMs: the mini-batches of a stream are strictly sequential, so splitting a
 // stream over several SMs is the only way to put idle SMs to work on it.
 //
-// What is local and what is exchanged.  Everything indexed by a hidden unit is local to the CTA that
+// What is local and what is exchanged (ttt_cluster.cuh: RowSplit).  Everything indexed by a hidden unit is local to the CTA that
 // owns the unit: its rows of W1^T and W2 (fp32 master copy in tensor memory as the accumulator of
 // their own update MMA, bf16 operand copy in shared memory), its b1 entries, Z1^T, X2^T, gelu', U1^T
 // and the state updates.  The two contractions over the hidden units, Z2 = X2 W2 and Z2b = X2b W2,
 // leave a partial 64 x 64 fp32 tile per CTA; the partial tiles are summed across the cluster through
-// distributed shared memory (ttt_cluster.cuh), after which every CTA holds the same Z2 and runs the
-// 64 x 64 LayerNorm stages redundantly (they are small).  Every CTA loads its own copy of the K, V, Q
+// distributed shared memory by reduce-scatter: CTA r receives the token rows 64 r / kC .. of every peer's
+// tile, runs the LayerNorm stage on those rows with all of its threads, and (for the fused LayerNorm,
+// whose result U2 every CTA needs as an MMA operand) copies its rows of the bf16 result into the peers'
+// shared memories.  Every CTA loads its own copy of the K, V, Q
 // tiles (plain TMA loads; after the first CTA they hit in L2).  b2 is kept, identically, by every CTA.
-// Z2b is needed only for the output: it is summed by reduce-scatter and every CTA stores the Out rows it owns.
+// Z2b is needed only for the output: every CTA normalises and stores the Out rows it owns.
 //
 // All accumulators are M = 64 tiles read with the 16x256b fragments (TokMap): a CTA's hidden units are
 // NB = 4 / kC blocks of 64 rows.  Per mini-batch the steps are those of the one-CTA kernel
@@ -41,7 +43,9 @@ struct Cfg {
   static constexpr int NB = 4 / kC;                  // 64-row blocks of hidden units per CTA
   static constexpr int R = 64 * NB;                  // hidden units per CTA
   static constexpr uint32_t HB = NB * TILE;          // bytes of an [R][64] bf16 tile
-  using Sum = ClusterSum<kC, 16384>;
+  using RS = RowSplit<kC>;                     // kC = 4: row-split LayerNorm stages
+  using Sum = ClusterSum<kC, 16384>;           // kC = 2: all-reduce, stages on the whole tile in both CTAs
+  static constexpr bool kRowSplit = kC == 4;   // measured: at kC = 2 the second hop costs more than the halved stage saves
   static constexpr uint32_t OFF_K = 0;
   static constexpr uint32_t OFF_V = OFF_K + kStages * TILE;
   static constexpr uint32_t OFF_Q = OFF_V + kStages * TILE;
@@ -52,12 +56,12 @@ struct Cfg {
   static constexpr uint32_t OFF_X2 = OFF_W2 + HB;
   static constexpr uint32_t OFF_GP = OFF_X2 + HB;
   static constexpr uint32_t OFF_SUM = OFF_GP + HB;                 // cluster exchange area
-  static constexpr uint32_t OFF_ETA = OFF_SUM + Sum::kBytes;
+  static constexpr uint32_t OFF_ETA = OFF_SUM + (kRowSplit ? RS::kBytes : Sum::kBytes);
   static constexpr uint32_t OFF_B2 = OFF_ETA + kStages * 128;
   static constexpr uint32_t OFF_GAMMA = OFF_B2 + 256;
   static constexpr uint32_t OFF_BETA = OFF_GAMMA + 256;
-  static constexpr uint32_t OFF_BAR = OFF_BETA + 256;              // kStages + 1 + 2 + 1 mbarriers
-  static constexpr uint32_t OFF_MISC = OFF_BAR + 64;
+  static constexpr uint32_t OFF_BAR = OFF_BETA + 256;              // kStages + 1 + 4 + 1 + 1 mbarriers
+  static constexpr uint32_t OFF_MISC = OFF_BAR + 128;
   static constexpr uint32_t OFF_PART = OFF_MISC + 64;              // fp32[4][64] column-sum partials
   static constexpr uint32_t OFF_XCH = OFF_PART + 1024;             // fp32[2][64][8] row-sum exchange between warp pairs
   static constexpr uint32_t SMEM_USED = OFF_XCH + 4096;
@@ -123,8 +127,9 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   float* sBeta = reinterpret_cast<float*>(smem + C::OFF_BETA);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);   // [kStages]
   uint64_t* mma_bar = full + kStages;
-  uint64_t* sum_bars = mma_bar + 1;                                  // [2]
-  uint64_t* drain_bar = sum_bars + 2;                                // abort path only
+  uint64_t* sum_bars = mma_bar + 1;                                  // [4]
+  uint64_t* drain_bar = sum_bars + 4;                                // abort path only
+  uint64_t* ag_bar = drain_bar + 1;                                  // all-gather of the U2 rows
   float* sPart = reinterpret_cast<float*>(smem + C::OFF_PART);
   float* sXch = reinterpret_cast<float*>(smem + C::OFF_XCH);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
@@ -137,9 +142,9 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   if (tid == kProd) {
     for (int s = 0; s < kStages; ++s) mbar_init(&full[s], 1);
     mbar_init(mma_bar, 4);
-    mbar_init(&sum_bars[0], C::Sum::kArrivals);
-    mbar_init(&sum_bars[1], C::Sum::kArrivals);
+    for (int i = 0; i < C::RS::kBufs; ++i) mbar_init(&sum_bars[i], C::kRowSplit ? C::RS::kBarCount : C::Sum::kArrivals);
     mbar_init(drain_bar, 4);
+    mbar_init(ag_bar, 1);
     fence_mbar_init();
     *abort_flag = 0;
     *never_flag = 0;
@@ -165,6 +170,15 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   cluster_wait();
   const uint32_t tmem = *tmem_slot;
 
+  typename C::RS rs;
+  rs.bufp = smem + C::OFF_SUM;
+  rs.bars = sum_bars;
+  rs.n = 0;
+  rs.rank = rank;
+  rs.abort_flag = abort_flag;
+  rs.limit = limit;
+  constexpr int NR = C::RS::NR;                     // rows per thread in the row-split stages
+  uint32_t ag_phase = 0;
   typename C::Sum csum;
   csum.bufp = smem + C::OFF_SUM;
   csum.bars = sum_bars;
@@ -287,11 +301,13 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     __syncwarp();                     \
   }
 
-  // the output tile of a mini-batch between the send and the receive of its reduce-scatter
-  float zo[16];
+  // The output of a mini-batch: its partial Z2b tile is sent at the end of the mini-batch (reduce-scatter);
+  // the sums are received, normalised and stored, by the CTA that owns the rows, in the next mini-batch while
+  // that one waits for its own Z2 sum.
   uint32_t zo_tag = 0;
   int zo_it = -1;
-  auto finish_out = [&]() {
+  float zo[16];          // kC = 2: the partial tile between the send and the receive of its reduce-scatter
+  auto finish_out_whole = [&]() {
     const bool mine = csum.reduce_scatter_recv(zo, tid, zo_tag);
     if (mine) {       // whole warp pairs (the two warps of a fragment quadrant) take this branch together
       const uint8_t* sQp = smem + C::OFF_Q + (zo_it % kStages) * TILE;
@@ -317,6 +333,31 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         }
       }
       tok_st_global(tm, p.out + (stream_id * NC + zo_it) * 4096, q);
+    }
+    zo_it = -1;
+  };
+
+  auto finish_out = [&]() {
+    const uint8_t* sQp = smem + C::OFF_Q + (zo_it % kStages) * TILE;
+    const float2 b2c = *reinterpret_cast<const float2*>(sB2 + 2 * lane);
+    const float2 gam = *reinterpret_cast<const float2*>(sGamma + 2 * lane);
+    const float2 bet = *reinterpret_cast<const float2*>(sBeta + 2 * lane);
+    float2 q[NR];
+#pragma unroll
+    for (int i = 0; i < NR; ++i) q[i] = C::RS::ld_pair(sQp, rs.row(i, warp), lane);
+    float z[NR][2];
+    rs.recv(z, warp, lane, zo_tag);
+    __nv_bfloat16* out_tile = p.out + (stream_id * NC + zo_it) * 4096;
+#pragma unroll
+    for (int i = 0; i < NR; ++i) {
+      z[i][0] += b2c.x;
+      z[i][1] += b2c.y;
+      const float mu = C::RS::row_sum(z[i][0] + z[i][1]) * (1.f / 64.f);
+      z[i][0] -= mu;
+      z[i][1] -= mu;
+      const float rstd = rsqrtf(C::RS::row_sum(fmaf(z[i][0], z[i][0], z[i][1] * z[i][1])) * (1.f / 64.f) + TTT_LN_EPS);
+      C::RS::st_pair_global(out_tile, rs.row(i, warp), lane, q[i].x + fmaf(gam.x, z[i][0] * rstd, bet.x),
+                            q[i].y + fmaf(gam.y, z[i][1] * rstd, bet.y));
     }
     zo_it = -1;
   };
@@ -349,7 +390,9 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       store_b1(p.b1c + ckc * 256);
       if (rank == 0 && tid < 64) p.b2c[ckc * 64 + tid] = sB2[tid];   // before this mini-batch's column sums reach b2
     }
-    if (zo_it >= 0) finish_out();          // the previous mini-batch's output, with the b2 it saw
+    if constexpr (!C::kRowSplit) {
+      if (zo_it >= 0) finish_out_whole();    // the previous mini-batch's output, with the b2 it saw
+    }
     wait_mma();
     // ---- EPI1: X2^T = gelu(Z1^T + b1), G' = gelu'(Z1^T + b1)
 #pragma unroll
@@ -368,12 +411,6 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       tok_st_tile(tm, sGP + b * TILE, gp);
     }
     publish();
-    // the previous mini-batch's Q tile has been read by every warp (its output is finished): its stage takes
-    // the loads of the mini-batch two ahead
-    if (tid == kProd && it >= 1 && loads_issued < NC && loads_issued == it - 1 + kStages) {
-      issue_loads(loads_issued);
-      ++loads_issued;
-    }
 
     // ---- MMA2: partial Z2 = X2 W2 over this CTA's hidden units
     TTT_ISSUE4(mma_tok_partial(tmem + C::TM_Z, smem_u32(sX2), smem_u32(sW2), NB),
@@ -386,7 +423,53 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       tc_fence_before_sync();      // the state columns are written by the fourth MMA group
     }
     wait_mma();
-    // ---- LN: Z2 summed over the cluster, then the fused LayerNorm + L2 gradient, U2 = -eta * dl/dZ2
+    // ---- LN: the partial Z2 tiles are summed by reduce-scatter; every CTA runs the fused LayerNorm + L2
+    // gradient, U2 = -eta * dl/dZ2, on the token rows it owns (all 256 threads, CPT columns of one row each)
+    // and hands its rows of U2 to the other CTAs' shared memories.
+    if constexpr (C::kRowSplit) {
+    {
+      float frag[16];
+      tok_ld(tm, tmem + C::TM_Z, frag);
+      const uint32_t tag = rs.send(frag, tid, warp, lane);
+      if (tid == 0) rs.arm_all_gather(ag_bar, 1);
+      const float2 b2c = *reinterpret_cast<const float2*>(sB2 + 2 * lane);
+      const float2 gam = *reinterpret_cast<const float2*>(sGamma + 2 * lane);
+      const float2 bet = *reinterpret_cast<const float2*>(sBeta + 2 * lane);
+      float2 kk[NR], vv[NR];
+      float neta[NR];
+#pragma unroll
+      for (int i = 0; i < NR; ++i) {
+        const int r = rs.row(i, warp);
+        kk[i] = C::RS::ld_pair(sK, r, lane);
+        vv[i] = C::RS::ld_pair(sV, r, lane);
+        neta[i] = -__bfloat162float(sEta[r]);
+      }
+      // while this sum is under way: the previous mini-batch's output, whose sum arrived long ago (b2 has
+      // not changed since: its update follows in the next MMA window)
+      if (zo_it >= 0) finish_out();
+      float z[NR][2];
+      rs.recv(z, warp, lane, tag);
+#pragma unroll
+      for (int i = 0; i < NR; ++i) {
+        z[i][0] += b2c.x;
+        z[i][1] += b2c.y;
+        const float mu = C::RS::row_sum(z[i][0] + z[i][1]) * (1.f / 64.f);
+        z[i][0] -= mu;
+        z[i][1] -= mu;
+        const float rstd = rsqrtf(C::RS::row_sum(fmaf(z[i][0], z[i][0], z[i][1] * z[i][1])) * (1.f / 64.f) + TTT_LN_EPS);
+        const float x0 = z[i][0] * rstd, x1 = z[i][1] * rstd;
+        const float g0 = (fmaf(gam.x, x0, bet.x) - (vv[i].x - kk[i].x)) * gam.x;
+        const float g1 = (fmaf(gam.y, x1, bet.y) - (vv[i].y - kk[i].y)) * gam.y;
+        const float a0 = C::RS::row_sum(g0 + g1);
+        const float a1 = C::RS::row_sum(fmaf(g0, x0, g1 * x1));
+        const float sc = neta[i] * rstd * (1.f / 64.f);
+        rs.all_gather_store(sU2, ag_bar, rs.row(i, warp), lane, (64.f * g0 - a0 - x0 * a1) * sc,
+                            (64.f * g1 - a0 - x1 * a1) * sc);
+      }
+    }
+    mbar_wait_cl(ag_bar, ag_phase, abort_flag, limit, kC);
+    ag_phase ^= 1u;
+    } else {
     {
       float xh[16], b2c[8], gam[8], bet[8];
       tok_ld(tm, tmem + C::TM_Z, xh);
@@ -432,7 +515,14 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       }
       tok_st_tile(tm, sU2, g);
     }
+    }
     publish();
+    // the previous mini-batch's Q tile has been read by every warp (its output is finished): its stage takes
+    // the loads of the mini-batch two ahead
+    if (tid == kProd && it >= 1 && loads_issued < NC && loads_issued == it - 1 + kStages) {
+      issue_loads(loads_issued);
+      ++loads_issued;
+    }
 
     // ---- MMA3: R^T = W2 U2^T
     TTT_ISSUE4(mma_hid64<false>(tmem + C::TM_A, smem_u32(sW2), smem_u32(sU2), 0u),
@@ -529,8 +619,14 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     // ---- OUT: Q + gamma * LN(Z2b + b2) + beta.  Z2b is an output only: its partial tiles are summed by
     // reduce-scatter, and every CTA normalises and stores the token rows it owns.  The partial tile is
     // sent now; it is received, normalised and stored inside the first MMA window of the next mini-batch.
-    tok_ld(tm, tmem + C::TM_Z, zo);
-    zo_tag = csum.reduce_scatter_send(zo, tid);
+    if constexpr (C::kRowSplit) {
+      float frag[16];
+      tok_ld(tm, tmem + C::TM_Z, frag);
+      zo_tag = rs.send(frag, tid, warp, lane);
+    } else {
+      tok_ld(tm, tmem + C::TM_Z, zo);
+      zo_tag = csum.reduce_scatter_send(zo, tid);
+    }
     zo_it = it;
     // the last CTA barrier of the mini-batch also takes the vote on leaving the loop: a peer can raise
     // this CTA's abort flag at any moment, and all 256 threads must see the same answer
@@ -540,7 +636,10 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     if (aborted) break;
   }
 #undef TTT_ISSUE4
-  if (!aborted && zo_it >= 0) finish_out();      // the last mini-batch's output
+  if (!aborted && zo_it >= 0) {                  // the last mini-batch's output
+    if constexpr (C::kRowSplit) finish_out();
+    else finish_out_whole();
+  }
 
   // ---- epilogue: optional final state, then teardown
   if (!aborted && p.W1f != nullptr) {
