@@ -216,10 +216,17 @@ int ttt_b200_version(void);
 
 /* How many CTAs (1, 2 or 4) the forward (backward = 0) or backward (backward != 0) launcher gives each
  * (batch, head) stream of a problem with `streams` = B*H streams on the current device when the flags leave
- * the choice to it: four when all CTAs fit on the GPU at once, else (forward only) two when those fit, else
- * one (measured thresholds); TTT_B200_CLUSTER overrides.  The reference fixes the split at compile time
+ * the choice to it: four when the device runs that many clusters of four at once
+ * (ttt_b200_cluster_capacity), else (forward only) two when those fit, else one (measured thresholds);
+ * TTT_B200_CLUSTER overrides.  The reference fixes the split at compile time
  * (kernels/ttt/ttt.cu:11-12, kernels/ttt_backward/ttt.cu:12-16).  Returns -1 on error. */
 int ttt_b200_pick_cluster(int streams, int backward);
+
+/* How many clusters of `cluster` (2 or 4) CTAs of the forward (backward = 0) or backward kernel the current
+ * device runs at the same time, from the CUDA occupancy query (a cluster lives inside one GPC, so this is
+ * less than SMs / cluster when the GPCs' SM counts are not multiples of it: 32 clusters of four on a 148-SM
+ * B200).  0 for other sizes or if the query fails.  No counterpart in the reference. */
+int ttt_b200_cluster_capacity(int cluster, int backward);
 
 /* Diagnostics (no counterpart in the reference): one CTA computes
  * D[M,N] = (+/-)A[M,K] * B[N,K]^T, `repeat` times accumulated, through the same shared-memory

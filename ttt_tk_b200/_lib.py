@@ -44,7 +44,7 @@ class BwdNoAllocArgs(ctypes.Structure):
 
 
 EXPORTS = ["ttt_b200_forward", "ttt_b200_backward", "ttt_b200_backward_noalloc", "ttt_b200_last_error", "ttt_b200_take_status",
-           "ttt_b200_version", "ttt_b200_pick_cluster", "ttt_b200_umma_selftest", "ttt_b200_wait_selftest", "ttt_b200_pack_tokens",
+           "ttt_b200_version", "ttt_b200_pick_cluster", "ttt_b200_cluster_capacity", "ttt_b200_umma_selftest", "ttt_b200_wait_selftest", "ttt_b200_pack_tokens",
            "ttt_b200_unpack_tokens", "ttt_b200_eta_gate", "ttt_b200_eta_gate_backward", "ttt_b200_unpack_layernorm",
            "ttt_b200_pack_layernorm_backward"]
 
@@ -72,6 +72,8 @@ def load():
     lib.ttt_b200_version.restype = ctypes.c_int
     lib.ttt_b200_pick_cluster.argtypes = [ctypes.c_int, ctypes.c_int]
     lib.ttt_b200_pick_cluster.restype = ctypes.c_int
+    lib.ttt_b200_cluster_capacity.argtypes = [ctypes.c_int, ctypes.c_int]
+    lib.ttt_b200_cluster_capacity.restype = ctypes.c_int
     lib.ttt_b200_umma_selftest.argtypes = [c_void_p, c_void_p, c_void_p] + [ctypes.c_int] * 7 + [c_void_p]
     lib.ttt_b200_umma_selftest.restype = ctypes.c_int
     lib.ttt_b200_wait_selftest.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_ulonglong), c_void_p]

@@ -49,9 +49,11 @@ constexpr int BAR_T = 5;       // +tile index (0..6)
 constexpr int BAR_IN = 12;     // +stage (0..1), recompute inputs
 constexpr int BAR_MMA = 14;
 constexpr int BAR_V = 15;      // recompute: the single V tile
-constexpr int BAR_SUM = 16;    // +buffer (0..1), cluster sums
-constexpr int BAR_DRAIN = 18;  // abort path only
-constexpr int NUM_BARS = 19;
+constexpr int BAR_SUM = 16;    // +buffer (0..3; the all-reduce form uses two), cluster sums
+constexpr int BAR_DRAIN = 20;  // abort path only
+constexpr int BAR_AG = 21;     // row-split form: rows of a stage's result arriving from the peers
+constexpr int BAR_AG2 = 22;    // the same for the deferred x_hat_ln
+constexpr int NUM_BARS = 23;
 
 template <int kC>
 struct Cfg {
@@ -59,10 +61,14 @@ struct Cfg {
   static constexpr int R = 64 * NB;
   static constexpr uint32_t HB = NB * TILE;            // bytes of an [R][64] bf16 tile
   using Sum = ClusterSum<kC, 18432>;                   // a 64 x 64 tile, optionally with two extra values per thread
+  // Four CTAs: the token stages are split by rows as well (every CTA runs them on the 16 token rows it owns
+  // and hands the bf16 results to its peers); measured slower than the all-reduce form at two CTAs.
+  static constexpr bool kRowSplit = kC == 4;
+  using RS = RowSplit<kC, true>;
   static constexpr uint32_t OFF_BIG = 0;               // 5 hidden-major buffers
   static constexpr uint32_t OFF_T = 5 * HB;            // 8 token tiles of 8 KB
   static constexpr uint32_t OFF_SUM = OFF_T + 8 * TILE;
-  static constexpr uint32_t OFF_B2 = OFF_SUM + Sum::kBytes;
+  static constexpr uint32_t OFF_B2 = OFF_SUM + (kRowSplit ? RS::kBytes : Sum::kBytes);
   static constexpr uint32_t OFF_GB2 = OFF_B2 + 256;
   static constexpr uint32_t OFF_GAMMA = OFF_GB2 + 256;
   static constexpr uint32_t OFF_BETA = OFF_GAMMA + 256;
@@ -72,12 +78,17 @@ struct Cfg {
   static constexpr uint32_t OFF_SIGF = OFF_SIGLN + 256;
   static constexpr uint32_t OFF_GB1 = OFF_SIGF + 256;       // fp32[R] copy of the per-thread dL/db1
   static constexpr uint32_t OFF_PART = OFF_GB1 + 1024;      // fp32[8][64] partial sums for d_eta (one row per warp)
-  static constexpr uint32_t OFF_CSUM = OFF_PART + 2048;     // fp32[3][4][64] column-sum partials
-  static constexpr uint32_t OFF_ETA = OFF_CSUM + 3072;      // bf16[2][64]
+  static constexpr uint32_t OFF_CSUM = OFF_PART + 2048;     // fp32[3][4][64] column-sum partials; row-split form: [4][64] + 2 x [8][64]
+  static constexpr uint32_t OFF_ETA = OFF_CSUM + 5120;      // bf16[2][64]
   static constexpr uint32_t OFF_BAR = OFF_ETA + 256;
   static constexpr uint32_t OFF_MISC = OFF_BAR + 192;
   static constexpr uint32_t OFF_XCH = OFF_MISC + 64;        // fp32[2][64][8] row-sum exchange between warp pairs
-  static constexpr uint32_t SMEM_USED = OFF_XCH + 4096;
+  // row-split form only: 1/std of x_hat_ln gathered from the row owners; d_gamma / d_beta addends of this
+  // CTA's own rows ([2][64]); rank 0's landing area for the peers' addends at the end ([kC][2][64])
+  static constexpr uint32_t OFF_SIGAG = OFF_XCH + 4096;
+  static constexpr uint32_t OFF_DGP = OFF_SIGAG + 256;
+  static constexpr uint32_t OFF_FIN = OFF_DGP + 512;
+  static constexpr uint32_t SMEM_USED = OFF_FIN + kC * 512;
   static constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;
   static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB per-CTA shared memory of sm_100");
   static_assert(NUM_BARS * 8 <= 192, "barrier area");
@@ -104,7 +115,7 @@ struct BwdClParams {
   float* d_gamma; float* d_beta;
   float* gW1; float* gb1; float* gW2; float* gb2;
   __nv_bfloat16* d_eta;
-  __nv_bfloat16* dXQ; __nv_bfloat16* dXK;               // bf16 [rows][64], row-major
+  __nv_bfloat16* dXQ; __nv_bfloat16* dXK; __nv_bfloat16* dXV;   // bf16 [rows][64], row-major
   int H, NC, cgs, nck;
   int drop_load;            // test only: mini-batch whose recompute inputs stream 0 never loads (-1: none)
   uint32_t* status;
@@ -151,6 +162,9 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   __nv_bfloat16* sEta = reinterpret_cast<__nv_bfloat16*>(smem + C::OFF_ETA);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   float* sXch = reinterpret_cast<float*>(smem + C::OFF_XCH);
+  float* sSigAG = reinterpret_cast<float*>(smem + C::OFF_SIGAG);
+  float* sDGp = reinterpret_cast<float*>(smem + C::OFF_DGP);       // [0..63] d_gamma, [64..127] d_beta addends of the own rows
+  float* sFin = reinterpret_cast<float*>(smem + C::OFF_FIN);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + C::OFF_MISC + 4);
   volatile uint32_t* never_flag = reinterpret_cast<volatile uint32_t*>(smem + C::OFF_MISC + 8);   // stays 0
@@ -160,7 +174,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     for (int i = 0; i < NUM_BARS; ++i) {
       uint32_t cnt = 1;
       if (i == BAR_MMA || i == BAR_DRAIN) cnt = 4;
-      if (i == BAR_SUM || i == BAR_SUM + 1) cnt = C::Sum::kArrivals;
+      if (i >= BAR_SUM && i < BAR_SUM + 4) cnt = C::kRowSplit ? C::RS::kBarCount : C::Sum::kArrivals;
       mbar_init(&bars[i], cnt);
     }
     fence_mbar_init();
@@ -184,6 +198,8 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     sGb2[tid] = p.gb2_last[sid * 64 + tid];
     sDG[tid] = 0.f;
     sDB[tid] = 0.f;
+    sDGp[tid] = 0.f;
+    sDGp[64 + tid] = 0.f;
   }
   float Gb1[NB][2];
 #pragma unroll
@@ -206,6 +222,15 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   csum.abort_flag = abort_flag;
   csum.limit = limit;
   auto cluster_sum = [&](float (&v)[16]) { csum.run(v, tid, lane); };
+  typename C::RS rs;
+  rs.bufp = smem + C::OFF_SUM;
+  rs.bars = &bars[BAR_SUM];
+  rs.n = 0;
+  rs.rank = rank;
+  rs.abort_flag = abort_flag;
+  rs.limit = limit;
+  constexpr int NR = C::RS::NR;
+  using RSx = typename C::RS;
 
   // ---- barrier bookkeeping: every thread waits on every barrier use, in program order
   uint32_t ph = 0;        // expected parity per barrier (indices 0..15)
@@ -427,6 +452,34 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         p.sc_sigln[zb_slot * 64 + tm.r1] = rs1;
       }
     };
+    // Row-split form: the sums of the rows this CTA owns are normalised here; the bf16 rows and their 1/std go
+    // to every CTA of the cluster (each keeps a whole tile for its scratch slot).
+    auto finish_xhln_rows = [&]() {
+      if (tid == 0) rs.arm_all_gather(&bars[BAR_AG2], 1, C::RS::ROWS * 4u);
+      const float2 b2c = *reinterpret_cast<const float2*>(sB2 + 2 * lane);
+      float z[NR][2];
+      rs.recv(z, warp, lane, zb_tag);
+#pragma unroll
+      for (int i = 0; i < NR; ++i) {
+        const int r = rs.row(i, warp);
+        z[i][0] += b2c.x;
+        z[i][1] += b2c.y;
+        const float mu = RSx::row_sum(z[i][0] + z[i][1]) * (1.f / 64.f);
+        z[i][0] -= mu;
+        z[i][1] -= mu;
+        const float rstd = rsqrtf(RSx::row_sum(fmaf(z[i][0], z[i][0], z[i][1] * z[i][1])) * (1.f / 64.f) + TTT_LN_EPS);
+        rs.all_gather_store(tXln, &bars[BAR_AG2], r, lane, z[i][0] * rstd, z[i][1] * rstd);
+        if (lane == 0) sSigAG[r] = rstd;
+        else if (lane < kC)
+          st_async_f1(mapa(smem_u32(sSigAG + r), rank ^ static_cast<uint32_t>(lane)),
+                      mapa(smem_u32(&bars[BAR_AG2]), rank ^ static_cast<uint32_t>(lane)), rstd);
+      }
+    };
+    // after the barrier that follows the wait on BAR_AG2: the gathered tile and its 1/std leave for the slot
+    auto store_xhln_rows = [&](long xslot) {
+      if (tid < 64) p.sc_sigln[xslot * 64 + tid] = sSigAG[tid];
+      if (tid == kProd) bulk_store_1d(p.sc_xhln + xslot * TILE, tXln, TILE);
+    };
     for (int j = 0; j < gsz; ++j) {
       const int s = j & 1;
       const long slot = slot0 + j;
@@ -441,10 +494,13 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                  if (NB > 1) HID_ONE(false, C::TM_A, bW1, sK, 0u, NB - 1),
                  ,
                  )
-      const long xhln_slot = zb_slot;          // the previous mini-batch's x_hat_ln, with the b2 it saw
-      if (zb_slot >= 0) {
-        finish_xhln();
-        zb_slot = -1;
+      long xhln_slot = -1;                     // the previous mini-batch's x_hat_ln, with the b2 it saw
+      if constexpr (!C::kRowSplit) {
+        xhln_slot = zb_slot;
+        if (zb_slot >= 0) {
+          finish_xhln();
+          zb_slot = -1;
+        }
       }
       wait_mma();
 #pragma unroll
@@ -480,7 +536,62 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                  )
       wait_mma();
       wait_bar(BAR_V);
-      {
+      long xrow_slot = -1;      // row-split form: the x_hat_ln gathered during this phase
+      if constexpr (C::kRowSplit) {
+        // the partial Z2 tiles are summed by reduce-scatter; the fused LayerNorm + L2 gradient runs on the token
+        // rows this CTA owns (warp = row pair, lane = column pair) and its rows of dl/dZ2 and U2 go to every CTA
+        float frag[16];
+        tok_ld(tm, tmem + C::TM_B, frag);
+        const uint32_t tag = rs.send(frag, tid, warp, lane);
+        if (tid == 0) rs.arm_all_gather(&bars[BAR_AG], 2);
+        const float2 b2c = *reinterpret_cast<const float2*>(sB2 + 2 * lane);
+        const float2 gam = *reinterpret_cast<const float2*>(sGamma + 2 * lane);
+        const float2 bet = *reinterpret_cast<const float2*>(sBeta + 2 * lane);
+        float2 kk[NR], vv[NR];
+        float neta[NR];
+#pragma unroll
+        for (int i = 0; i < NR; ++i) {
+          const int r = rs.row(i, warp);
+          kk[i] = RSx::ld_pair(sK, r, lane);
+          vv[i] = RSx::ld_pair(sV, r, lane);
+          neta[i] = -__bfloat162float(eta[r]);
+        }
+        // while this sum is under way: the previous mini-batch's x_hat_ln, whose sum arrived long ago (b2 has
+        // not changed since: its update follows in the next MMA window)
+        if (zb_slot >= 0) {
+          xrow_slot = zb_slot;
+          finish_xhln_rows();
+          zb_slot = -1;
+        }
+        float z[NR][2];
+        rs.recv(z, warp, lane, tag);
+#pragma unroll
+        for (int i = 0; i < NR; ++i) {
+          const int r = rs.row(i, warp);
+          z[i][0] += b2c.x;
+          z[i][1] += b2c.y;
+          const float mu = RSx::row_sum(z[i][0] + z[i][1]) * (1.f / 64.f);
+          z[i][0] -= mu;
+          z[i][1] -= mu;
+          const float rstd = rsqrtf(RSx::row_sum(fmaf(z[i][0], z[i][0], z[i][1] * z[i][1])) * (1.f / 64.f) + TTT_LN_EPS);
+          const float x0 = z[i][0] * rstd, x1 = z[i][1] * rstd;
+          const float g0 = (fmaf(gam.x, x0, bet.x) - (vv[i].x - kk[i].x)) * gam.x;
+          const float g1 = (fmaf(gam.y, x1, bet.y) - (vv[i].y - kk[i].y)) * gam.y;
+          const float a0 = RSx::row_sum(g0 + g1);
+          const float a1 = RSx::row_sum(fmaf(g0, x0, g1 * x1));
+          const float sc = rstd * (1.f / 64.f);
+          // x_hat_fused leaves through this CTA's rows of the V tile; dl/dZ2 is rounded to bf16 once (the update
+          // uses -eta times the rounded value)
+          RSx::st_pair(tV, r, lane, x0, x1);
+          const float d0 = __bfloat162float(__float2bfloat16((64.f * g0 - a0 - x0 * a1) * sc));
+          const float d1 = __bfloat162float(__float2bfloat16((64.f * g1 - a0 - x1 * a1) * sc));
+          rs.all_gather_store(tGZ2, &bars[BAR_AG], r, lane, d0, d1);
+          rs.all_gather_store(tU2, &bars[BAR_AG], r, lane, neta[i] * d0, neta[i] * d1);
+          if (lane == 0) p.sc_sigf[slot * 64 + r] = rstd;
+        }
+        wait_bar(BAR_AG);
+        if (xrow_slot >= 0) wait_bar(BAR_AG2);
+      } else {
         float xh[16], b2c[8], gam[8], bet[8];
         tok_ld(tm, tmem + C::TM_B, xh);
         cluster_sum(xh);
@@ -545,8 +656,16 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       publish();
 
       // MMA3: R^T = W2 gZ2^T
+      if constexpr (C::kRowSplit) {
+        if (xrow_slot >= 0) store_xhln_rows(xrow_slot);
+      }
       if (tid == kProd) {
-        bulk_store_1d(p.sc_xhf + slot * TILE, tV, TILE);
+        if constexpr (C::kRowSplit) {   // only the rows this CTA owns hold x_hat_fused (the others still hold V)
+          constexpr uint32_t RB = C::RS::ROWS * 128u;
+          bulk_store_1d(p.sc_xhf + slot * TILE + rank * RB, tV + rank * RB, RB);
+        } else {
+          bulk_store_1d(p.sc_xhf + slot * TILE, tV, TILE);
+        }
         bulk_store_1d(p.sc_gZ2 + slot * TILE, tGZ2, TILE);
         tma_commit_group();
       }
@@ -662,7 +781,8 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       // recompute waits for it.  Its partial tile is sent now; the sum is received and normalised inside the
       // first MMA window of the next mini-batch (or right after the group's last one).
       tok_ld(tm, tmem + C::TM_B, zb);
-      zb_tag = csum.allreduce_send(zb, tid);
+      if constexpr (C::kRowSplit) zb_tag = rs.send(zb, tid, warp, lane);
+      else zb_tag = csum.allreduce_send(zb, tid);
       zb_slot = slot;
       if (tid == kProd) tma_wait_group_read<0>();   // every big image of this mini-batch has left shared memory
       aborted = publish_vote();
@@ -670,7 +790,13 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       if (aborted) break;
     }
     if (aborted) break;
-    {   // the group's last x_hat_ln
+    if constexpr (C::kRowSplit) {   // the group's last x_hat_ln
+      finish_xhln_rows();
+      wait_bar(BAR_AG2);
+      publish();
+      store_xhln_rows(zb_slot);
+      if (tid == kProd) tma_commit_group();
+    } else {
       finish_xhln();
       publish();
       if (tid == kProd) {
@@ -745,6 +871,15 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     float dk_pend[16];          // a step's share of dK between its send and its receive
     uint32_t dk_tag = 0;
     int dk_row0 = -1;
+    float dk_gly[NR][2];        // row-split form: the LayerNorm term of dK for the rows this CTA owns
+    auto finish_dk_rows = [&]() {
+      float z[NR][2];
+      rs.recv(z, warp, lane, dk_tag);
+#pragma unroll
+      for (int i = 0; i < NR; ++i)
+        RSx::st_pair_global(p.dXK + static_cast<long>(dk_row0) * 64, rs.row(i, warp), lane, z[i][0] + dk_gly[i][0],
+                            z[i][1] + dk_gly[i][1]);
+    };
     for (int j = gsz - 1; j >= 0; --j) {
       const long slot = slot0 + j;
       const int row0 = static_cast<int>(tok_rows0 + (long)(i0 + j) * 64);
@@ -810,7 +945,11 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         }
       }
       if (dk_row0 >= 0) {     // the previous step's dK
-        if (csum.reduce_scatter_recv(dk_pend, tid, dk_tag)) tok_st_global(tm, p.dXK + static_cast<long>(dk_row0) * 64, dk_pend);
+        if constexpr (C::kRowSplit) {
+          finish_dk_rows();
+        } else {
+          if (csum.reduce_scatter_recv(dk_pend, tid, dk_tag)) tok_st_global(tm, p.dXK + static_cast<long>(dk_row0) * 64, dk_pend);
+        }
         dk_row0 = -1;
       }
       wait_mma();
@@ -885,7 +1024,9 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       // received inside the next MMA window: nobody waits for the exchange.
       float dq[16];
       tok_ld(tm, tmem + C::TM_B, dq);
-      const uint32_t dq_tag = csum.reduce_scatter_send(dq, tid);
+      uint32_t dq_tag;
+      if constexpr (C::kRowSplit) dq_tag = rs.send(dq, tid, warp, lane);
+      else dq_tag = csum.reduce_scatter_send(dq, tid);
       publish();
       wait_bar(BAR_BIG + ib4);
       wait_bar(BAR_T + 4);
@@ -917,7 +1058,17 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         }
         *reinterpret_cast<float2*>(sPart + warp * 64 + 2 * lane) = make_float2(a0 + c0, a1 + c1);
       }
-      if (csum.reduce_scatter_recv(dq, tid, dq_tag)) {
+      if constexpr (C::kRowSplit) {
+        float2 go[NR];
+#pragma unroll
+        for (int i = 0; i < NR; ++i) go[i] = RSx::ld_pair(t_go, rs.row(i, warp), lane);
+        float z[NR][2];
+        rs.recv(z, warp, lane, dq_tag);
+#pragma unroll
+        for (int i = 0; i < NR; ++i)
+          RSx::st_pair_global(p.dXQ + static_cast<long>(row0) * 64, rs.row(i, warp), lane, go[i].x + z[i][0],
+                              go[i].y + z[i][1]);
+      } else if (csum.reduce_scatter_recv(dq, tid, dq_tag)) {
         float go[16];
         tok_ld_tile(tm, t_go, go);
 #pragma unroll
@@ -976,7 +1127,99 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       wait_bar(BAR_T + 6);
       wait_bar(BAR_T + 1);   // V
       // ---- E4: second order through the fused LayerNorm + L2 gradient (token-major, all 8 warps)
-      {
+      if constexpr (C::kRowSplit) {
+        // Row-split form.  Fragment side: this CTA's shares X2 G_W2 (acc1), P W2 (acc2), gZ1 G_W1 (t1); what the
+        // step needs from them is linear: A2 = -eta acc1 + acc2 and the d_eta row sums of gz acc1 + t1 K travel
+        // to the owner of the rows, -eta t1 stays for dK.  U2 = -eta gZ2 needs no sum: every CTA writes all of it.
+        uint32_t a2_tag;
+        {
+          float A2[16], gz[16], kk[16], acc1[16], acc2[16], t1[16];
+          const float eta0 = __bfloat162float(sEta[tm.r0]), eta1 = __bfloat162float(sEta[tm.r1]);
+          tok_ld_tile(tm, t_gz2, gz);
+          tok_ld_tile(tm, t_k, kk);
+          tok_ld3(tm, tmem + C::TM_B + 64, acc1, tmem + C::TM_A, acc2, tmem + C::TM_B, t1);
+          float de0 = 0.f, de1 = 0.f;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int x0 = 4 * q + h, x1 = 4 * q + 2 + h;
+              A2[x0] = fmaf(-eta0, acc1[x0], acc2[x0]);
+              A2[x1] = fmaf(-eta1, acc1[x1], acc2[x1]);
+              de0 = fmaf(gz[x0], acc1[x0], fmaf(t1[x0], kk[x0], de0));
+              de1 = fmaf(gz[x1], acc1[x1], fmaf(t1[x1], kk[x1], de1));
+              kp[x0] = -eta0 * t1[x0];
+              kp[x1] = -eta1 * t1[x1];
+              gz[x0] *= -eta0;
+              gz[x1] *= -eta1;
+            }
+          }
+          if (row_writer) {     // the partial sums over this CTA's hidden units of gZ1 * G_b1, once per row
+#pragma unroll
+            for (int w = 0; w < 8; ++w) {
+              de0 += sPart[w * 64 + tm.r0];
+              de1 += sPart[w * 64 + tm.r1];
+            }
+          }
+          a2_tag = rs.send_x(A2, de0, de1, tid, warp, lane);
+          if (tid == 0) rs.arm_all_gather(&bars[BAR_AG], 1);
+          tok_st_tile(tm, t_g, gz);
+        }
+        // Row side: the rows this CTA owns (warp = row pair, lane = column pair)
+        const float2 gam = *reinterpret_cast<const float2*>(sGamma + 2 * lane);
+        const float2 bet = *reinterpret_cast<const float2*>(sBeta + 2 * lane);
+        const float2 gb2 = *reinterpret_cast<const float2*>(sGb2 + 2 * lane);
+        float2 gzr[NR], xh[NR], vv[NR], kr[NR];
+        float etar[NR], rsd[NR];
+#pragma unroll
+        for (int i = 0; i < NR; ++i) {
+          const int r = rs.row(i, warp);
+          gzr[i] = RSx::ld_pair(t_gz2, r, lane);
+          xh[i] = RSx::ld_pair(t_xf, r, lane);
+          vv[i] = RSx::ld_pair(t_a, r, lane);
+          kr[i] = RSx::ld_pair(t_k, r, lane);
+          etar[i] = __bfloat162float(sEta[r]);
+          rsd[i] = sSigF[r];       // 1 / std
+        }
+        float z[NR][2], ex[NR];
+        rs.recv_x(z, ex, warp, lane, a2_tag);
+        float ca0 = 0.f, ca1 = 0.f, cv0 = 0.f, cv1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < NR; ++i) {
+          const int r = rs.row(i, warp);
+          const float rstd = rsd[i];
+          // grad_output_fused = gamma x_hat_fused + beta - (V - K)
+          const float go0 = fmaf(gam.x, xh[i].x, bet.x) - (vv[i].x - kr[i].x);
+          const float go1 = fmaf(gam.y, xh[i].y, bet.y) - (vv[i].y - kr[i].y);
+          // the G_b2 parts of u = acc1 + G_b2
+          const float A0 = fmaf(-etar[i], gb2.x, z[i][0]), A1 = fmaf(-etar[i], gb2.y, z[i][1]);
+          const float de = ex[i] + RSx::row_sum(fmaf(gzr[i].x, gb2.x, gzr[i].y * gb2.y));
+          const float s2 = RSx::row_sum(A0 + A1);
+          const float s3 = RSx::row_sum(fmaf(A0, xh[i].x, A1 * xh[i].y));
+          const float s4 = RSx::row_sum(fmaf(go0 * gam.x, xh[i].x, go1 * gam.y * xh[i].y));
+          const float bt0 = (A0 - (s2 + xh[i].x * s3) * (1.f / 64.f)) * rstd;
+          const float bt1 = (A1 - (s2 + xh[i].y * s3) * (1.f / 64.f)) * rstd;
+          const float gly0 = gam.x * bt0, gly1 = gam.y * bt1;
+          ca0 += fmaf(go0, bt0, gly0 * xh[i].x);      // d_gamma addends
+          ca1 += fmaf(go1, bt1, gly1 * xh[i].y);
+          cv0 += gly0;                                // d_beta addends
+          cv1 += gly1;
+          dk_gly[i][0] = gly0;
+          dk_gly[i][1] = gly1;
+          RSx::st_pair_global(p.dXV + static_cast<long>(row0) * 64, r, lane, -gly0, -gly1);
+          const float gx0 = fmaf(gly0, gam.x, -(go0 * gam.x * s3 + A0 * s4) * rstd * (1.f / 64.f));
+          const float gx1 = fmaf(gly1, gam.y, -(go1 * gam.y * s3 + A1 * s4) * rstd * (1.f / 64.f));
+          const float sa0 = RSx::row_sum(((-gx0 * xh[i].x - A0 * gzr[i].x) + (-gx1 * xh[i].y - A1 * gzr[i].y)) * rstd);
+          const float sa1 = RSx::row_sum(gx0 + gx1);
+          rs.all_gather_store(t_q, &bars[BAR_AG], r, lane,
+                              fmaf(gx0, rstd, (sa0 * xh[i].x - sa1 * rstd) * (1.f / 64.f)),      // gZ2in
+                              fmaf(gx1, rstd, (sa0 * xh[i].y - sa1 * rstd) * (1.f / 64.f)));
+          if (lane == 0) p.d_eta[(sid * NC + i0 + j) * 64 + r] = __float2bfloat16(-de);
+        }
+        *reinterpret_cast<float2*>(part + 256 + warp * 64 + 2 * lane) = make_float2(ca0, ca1);
+        *reinterpret_cast<float2*>(part + 768 + warp * 64 + 2 * lane) = make_float2(cv0, cv1);
+        wait_bar(BAR_AG);
+      } else {
         float A2[16], gz[16], xh[16], go[16];
         float gam[8];
         tok_ld_cols(tm, sGamma, gam);
@@ -1102,15 +1345,31 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       }
       publish();
       // G11 (+ G_W2snap U2^T) // G12
-      if (tid == kProd && (turn + 1) % kC == rank) {
-        tma_store_2d(&tmDV, t_go, 0, row0);
-        tma_commit_group();
+      if constexpr (!C::kRowSplit) {
+        if (tid == kProd && (turn + 1) % kC == rank) {
+          tma_store_2d(&tmDV, t_go, 0, row0);
+          tma_commit_group();
+        }
       }
       TTT_ISSUE4(HID_ONE(false, C::TM_B, big(ib1), t_q, 0u, 0); HID_ONE(false, C::TM_B, big(ib3), t_g, 1u, 0),
                  if (NB > 1) { HID_ONE(false, C::TM_B, big(ib1), t_q, 0u, NB - 1); HID_ONE(false, C::TM_B, big(ib3), t_g, 1u, NB - 1); },
                  HID_ONE(false, C::TM_A, big(ib1), t_gz2, 0u, 0),
                  if (NB > 1) HID_ONE(false, C::TM_A, big(ib1), t_gz2, 0u, NB - 1))
-      {
+      if constexpr (C::kRowSplit) {
+        part[tid] = colsum16(t_q);      // the gathered gZ2in tile: G_b2 stays replicated
+        __syncthreads();
+        if (tid < 64) {
+          sGb2[tid] += part_sum(0);
+          float a = 0.f, v = 0.f;       // this CTA's rows only: summed over the cluster at the end
+#pragma unroll
+          for (int w = 0; w < 8; ++w) {
+            a += part[256 + w * 64 + tid];
+            v += part[768 + w * 64 + tid];
+          }
+          sDGp[tid] += a;
+          sDGp[64 + tid] += v;
+        }
+      } else {
         part[tid] = colsum16(t_q);
         part[256 + tid] = colsum16(t_a);
         part[512 + tid] = colsum16(t_go);
@@ -1182,7 +1441,8 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         tok_ld(tm, tmem + C::TM_A, acc);
 #pragma unroll
         for (int q = 0; q < 16; ++q) dk_pend[q] = kp[q] + acc[q];
-        dk_tag = csum.reduce_scatter_send(dk_pend, tid);
+        if constexpr (C::kRowSplit) dk_tag = rs.send(dk_pend, tid, warp, lane);
+        else dk_tag = csum.reduce_scatter_send(dk_pend, tid);
         dk_row0 = row0;
       }
       aborted = publish_vote();
@@ -1195,8 +1455,12 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       if (aborted) break;
     }
     if (aborted) break;
-    if (dk_row0 >= 0 && csum.reduce_scatter_recv(dk_pend, tid, dk_tag))      // the group's last dK
-      tok_st_global(tm, p.dXK + static_cast<long>(dk_row0) * 64, dk_pend);
+    if constexpr (C::kRowSplit) {      // the group's last dK
+      if (dk_row0 >= 0) finish_dk_rows();
+    } else {
+      if (dk_row0 >= 0 && csum.reduce_scatter_recv(dk_pend, tid, dk_tag))
+        tok_st_global(tm, p.dXK + static_cast<long>(dk_row0) * 64, dk_pend);
+    }
     if (tid == kProd) tma_wait_group_read<0>();   // the last dV has left its tile (the recompute writes it again)
 
     // ---- park the gradient state (tensor memory -> grad_L_W*_init); the last group leaves the result
@@ -1226,7 +1490,30 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         p.gb1[sid * 256 + hid0 + 64 * b + tm.r1] = Gb1[b][1];
       }
     }
-    if (rank == 0 && tid < 64) {
+    if constexpr (C::kRowSplit) {
+      // d_gamma / d_beta: the replicated addends (output LayerNorm) plus every CTA's own-row addends, summed by
+      // rank 0 in rank order
+      if (rank == 0) {
+        if (tid == 0) mbar_expect_tx(&bars[BAR_AG], (kC - 1) * 512u);
+      } else if (tid < 32) {
+        const float4 v = reinterpret_cast<const float4*>(sDGp)[tid];
+        st_async_f4(mapa(smem_u32(sFin + rank * 128 + tid * 4), 0), mapa(smem_u32(&bars[BAR_AG]), 0), v.x, v.y, v.z, v.w);
+      }
+      if (rank == 0) {
+        wait_bar(BAR_AG);
+        if (tid < 64) {
+          float dg = sDG[tid] + sDGp[tid], db = sDB[tid] + sDGp[64 + tid];
+#pragma unroll
+          for (int r = 1; r < kC; ++r) {
+            dg += sFin[r * 128 + tid];
+            db += sFin[r * 128 + 64 + tid];
+          }
+          p.gb2[sid * 64 + tid] = sGb2[tid];
+          p.d_gamma[sid * 64 + tid] = dg;
+          p.d_beta[sid * 64 + tid] = db;
+        }
+      }
+    } else if (rank == 0 && tid < 64) {
       p.gb2[sid * 64 + tid] = sGb2[tid];
       p.d_gamma[sid * 64 + tid] = sDG[tid];
       p.d_beta[sid * 64 + tid] = sDB[tid];
@@ -1255,8 +1542,9 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   if (warp == 0) tmem_dealloc(tmem, C::TM_COLS);
 }
 
+// Once per device: the kernel's dynamic shared memory limit.
 template <int kC>
-int launch_cluster(const CUtensorMap* tm, const BwdClParams& p, int streams, cudaStream_t stream) {
+int prepare_kernel() {
   using C = Cfg<kC>;
   static std::once_flag once[64];
   static cudaError_t attr_err[64];
@@ -1264,10 +1552,48 @@ int launch_cluster(const CUtensorMap* tm, const BwdClParams& p, int streams, cud
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return ttt_set_error(TTT_B200_ERR_LAUNCH, "device index out of range");
   std::call_once(once[dev], [&] {
-    attr_err[dev] = cudaFuncSetAttribute(ttt_bwd_cluster_kernel<kC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         C::SMEM_BYTES);
+    attr_err[dev] = cudaFuncSetAttribute(ttt_bwd_cluster_kernel<kC>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   });
   if (attr_err[dev] != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(attr_err[dev]));
+  return TTT_B200_OK;
+}
+
+// How many clusters of kC CTAs the device runs at once (a cluster lives inside one GPC, and the GPCs' SM counts
+// are not all multiples of kC: fewer than SMs / kC).  0 if the query fails.
+template <int kC>
+int cluster_capacity() {
+  using C = Cfg<kC>;
+  static std::once_flag once[64];
+  static int cap[64];
+  if (prepare_kernel<kC>()) return 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::call_once(once[dev], [&] {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(kC * 64);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kC;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, ttt_bwd_cluster_kernel<kC>, &cfg) != cudaSuccess) {
+      cudaGetLastError();
+      n = 0;
+    }
+    cap[dev] = n;
+  });
+  return cap[dev];
+}
+
+template <int kC>
+int launch_cluster(const CUtensorMap* tm, const BwdClParams& p, int streams, cudaStream_t stream) {
+  using C = Cfg<kC>;
+  if (int rc = prepare_kernel<kC>()) return rc;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(streams) * kC);
   cfg.blockDim = dim3(kThreads);
@@ -1318,6 +1644,7 @@ int ttt_launch_backward_cluster(const ttt_b200_bwd_args* a, int cluster, cudaStr
   p.d_eta = static_cast<__nv_bfloat16*>(a->grad_L_last_eta);
   p.dXQ = static_cast<__nv_bfloat16*>(a->grad_L_XQ);
   p.dXK = static_cast<__nv_bfloat16*>(a->grad_L_XK);
+  p.dXV = static_cast<__nv_bfloat16*>(a->grad_L_XV);
   p.H = a->H; p.NC = a->NC; p.cgs = a->checkpoint_group_size; p.nck = a->num_checkpoints;
   p.drop_load = drop_load;
   p.status = status;
@@ -1326,4 +1653,8 @@ int ttt_launch_backward_cluster(const ttt_b200_bwd_args* a, int cluster, cudaStr
   if (cluster == 2) return launch_cluster<2>(tm, p, streams, stream);
   if (cluster == 4) return launch_cluster<4>(tm, p, streams, stream);
   return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "cluster size must be 2 or 4");
+}
+
+int ttt_backward_cluster_capacity(int cluster) {
+  return cluster == 2 ? cluster_capacity<2>() : cluster == 4 ? cluster_capacity<4>() : 0;
 }

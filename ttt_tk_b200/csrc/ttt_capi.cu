@@ -21,6 +21,8 @@ int ttt_launch_backward(const ttt_b200_bwd_args* a, cudaStream_t stream, uint32_
                         int drop_load);
 int ttt_launch_backward_cluster(const ttt_b200_bwd_args* a, int cluster, cudaStream_t stream, uint32_t* status,
                                 uint64_t limit_ns, int drop_load);
+int ttt_forward_cluster_capacity(int cluster);
+int ttt_backward_cluster_capacity(int cluster);
 int ttt_launch_forward_cluster(const ttt_b200_fwd_args* a, int cluster, cudaStream_t stream, uint32_t* status,
                                uint64_t limit_ns, int drop_load);
 
@@ -57,21 +59,6 @@ namespace {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// SM count of the current device (cached per device index).
-int sm_count() {
-  static std::mutex mu;
-  static int cached[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  std::lock_guard<std::mutex> lk(mu);
-  if (cached[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) n = 148;
-    cached[dev] = n;
-  }
-  return cached[dev];
-}
-
 }  // namespace
 
 // How many CTAs share one stream.  The mini-batches of a stream are strictly sequential, so with fewer
@@ -97,8 +84,13 @@ int ttt_pick_cluster(int streams, uint32_t flags, bool backward, int* cluster) {
     *cluster = forced;
     return TTT_B200_OK;
   }
-  const int sms = sm_count();
-  *cluster = 4 * streams <= sms ? 4 : (!backward && 2 * streams <= sms ? 2 : 1);
+  // all streams must be resident at once for the sharding to pay: the widest cluster size whose capacity
+  // (clusters the device runs at the same time) covers them.  The backward gains nothing from two CTAs per
+  // stream beyond the stream counts four CTAs cover (measured), so it never picks two.
+  auto capacity = [&](int c) { return backward ? ttt_backward_cluster_capacity(c) : ttt_forward_cluster_capacity(c); };
+  if (streams <= capacity(4)) *cluster = 4;
+  else if (!backward && streams <= capacity(2)) *cluster = 2;
+  else *cluster = 1;
   return TTT_B200_OK;
 }
 
@@ -277,6 +269,10 @@ extern "C" int ttt_b200_take_status(void) {
 }
 
 extern "C" int ttt_b200_version(void) { return 1001; }
+
+extern "C" int ttt_b200_cluster_capacity(int cluster, int backward) {
+  return backward ? ttt_backward_cluster_capacity(cluster) : ttt_forward_cluster_capacity(cluster);
+}
 
 extern "C" int ttt_b200_pick_cluster(int streams, int backward) {
   int c = 1;

@@ -156,6 +156,11 @@ __device__ __forceinline__ void st_async_f4(uint32_t addr, uint32_t bar, float a
                "r"(bar), "f"(a), "f"(b), "f"(c), "f"(d)
                : "memory");
 }
+__device__ __forceinline__ void st_async_f1(uint32_t cluster_addr, uint32_t cluster_bar, float a) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.f32 [%0], %2, [%1];" ::"r"(cluster_addr),
+               "r"(cluster_bar), "f"(a)
+               : "memory");
+}
 __device__ __forceinline__ void st_async_f2(uint32_t addr, uint32_t bar, float a, float b) {
   asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.f32 [%0], {%2, %3}, [%1];" ::"r"(addr),
                "r"(bar), "f"(a), "f"(b)
@@ -370,12 +375,16 @@ struct ClusterSum {
 // Row layout of the stage: warp w works on row pair w of each of the CTA's QPC quadrants, lane l on the
 // column pair l: NR = 2 QPC rows x 2 columns per thread; a row lives in one warp, so row sums are five
 // xor-shuffles.
-template <int kC>
+// kExtras: a slot also has room for two extra per-row values from each of the 8 fragment threads that share
+// a row pair ([quadrant][row pair][colhalf x 4 + lane % 4] float2 after the tile), which send_x / recv_x sum
+// over the contributors as well: per-row scalars that are linear in the partial tiles travel with them.
+template <int kC, bool kExtras = false>
 struct RowSplit {
   static constexpr int QPC = 4 / kC;                          // fragment quadrants per CTA
   static constexpr int ROWS = 16 * QPC;
   static constexpr int NR = 2 * QPC;                          // rows per thread in the row layout
-  static constexpr uint32_t kSlotBytes = QPC * 4096u;
+  static constexpr uint32_t kTileBytes = QPC * 4096u;
+  static constexpr uint32_t kSlotBytes = kTileBytes + (kExtras ? QPC * 512u : 0u);
   static constexpr uint32_t kBufBytes = kC * kSlotBytes;      // 16 KB
   static constexpr int kBufs = 4;
   static constexpr uint32_t kBytes = kBufs * kBufBytes;
@@ -392,28 +401,42 @@ struct RowSplit {
   static __device__ __forceinline__ uint32_t owner_of(int warp) { return static_cast<uint32_t>(warp & 3) / QPC; }
   // Send this thread's 16 partial values to the owner of its rows (or file them in this CTA's own slot).
   // Returns the tag for recv().
-  __device__ __forceinline__ uint32_t send(const float (&v)[16], int tid, int warp, int lane) {
+  template <bool kX>
+  __device__ __forceinline__ uint32_t send_impl(const float (&v)[16], float e0, float e1, int tid, int warp, int lane) {
+    static_assert(!kX || kExtras, "this exchange area has no room for extra values");
     const uint32_t b = n & 3u, par = (n >> 2) & 1u;
     ++n;
     const uint32_t owner = owner_of(warp);
     const uint32_t lq = static_cast<uint32_t>(warp & 3) % QPC, colhalf = static_cast<uint32_t>(warp >> 2);
-    const uint32_t off = b * kBufBytes + rank * kSlotBytes + lq * 4096u + static_cast<uint32_t>(lane >> 2) * 512u +
+    const uint32_t slot = b * kBufBytes + rank * kSlotBytes;
+    const uint32_t off = slot + lq * 4096u + static_cast<uint32_t>(lane >> 2) * 512u +
                          (colhalf * 16u + static_cast<uint32_t>(lane & 3)) * 16u;
-    if (tid == 0) mbar_expect_tx(&bars[b], (kC - 1) * kSlotBytes);
+    const uint32_t xoff = slot + kTileBytes + lq * 512u + static_cast<uint32_t>(lane >> 2) * 64u +
+                          (colhalf * 4u + static_cast<uint32_t>(lane & 3)) * 8u;
+    if (tid == 0) mbar_expect_tx(&bars[b], (kC - 1) * (kX ? kSlotBytes : kTileBytes));
     if (owner != rank) {
       const uint32_t dst = mapa(smem_u32(bufp) + off, owner);
       const uint32_t rbar = mapa(smem_u32(&bars[b]), owner);
 #pragma unroll
       for (int j = 0; j < 4; ++j)
         st_async_f4(dst + j * 64u, rbar, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+      if constexpr (kX) st_async_f2(mapa(smem_u32(bufp) + xoff, owner), rbar, e0, e1);
     } else {
       float4* dst = reinterpret_cast<float4*>(bufp + off);
 #pragma unroll
       for (int j = 0; j < 4; ++j) dst[j * 4] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+      if constexpr (kX) *reinterpret_cast<float2*>(bufp + xoff) = make_float2(e0, e1);
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars[b]);
     }
     return b | (par << 2);
+  }
+  __device__ __forceinline__ uint32_t send(const float (&v)[16], int tid, int warp, int lane) {
+    return send_impl<false>(v, 0.f, 0.f, tid, warp, lane);
+  }
+  // e0 / e1: this thread's contributions to the extra value of its rows r0 / r1
+  __device__ __forceinline__ uint32_t send_x(const float (&v)[16], float e0, float e1, int tid, int warp, int lane) {
+    return send_impl<true>(v, e0, e1, tid, warp, lane);
   }
 
   // ---- row side: row i of the thread (i = 2 lq + h) is token row 16 (QPC rank + lq) + warp + 8 h of the tile
@@ -437,6 +460,29 @@ struct RowSplit {
       z[2 * lq + 1][0] = acc.z; z[2 * lq + 1][1] = acc.w;
     }
   }
+  // recv() plus the extra values: e[i] = the sum over all CTAs and contributors for row i (all lanes get it)
+  __device__ __forceinline__ void recv_x(float (&z)[NR][2], float (&e)[NR], int warp, int lane, uint32_t tag) {
+    recv(z, warp, lane, tag);
+    const uint32_t b = tag & 3u;
+    const uint8_t* base = bufp + b * kBufBytes + kTileBytes + static_cast<uint32_t>(warp) * 64u +
+                          static_cast<uint32_t>(lane & 7) * 8u;
+#pragma unroll
+    for (int lq = 0; lq < QPC; ++lq) {
+      float2 acc = *reinterpret_cast<const float2*>(base + lq * 512u);
+#pragma unroll
+      for (int s = 1; s < kC; ++s) {
+        const float2 f = *reinterpret_cast<const float2*>(base + s * kSlotBytes + lq * 512u);
+        acc.x += f.x; acc.y += f.y;
+      }
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) {       // lanes 0..7 hold the eight contributors (the others repeat them)
+        acc.x += __shfl_xor_sync(0xffffffffu, acc.x, o);
+        acc.y += __shfl_xor_sync(0xffffffffu, acc.y, o);
+      }
+      e[2 * lq] = acc.x;
+      e[2 * lq + 1] = acc.y;
+    }
+  }
   static __device__ __forceinline__ float row_sum(float x) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
@@ -447,6 +493,9 @@ struct RowSplit {
     const uint32_t w = *reinterpret_cast<const uint32_t*>(tile + sw128_off(r, lane >> 2) + (lane & 3) * 4);
     return make_float2(bf16_lo(w), bf16_hi(w));
   }
+  static __device__ __forceinline__ void st_pair(uint8_t* tile, int r, int lane, float a, float b) {
+    *reinterpret_cast<uint32_t*>(tile + sw128_off(r, lane >> 2) + (lane & 3) * 4) = pack_bf16(a, b);
+  }
   static __device__ __forceinline__ void st_pair_global(__nv_bfloat16* tile, int r, int lane, float a, float b) {
     *reinterpret_cast<uint32_t*>(tile + r * 64 + 2 * lane) = pack_bf16(a, b);
   }
@@ -456,8 +505,19 @@ struct RowSplit {
   // `ag_bar`, into the same place of every peer's tile (four neighbouring lanes make up one 16-byte chunk;
   // all 32 lanes call this).  The receiver waits on its `ag_bar` (armed by arm_all_gather) and runs the usual
   // proxy fence + CTA barrier before an MMA reads the tile.
-  __device__ __forceinline__ void arm_all_gather(uint64_t* ag_bar, int ntiles) const {
-    mbar_expect_tx(ag_bar, (kC - 1) * ROWS * 128u * static_cast<uint32_t>(ntiles));
+  __device__ __forceinline__ void arm_all_gather(uint64_t* ag_bar, int ntiles, uint32_t extra_bytes = 0) const {
+    mbar_expect_tx(ag_bar, (kC - 1) * (ROWS * 128u * static_cast<uint32_t>(ntiles) + extra_bytes));
+  }
+  // four fp32 values (16 bytes at `dst`, the same address in every CTA) to this CTA and every peer, counted on
+  // the peers' `ag_bar` like the tiles of an all-gather
+  __device__ __forceinline__ void all_gather_f4(float* dst, uint64_t* ag_bar, float a, float b, float c, float d) const {
+    *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d);
+    const uint32_t adr = smem_u32(dst), ba = smem_u32(ag_bar);
+#pragma unroll
+    for (int s = 1; s < kC; ++s) {
+      const uint32_t peer = rank ^ static_cast<uint32_t>(s);
+      st_async_f4(mapa(adr, peer), mapa(ba, peer), a, b, c, d);
+    }
   }
   __device__ __forceinline__ void all_gather_store(uint8_t* tile, uint64_t* ag_bar, int r, int lane, float a, float b) const {
     const uint32_t w0 = pack_bf16(a, b);

@@ -676,9 +676,9 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   if (warp == 0) tmem_dealloc(tmem, C::TM_COLS);
 }
 
+// Once per device: the kernel's dynamic shared memory limit.
 template <int kC>
-int launch_cluster(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const CUtensorMap& tmOut,
-                   const FwdClParams& p, int streams, cudaStream_t stream) {
+int prepare_kernel() {
   using C = Cfg<kC>;
   static std::once_flag once[64];
   static cudaError_t attr_err[64];
@@ -686,10 +686,49 @@ int launch_cluster(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtenso
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return ttt_set_error(TTT_B200_ERR_LAUNCH, "device index out of range");
   std::call_once(once[dev], [&] {
-    attr_err[dev] = cudaFuncSetAttribute(ttt_fwd_cluster_kernel<kC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         C::SMEM_BYTES);
+    attr_err[dev] = cudaFuncSetAttribute(ttt_fwd_cluster_kernel<kC>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   });
   if (attr_err[dev] != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(attr_err[dev]));
+  return TTT_B200_OK;
+}
+
+// How many clusters of kC CTAs the device runs at once (a cluster lives inside one GPC, and the GPCs' SM counts
+// are not all multiples of kC: fewer than SMs / kC).  0 if the query fails.
+template <int kC>
+int cluster_capacity() {
+  using C = Cfg<kC>;
+  static std::once_flag once[64];
+  static int cap[64];
+  if (prepare_kernel<kC>()) return 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::call_once(once[dev], [&] {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(kC * 64);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kC;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, ttt_fwd_cluster_kernel<kC>, &cfg) != cudaSuccess) {
+      cudaGetLastError();
+      n = 0;
+    }
+    cap[dev] = n;
+  });
+  return cap[dev];
+}
+
+template <int kC>
+int launch_cluster(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const CUtensorMap& tmOut,
+                   const FwdClParams& p, int streams, cudaStream_t stream) {
+  using C = Cfg<kC>;
+  if (int rc = prepare_kernel<kC>()) return rc;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(streams) * kC);
   cfg.blockDim = dim3(kThreads);
@@ -735,4 +774,8 @@ int ttt_launch_forward_cluster(const ttt_b200_fwd_args* a, int cluster, cudaStre
   if (cluster == 2) return launch_cluster<2>(tmQ, tmK, tmV, tmOut, p, streams, stream);
   if (cluster == 4) return launch_cluster<4>(tmQ, tmK, tmV, tmOut, p, streams, stream);
   return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "cluster size must be 2 or 4");
+}
+
+int ttt_forward_cluster_capacity(int cluster) {
+  return cluster == 2 ? cluster_capacity<2>() : cluster == 4 ? cluster_capacity<4>() : 0;
 }
