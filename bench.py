@@ -369,6 +369,20 @@ def run_ours(args, rank, world, local_rank):
     h2d_ms, _ = timed(copy_in)
     d2h_ms, _ = timed(copy_out)
 
+    # both directions at once (two streams): the floor of an end-to-end step, whose copies in and out overlap
+    side = torch.cuda.Stream(device=dev)
+
+    def copy_both():
+        main = torch.cuda.current_stream()
+        side.wait_stream(main)
+        copy_in()
+        with torch.cuda.stream(side):
+            copy_out()
+        main.wait_stream(side)
+
+    copy_both()
+    duplex_ms, _ = timed(copy_both)
+
     # ---- N replicas of the whole problem (weak scaling), as an extra number of the same run
     weak = None
     if strong and world > 1:
@@ -439,8 +453,12 @@ def run_ours(args, rank, world, local_rank):
                 "host_issue_ms_per_step": t_issue,
                 "h2d_gbs_alone_per_rank": h2d / (h2d_ms * 1e-3) / 1e9,
                 "d2h_gbs_alone_per_rank": d2h / (d2h_ms * 1e-3) / 1e9,
+                "copies_both_directions_ms": duplex_ms,
+                "frac_of_copy_floor": duplex_ms / e2e_ms,
                 "copy_note": "bytes are per rank; the *_alone figures time one direction with all ranks copying at once "
-                             "(slowest rank), i.e. what the host's PCIe / memory fabric gives each rank",
+                             "(slowest rank), i.e. what the host's PCIe / memory fabric gives each rank; "
+                             "copies_both_directions_ms times one step's copies in and out running at the same time with "
+                             "no kernel at all: the floor of an end-to-end step (frac_of_copy_floor = that / ms_per_step)",
                 "pipelining": f"{len(chunks)} (batch element, head range) chunks, each with a stream for copies in + "
                               "kernels and one for copies out, not joined between steps: copies in, kernels and copies out "
                               "of neighbouring steps overlap"},

@@ -20,11 +20,20 @@
 //   mini-batch.  dQ and dK are outputs only: they are summed by reduce-scatter (every CTA finishes and
 //   stores the token rows it owns), which sends kC times fewer bytes than an all-reduce.
 //
-//   replicated: everything 64 x 64 (LayerNorm stages, second-order terms), b2, dL/db2, d_gamma,
-//   d_beta; every CTA computes them from the same summed tiles, bit for bit.  The token-tile scratch
-//   (x_hat_fused, dl/dZ2, x_hat_ln, 1/std) is written by every CTA with the same bytes, so that a CTA
-//   only ever reads back what it has written itself.  The CTAs take turns storing dV; rank 0 stores d_eta and the
-//   per-stream vectors.
+//   the 64 x 64 token stages (LayerNorm stages, second-order terms), in one of two forms:
+//
+//   kC = 2, replicated: every CTA computes them from the same summed tiles, bit for bit, together with b2,
+//   dL/db2, d_gamma, d_beta.  The token-tile scratch (x_hat_fused, dl/dZ2, x_hat_ln, 1/std) is written by
+//   every CTA with the same bytes, so that a CTA only ever reads back what it has written itself.  The CTAs
+//   take turns storing dV; rank 0 stores d_eta and the per-stream vectors.
+//
+//   kC = 4, split by rows (RowSplit in ttt_cluster.cuh): every sum is a reduce-scatter to the CTA that owns
+//   the 16 token rows, which runs the stage on them (warp = row pair, lane = column pair) and hands the bf16
+//   rows that feed MMAs (dl/dZ2, U2, x_hat_ln, gZ2in) to every peer's operand tile.  x_hat_fused and the
+//   1/std vectors are needed by the row's owner only: a CTA writes and reads back its own rows of those
+//   scratch tiles.  dQ, dK, dV, d_eta are stored by the owner of the row.  b2 and dL/db2 stay replicated
+//   (column sums of gathered tiles); the d_gamma / d_beta addends of the second-order stage are summed per
+//   CTA over its own rows and added up by rank 0, in rank order, at the end.
 //
 // Every wait is bounded; a wait that runs out raises the abort flag of the whole cluster, the vote on
 // leaving a loop is taken CTA-wide at a barrier, and no CTA exits before its peers have reached the
