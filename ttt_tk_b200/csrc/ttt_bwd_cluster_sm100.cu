@@ -1068,15 +1068,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         *reinterpret_cast<float2*>(sPart + warp * 64 + 2 * lane) = make_float2(a0 + c0, a1 + c1);
       }
       if constexpr (C::kRowSplit) {
-        float2 go[NR];
-#pragma unroll
-        for (int i = 0; i < NR; ++i) go[i] = RSx::ld_pair(t_go, rs.row(i, warp), lane);
-        float z[NR][2];
-        rs.recv(z, warp, lane, dq_tag);
-#pragma unroll
-        for (int i = 0; i < NR; ++i)
-          RSx::st_pair_global(p.dXQ + static_cast<long>(row0) * 64, rs.row(i, warp), lane, go[i].x + z[i][0],
-                              go[i].y + z[i][1]);
+        // finished inside E4's wait for its own sum
       } else if (csum.reduce_scatter_recv(dq, tid, dq_tag)) {
         float go[16];
         tok_ld_tile(tm, t_go, go);
@@ -1189,6 +1181,17 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           kr[i] = RSx::ld_pair(t_k, r, lane);
           etar[i] = __bfloat162float(sEta[r]);
           rsd[i] = sSigF[r];       // 1 / std
+        }
+        {   // while the A2 sum is under way: dQ = dL/dOut + the sum sent in E2, on the rows this CTA owns
+          float2 go[NR];
+#pragma unroll
+          for (int i = 0; i < NR; ++i) go[i] = RSx::ld_pair(t_go, rs.row(i, warp), lane);
+          float zq[NR][2];
+          rs.recv(zq, warp, lane, dq_tag);
+#pragma unroll
+          for (int i = 0; i < NR; ++i)
+            RSx::st_pair_global(p.dXQ + static_cast<long>(row0) * 64, rs.row(i, warp), lane, go[i].x + zq[i][0],
+                                go[i].y + zq[i][1]);
         }
         float z[NR][2], ex[NR];
         rs.recv_x(z, ex, warp, lane, a2_tag);
