@@ -82,3 +82,34 @@ def test_cluster_forward_long_sequence_heads_only():
     assert orc.rel_l2(res["Out"], ref["Out"]) <= TOL
     for k in ("W1_checkpoints", "W2_checkpoints", "W1_final", "W2_final"):
         assert orc.rel_l2(res[k], ref[k]) <= TOL, k
+
+
+def test_launcher_choice_follows_the_cluster_capacity():
+    """The launcher gives a stream four CTAs only while the device runs that many clusters of four at
+    the same time (the occupancy query, not SMs / 4), the forward two while those fit, else one; the
+    backward never picks two."""
+    from ttt_tk_b200 import _lib
+    lib = _lib.lib()
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    for backward in (0, 1):
+        c2, c4 = lib.ttt_b200_cluster_capacity(2, backward), lib.ttt_b200_cluster_capacity(4, backward)
+        assert 0 < c4 <= sms // 4 and 0 < c2 <= sms // 2 and c4 <= c2
+        assert lib.ttt_b200_cluster_capacity(3, backward) == 0
+        assert lib.ttt_b200_pick_cluster(1, backward) == 4
+        assert lib.ttt_b200_pick_cluster(c4, backward) == 4
+        assert lib.ttt_b200_pick_cluster(c4 + 1, backward) == (1 if backward else 2)
+        assert lib.ttt_b200_pick_cluster(c2, backward) == (1 if backward else 2)
+        assert lib.ttt_b200_pick_cluster(c2 + 1, backward) == 1
+        assert lib.ttt_b200_pick_cluster(0, backward) == -1
+
+
+def test_a_problem_at_the_capacity_of_four_cta_clusters_runs_in_one_wave():
+    """B*H equal to the capacity for clusters of four: the launcher picks four CTAs per stream and the
+    result matches the oracle (every cluster is resident, none waits for a peer that is not running)."""
+    from ttt_tk_b200 import _lib
+    cap = _lib.lib().ttt_b200_cluster_capacity(4, 0)
+    d = orc.make_inputs(1, cap, 2, seed=5)
+    ref = orc.ttt_forward(d["XQ"], d["XK"], d["XV"], d["last_eta"], d["ttt_norm_weight"], d["ttt_norm_bias"],
+                          d["W1"], d["b1"], d["W2"], d["b2"], 2)
+    res = run_forward(d, 2, None)
+    assert orc.rel_l2(res["Out"], ref["Out"]) <= TOL

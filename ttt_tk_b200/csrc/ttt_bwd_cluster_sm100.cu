@@ -71,7 +71,8 @@ struct Cfg {
   static constexpr uint32_t HB = NB * TILE;            // bytes of an [R][64] bf16 tile
   using Sum = ClusterSum<kC, 18432>;                   // a 64 x 64 tile, optionally with two extra values per thread
   // Four CTAs: the token stages are split by rows as well (every CTA runs them on the 16 token rows it owns
-  // and hands the bf16 results to its peers); measured slower than the all-reduce form at two CTAs.
+  // and hands the bf16 results to its peers).  At two CTAs the row-split form works too (set this to true) but
+  // was measured slower than the all-reduce form: 22.9 against 21.2 us per mini-batch at 32 streams.
   static constexpr bool kRowSplit = kC == 4;
   using RS = RowSplit<kC, true>;
   static constexpr uint32_t OFF_BIG = 0;               // 5 hidden-major buffers
@@ -87,17 +88,18 @@ struct Cfg {
   static constexpr uint32_t OFF_SIGF = OFF_SIGLN + 256;
   static constexpr uint32_t OFF_GB1 = OFF_SIGF + 256;       // fp32[R] copy of the per-thread dL/db1
   static constexpr uint32_t OFF_PART = OFF_GB1 + 1024;      // fp32[8][64] partial sums for d_eta (one row per warp)
-  static constexpr uint32_t OFF_CSUM = OFF_PART + 2048;     // fp32[3][4][64] column-sum partials; row-split form: [4][64] + 2 x [8][64]
-  static constexpr uint32_t OFF_ETA = OFF_CSUM + 5120;      // bf16[2][64]
+  // fp32[3][4][64] column-sum partials (the row-split form keeps the second-order stage's own-row partials,
+  // 2 x [8][64], in the row-sum exchange area, which is not in use between that stage and their sum)
+  static constexpr uint32_t OFF_CSUM = OFF_PART + 2048;
+  static constexpr uint32_t OFF_ETA = OFF_CSUM + 3072;      // bf16[2][64]
   static constexpr uint32_t OFF_BAR = OFF_ETA + 256;
   static constexpr uint32_t OFF_MISC = OFF_BAR + 192;
   static constexpr uint32_t OFF_XCH = OFF_MISC + 64;        // fp32[2][64][8] row-sum exchange between warp pairs
   // row-split form only: 1/std of x_hat_ln gathered from the row owners; d_gamma / d_beta addends of this
-  // CTA's own rows ([2][64]); rank 0's landing area for the peers' addends at the end ([kC][2][64])
+  // CTA's own rows ([2][64])
   static constexpr uint32_t OFF_SIGAG = OFF_XCH + 4096;
   static constexpr uint32_t OFF_DGP = OFF_SIGAG + 256;
-  static constexpr uint32_t OFF_FIN = OFF_DGP + 512;
-  static constexpr uint32_t SMEM_USED = OFF_FIN + kC * 512;
+  static constexpr uint32_t SMEM_USED = OFF_DGP + 512;
   static constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;
   static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB per-CTA shared memory of sm_100");
   static_assert(NUM_BARS * 8 <= 192, "barrier area");
@@ -173,7 +175,6 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   float* sXch = reinterpret_cast<float*>(smem + C::OFF_XCH);
   float* sSigAG = reinterpret_cast<float*>(smem + C::OFF_SIGAG);
   float* sDGp = reinterpret_cast<float*>(smem + C::OFF_DGP);       // [0..63] d_gamma, [64..127] d_beta addends of the own rows
-  float* sFin = reinterpret_cast<float*>(smem + C::OFF_FIN);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + C::OFF_MISC + 4);
   volatile uint32_t* never_flag = reinterpret_cast<volatile uint32_t*>(smem + C::OFF_MISC + 8);   // stays 0
@@ -1228,8 +1229,8 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                               fmaf(gx1, rstd, (sa0 * xh[i].y - sa1 * rstd) * (1.f / 64.f)));
           if (lane == 0) p.d_eta[(sid * NC + i0 + j) * 64 + r] = __float2bfloat16(-de);
         }
-        *reinterpret_cast<float2*>(part + 256 + warp * 64 + 2 * lane) = make_float2(ca0, ca1);
-        *reinterpret_cast<float2*>(part + 768 + warp * 64 + 2 * lane) = make_float2(cv0, cv1);
+        *reinterpret_cast<float2*>(sXch + warp * 64 + 2 * lane) = make_float2(ca0, ca1);
+        *reinterpret_cast<float2*>(sXch + 512 + warp * 64 + 2 * lane) = make_float2(cv0, cv1);
         wait_bar(BAR_AG);
       } else {
         float A2[16], gz[16], xh[16], go[16];
@@ -1368,16 +1369,21 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                  HID_ONE(false, C::TM_A, big(ib1), t_gz2, 0u, 0),
                  if (NB > 1) HID_ONE(false, C::TM_A, big(ib1), t_gz2, 0u, NB - 1))
       if constexpr (C::kRowSplit) {
+        // the second-order stage's d_gamma / d_beta partials (this CTA's rows only: summed over the cluster at
+        // the end) are read out of the row-sum exchange area before the barrier below; the next epilogue, which
+        // uses that area again, comes after it
+        float a = 0.f, v = 0.f;
+        if (tid < 64) {
+#pragma unroll
+          for (int w = 0; w < 8; ++w) {
+            a += sXch[w * 64 + tid];
+            v += sXch[512 + w * 64 + tid];
+          }
+        }
         part[tid] = colsum16(t_q);      // the gathered gZ2in tile: G_b2 stays replicated
         __syncthreads();
         if (tid < 64) {
           sGb2[tid] += part_sum(0);
-          float a = 0.f, v = 0.f;       // this CTA's rows only: summed over the cluster at the end
-#pragma unroll
-          for (int w = 0; w < 8; ++w) {
-            a += part[256 + w * 64 + tid];
-            v += part[768 + w * 64 + tid];
-          }
           sDGp[tid] += a;
           sDGp[64 + tid] += v;
         }
@@ -1504,7 +1510,9 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     }
     if constexpr (C::kRowSplit) {
       // d_gamma / d_beta: the replicated addends (output LayerNorm) plus every CTA's own-row addends, summed by
-      // rank 0 in rank order
+      // rank 0 in rank order.  The peers' addends ([kC][2][64]) land in the exchange buffer after next: the last
+      // sum that used it was received by every CTA before the last-but-one was sent.
+      float* sFin = reinterpret_cast<float*>(rs.bufp + ((rs.n + 1u) & 3u) * C::RS::kBufBytes);
       if (rank == 0) {
         if (tid == 0) mbar_expect_tx(&bars[BAR_AG], (kC - 1) * 512u);
       } else if (tid < 32) {

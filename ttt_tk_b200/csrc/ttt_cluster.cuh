@@ -375,24 +375,29 @@ struct ClusterSum {
 // Row layout of the stage: warp w works on row pair w of each of the CTA's QPC quadrants, lane l on the
 // column pair l: NR = 2 QPC rows x 2 columns per thread; a row lives in one warp, so row sums are five
 // xor-shuffles.
-// kExtras: a slot also has room for two extra per-row values from each of the 8 fragment threads that share
-// a row pair ([quadrant][row pair][colhalf x 4 + lane % 4] float2 after the tile), which send_x / recv_x sum
-// over the contributors as well: per-row scalars that are linear in the partial tiles travel with them.
+// kExtras: a second, smaller exchange area (two alternating buffers of one slot per CTA) takes two extra per-row
+// values from each of the 8 fragment threads that share a row pair ([quadrant][row pair][colhalf x 4 + lane % 4]
+// float2), which send_x / recv_x sum over the contributors as well: per-row scalars that are linear in the
+// partial tiles travel with them, counted on the same mbarrier.  Two buffers are enough when sums with extras
+// are separated by other sums, as they are here (one per reverse step).
 template <int kC, bool kExtras = false>
 struct RowSplit {
   static constexpr int QPC = 4 / kC;                          // fragment quadrants per CTA
   static constexpr int ROWS = 16 * QPC;
   static constexpr int NR = 2 * QPC;                          // rows per thread in the row layout
   static constexpr uint32_t kTileBytes = QPC * 4096u;
-  static constexpr uint32_t kSlotBytes = kTileBytes + (kExtras ? QPC * 512u : 0u);
+  static constexpr uint32_t kSlotBytes = kTileBytes;
   static constexpr uint32_t kBufBytes = kC * kSlotBytes;      // 16 KB
   static constexpr int kBufs = 4;
-  static constexpr uint32_t kBytes = kBufs * kBufBytes;
+  static constexpr uint32_t kXSlotBytes = QPC * 512u;
+  static constexpr uint32_t kXBufBytes = kC * kXSlotBytes;
+  static constexpr uint32_t kBytes = kBufs * kBufBytes + (kExtras ? 2 * kXBufBytes : 0u);   // tiles, then extras
   static constexpr uint32_t kBarCount = 1 + 2 * QPC;          // arming thread + the warps of the own quadrants
 
   uint8_t* bufp;
   uint64_t* bars;        // [kBufs]
   uint32_t n;
+  uint32_t nx = 0;       // sums with extras so far
   uint32_t rank;
   volatile uint32_t* abort_flag;
   uint64_t limit;
@@ -406,14 +411,16 @@ struct RowSplit {
     static_assert(!kX || kExtras, "this exchange area has no room for extra values");
     const uint32_t b = n & 3u, par = (n >> 2) & 1u;
     ++n;
+    const uint32_t xb = nx & 1u;
+    if constexpr (kX) ++nx;
     const uint32_t owner = owner_of(warp);
     const uint32_t lq = static_cast<uint32_t>(warp & 3) % QPC, colhalf = static_cast<uint32_t>(warp >> 2);
     const uint32_t slot = b * kBufBytes + rank * kSlotBytes;
     const uint32_t off = slot + lq * 4096u + static_cast<uint32_t>(lane >> 2) * 512u +
                          (colhalf * 16u + static_cast<uint32_t>(lane & 3)) * 16u;
-    const uint32_t xoff = slot + kTileBytes + lq * 512u + static_cast<uint32_t>(lane >> 2) * 64u +
-                          (colhalf * 4u + static_cast<uint32_t>(lane & 3)) * 8u;
-    if (tid == 0) mbar_expect_tx(&bars[b], (kC - 1) * (kX ? kSlotBytes : kTileBytes));
+    const uint32_t xoff = kBufs * kBufBytes + xb * kXBufBytes + rank * kXSlotBytes + lq * 512u +
+                          static_cast<uint32_t>(lane >> 2) * 64u + (colhalf * 4u + static_cast<uint32_t>(lane & 3)) * 8u;
+    if (tid == 0) mbar_expect_tx(&bars[b], (kC - 1) * (kTileBytes + (kX ? kXSlotBytes : 0u)));
     if (owner != rank) {
       const uint32_t dst = mapa(smem_u32(bufp) + off, owner);
       const uint32_t rbar = mapa(smem_u32(&bars[b]), owner);
@@ -429,7 +436,7 @@ struct RowSplit {
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars[b]);
     }
-    return b | (par << 2);
+    return b | (par << 2) | (xb << 3);
   }
   __device__ __forceinline__ uint32_t send(const float (&v)[16], int tid, int warp, int lane) {
     return send_impl<false>(v, 0.f, 0.f, tid, warp, lane);
@@ -445,7 +452,7 @@ struct RowSplit {
   }
   // Wait for the partial tiles and return their sums (rank order): z[i][0..1] = row i, columns 2 lane, 2 lane + 1.
   __device__ __forceinline__ void recv(float (&z)[NR][2], int warp, int lane, uint32_t tag) {
-    const uint32_t b = tag & 3u, par = tag >> 2;
+    const uint32_t b = tag & 3u, par = (tag >> 2) & 1u;
     mbar_wait_cl(&bars[b], par, abort_flag, limit, kC);
     const uint8_t* base = bufp + b * kBufBytes + static_cast<uint32_t>(warp) * 512u + static_cast<uint32_t>(lane) * 16u;
 #pragma unroll
@@ -463,15 +470,15 @@ struct RowSplit {
   // recv() plus the extra values: e[i] = the sum over all CTAs and contributors for row i (all lanes get it)
   __device__ __forceinline__ void recv_x(float (&z)[NR][2], float (&e)[NR], int warp, int lane, uint32_t tag) {
     recv(z, warp, lane, tag);
-    const uint32_t b = tag & 3u;
-    const uint8_t* base = bufp + b * kBufBytes + kTileBytes + static_cast<uint32_t>(warp) * 64u +
+    const uint32_t xb = (tag >> 3) & 1u;
+    const uint8_t* base = bufp + kBufs * kBufBytes + xb * kXBufBytes + static_cast<uint32_t>(warp) * 64u +
                           static_cast<uint32_t>(lane & 7) * 8u;
 #pragma unroll
     for (int lq = 0; lq < QPC; ++lq) {
       float2 acc = *reinterpret_cast<const float2*>(base + lq * 512u);
 #pragma unroll
       for (int s = 1; s < kC; ++s) {
-        const float2 f = *reinterpret_cast<const float2*>(base + s * kSlotBytes + lq * 512u);
+        const float2 f = *reinterpret_cast<const float2*>(base + s * kXSlotBytes + lq * 512u);
         acc.x += f.x; acc.y += f.y;
       }
 #pragma unroll
