@@ -82,6 +82,30 @@ typedef struct ttt_b200_fwd_args {
   float* b2_final;
 } ttt_b200_fwd_args;
 
+/* Arguments of the TTT-Linear forward: the same operator with the inner model reduced to one linear layer,
+ * f(x) = x W1 + b1 with W1 [64 x 64] (the hidden layer, W2 and b2 dropped; everything else, the checkpoint
+ * rule included, as in ttt_b200_fwd_args).  The reference has no counterpart: it ships the TTT-MLP operator
+ * only (README.md:18).  Forward only. */
+typedef struct ttt_b200_linear_fwd_args {
+  const void* XQ;                /* bf16 [B,H,NC,64,64] */
+  const void* XK;                /* bf16 [B,H,NC,64,64] */
+  const void* XV;                /* bf16 [B,H,NC,64,64] */
+  const void* last_eta;          /* bf16 [B,H,NC,64] */
+  const float* ttt_norm_weight;  /* [H,64] */
+  const float* ttt_norm_bias;    /* [H,64] */
+  const float* W1;               /* [B,H,64,64] (input feature x output feature) */
+  const float* b1;               /* [B,H,64] */
+  float* W1_checkpoints;         /* [B,H,n,64,64], n = ceil(NC / checkpoint_group_size) */
+  float* b1_checkpoints;         /* [B,H,n,64] */
+  void* Out;                     /* bf16 [B,H,NC,64,64] */
+  int32_t B, H, NC;
+  int32_t checkpoint_group_size;
+  int32_t num_checkpoints;       /* size(2) of the checkpoint tensors; must equal n */
+  uint32_t flags;                /* TTT_B200_FLAG_SYNC, TTT_B200_FLAG_TEST_LOST_LOAD; the cluster bits are ignored */
+  float* W1_final;               /* optional (both or neither): state after the last mini-batch */
+  float* b1_final;
+} ttt_b200_linear_fwd_args;
+
 /* Arguments of the backward.  Replaces ttt_backward(...43 positional arguments...)
  * -- kernels/ttt_backward/ttt.cu:1451-1495; same order.  The sixteen `*_group` tensors are
  * caller-provided scratch of the reference's shapes; this implementation uses a subset of
@@ -206,6 +230,10 @@ int ttt_b200_backward_noalloc(const ttt_b200_bwd_noalloc_args* args, void* strea
 
 /* Last error text of the calling thread ("" if none). */
 const char* ttt_b200_last_error(void);
+
+/* TTT-Linear forward (see ttt_b200_linear_fwd_args): one CTA per (batch, head) stream, stream-ordered,
+ * same status codes and status-word protocol as ttt_b200_forward. */
+int ttt_b200_linear_forward(const ttt_b200_linear_fwd_args* args, void* cuda_stream);
 
 /* Take (read and clear) the device-side status word: 0, or TTT_B200_ERR_TIMEOUT if a kernel of
  * this process gave up on a bounded wait since the last take.  Call after synchronising. */

@@ -30,6 +30,16 @@ class FwdArgs(ctypes.Structure):
     _fields_ = [(n, c_void_p) for n in FWD_FIELDS] + _DIMS + [(n, c_void_p) for n in FWD_TAIL]
 
 
+# ttt_b200_linear_forward: the forward's tensors without W2 / b2 and their checkpoints
+LINEAR_FWD_FIELDS = ["XQ", "XK", "XV", "last_eta", "ttt_norm_weight", "ttt_norm_bias", "W1", "b1",
+                     "W1_checkpoints", "b1_checkpoints", "Out"]
+LINEAR_FWD_TAIL = ["W1_final", "b1_final"]
+
+
+class LinearFwdArgs(ctypes.Structure):
+    _fields_ = [(n, c_void_p) for n in LINEAR_FWD_FIELDS] + _DIMS + [(n, c_void_p) for n in LINEAR_FWD_TAIL]
+
+
 class BwdArgs(ctypes.Structure):
     _fields_ = [(n, c_void_p) for n in BWD_FIELDS] + _DIMS
 
@@ -43,7 +53,7 @@ class BwdNoAllocArgs(ctypes.Structure):
     _fields_ = [(n, c_void_p) for n in BWD_NOALLOC_FIELDS] + _DIMS
 
 
-EXPORTS = ["ttt_b200_forward", "ttt_b200_backward", "ttt_b200_backward_noalloc", "ttt_b200_last_error", "ttt_b200_take_status",
+EXPORTS = ["ttt_b200_forward", "ttt_b200_linear_forward", "ttt_b200_backward", "ttt_b200_backward_noalloc", "ttt_b200_last_error", "ttt_b200_take_status",
            "ttt_b200_version", "ttt_b200_pick_cluster", "ttt_b200_cluster_capacity", "ttt_b200_umma_selftest", "ttt_b200_wait_selftest", "ttt_b200_pack_tokens",
            "ttt_b200_unpack_tokens", "ttt_b200_eta_gate", "ttt_b200_eta_gate_backward", "ttt_b200_unpack_layernorm",
            "ttt_b200_pack_layernorm_backward"]
@@ -60,6 +70,8 @@ def load():
     lib = ctypes.CDLL(LIB_PATH)
     lib.ttt_b200_forward.argtypes = [ctypes.POINTER(FwdArgs), c_void_p]
     lib.ttt_b200_forward.restype = ctypes.c_int
+    lib.ttt_b200_linear_forward.argtypes = [ctypes.POINTER(LinearFwdArgs), c_void_p]
+    lib.ttt_b200_linear_forward.restype = ctypes.c_int
     lib.ttt_b200_backward.argtypes = [ctypes.POINTER(BwdArgs), c_void_p]
     lib.ttt_b200_backward.restype = ctypes.c_int
     lib.ttt_b200_backward_noalloc.argtypes = [ctypes.POINTER(BwdNoAllocArgs), c_void_p]

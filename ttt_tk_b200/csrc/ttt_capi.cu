@@ -21,6 +21,8 @@ int ttt_launch_backward(const ttt_b200_bwd_args* a, cudaStream_t stream, uint32_
                         int drop_load);
 int ttt_launch_backward_cluster(const ttt_b200_bwd_args* a, int cluster, cudaStream_t stream, uint32_t* status,
                                 uint64_t limit_ns, int drop_load);
+int ttt_launch_linear_forward(const ttt_b200_linear_fwd_args* a, cudaStream_t stream, uint32_t* status,
+                              uint64_t limit_ns, int drop_load);
 int ttt_forward_cluster_capacity(int cluster);
 int ttt_backward_cluster_capacity(int cluster);
 int ttt_launch_forward_cluster(const ttt_b200_fwd_args* a, int cluster, cudaStream_t stream, uint32_t* status,
@@ -224,6 +226,27 @@ extern "C" int ttt_b200_forward(const ttt_b200_fwd_args* a, void* stream_) {
   if (int rc = cluster == 1 ? ttt_launch_forward(a, stream, status, wait_limit_ns(), drop)
                             : ttt_launch_forward_cluster(a, cluster, stream, status, wait_limit_ns(), drop))
     return rc;
+  if (a->flags & TTT_B200_FLAG_SYNC) return ttt_check_status(stream);
+  return TTT_B200_OK;
+}
+
+extern "C" int ttt_b200_linear_forward(const ttt_b200_linear_fwd_args* a, void* stream_) {
+  TTT_REQUIRE(a != nullptr, "args is NULL");
+  if (int rc = check_dims(a->B, a->H, a->NC, a->checkpoint_group_size, a->num_checkpoints)) return rc;
+  const void* ptrs[] = {a->XQ, a->XK, a->XV, a->last_eta, a->ttt_norm_weight, a->ttt_norm_bias, a->W1, a->b1,
+                        a->W1_checkpoints, a->b1_checkpoints, a->Out};
+  for (const void* q : ptrs) {
+    TTT_REQUIRE(q != nullptr, "a required tensor pointer is NULL");
+    TTT_REQUIRE(aligned16(q), "tensor pointers must be 16-byte aligned");
+  }
+  TTT_REQUIRE((a->W1_final != nullptr) == (a->b1_final != nullptr), "W1_final and b1_final must be given together or not at all");
+  if (a->W1_final != nullptr)
+    TTT_REQUIRE(aligned16(a->W1_final) && aligned16(a->b1_final), "tensor pointers must be 16-byte aligned");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  uint32_t* status = nullptr;
+  if (int rc = pre_launch(&status)) return rc;
+  const int drop = (a->flags & TTT_B200_FLAG_TEST_LOST_LOAD) ? (a->NC > 1 ? 1 : 0) : -1;
+  if (int rc = ttt_launch_linear_forward(a, stream, status, wait_limit_ns(), drop)) return rc;
   if (a->flags & TTT_B200_FLAG_SYNC) return ttt_check_status(stream);
   return TTT_B200_OK;
 }

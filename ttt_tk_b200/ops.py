@@ -129,6 +129,47 @@ def ttt_forward(XQ, XK, XV, last_eta, ttt_norm_weight, ttt_norm_bias, W1, b1, W2
     return Out
 
 
+def ttt_linear_forward(XQ, XK, XV, last_eta, ttt_norm_weight, ttt_norm_bias, W1, b1,
+                       W1_checkpoints, b1_checkpoints, Out, checkpoint_group_size, *,
+                       final_state=None, sync=False, _lost_load=False):
+    """TTT-Linear forward over the whole sequence: `ttt_forward` with the inner model reduced to one linear
+    layer (W1 [B,H,64,64], b1 [B,H,1,64]; no W2 / b2); writes `Out` and the state checkpoints.  The reference
+    has no counterpart (it ships the MLP operator only).  `final_state` = (W1, b1) fp32 tensors that receive
+    the state after the last mini-batch."""
+    lib = _lib.lib()
+    B, H, NC, cgs, n = _dims(XQ, checkpoint_group_size, W1_checkpoints)
+    dev = XQ.device
+    bf, f32 = torch.bfloat16, torch.float32
+    tok = (B, H, NC, CS, F)
+    _chk_tensor(XQ, "XQ", bf, tok, dev)
+    _chk_tensor(XK, "XK", bf, tok, dev)
+    _chk_tensor(XV, "XV", bf, tok, dev)
+    _chk_eta(last_eta, "last_eta", B, H, NC, dev)
+    _chk_tensor(ttt_norm_weight, "ttt_norm_weight", f32, (1, H, 1, F), dev)
+    _chk_tensor(ttt_norm_bias, "ttt_norm_bias", f32, (1, H, 1, F), dev)
+    _chk_tensor(W1, "W1", f32, (B, H, F, F), dev)
+    _chk_tensor(b1, "b1", f32, (B, H, 1, F), dev)
+    _chk_tensor(W1_checkpoints, "W1_checkpoints", f32, (B, H, n, F, F), dev)
+    _chk_tensor(b1_checkpoints, "b1_checkpoints", f32, (B, H, n, 1, F), dev)
+    _chk_tensor(Out, "Out", bf, tok, dev)
+    a = _lib.LinearFwdArgs()
+    vals = [XQ, XK, XV, last_eta, ttt_norm_weight, ttt_norm_bias, W1, b1, W1_checkpoints, b1_checkpoints, Out]
+    for name, t in zip(_lib.LINEAR_FWD_FIELDS, vals):
+        setattr(a, name, t.data_ptr())
+    if final_state is not None:
+        _check(len(final_state) == 2, "final_state must be (W1, b1)")
+        for name, t, shp in zip(_lib.LINEAR_FWD_TAIL, final_state, [(B, H, F, F), (B, H, 1, F)]):
+            _chk_tensor(t, name, f32, shp, dev)
+            setattr(a, name, t.data_ptr())
+    a.B, a.H, a.NC, a.checkpoint_group_size, a.num_checkpoints = B, H, NC, cgs, n
+    a.flags = _flags(sync, None, _lost_load)
+    with torch.cuda.device(dev):
+        rc = lib.ttt_b200_linear_forward(ctypes.byref(a), _stream_ptr(dev))
+    if rc != 0:
+        _raise(lib, rc, "ttt_linear_forward")
+    return Out
+
+
 def ttt_backward(XQ, XK, XV, last_eta, ttt_norm_weight, ttt_norm_bias,
                  W1_checkpoints, b1_checkpoints, W2_checkpoints, b2_checkpoints, Out,
                  W1_init_group, b1_init_group, W2_init_group, b2_init_group,
