@@ -47,6 +47,8 @@ WORKLOADS = {
     "c2half": (2, 32, 128, 8, "half of configs[2] (what each of two GPUs gets): B=2 H=32 seq=8192 (NC=128) cgs=8"),
     "profc2": (2, 32, 16, 8, "profiling case with 64 streams (B=2 H=32) at seq=1024 (NC=16) cgs=8"),
     "glue": (4, 32, 128, 8, "layer-side kernels at the configs[2] shape: B=4 T=8192 H=32"),
+    "linear": (64, 24, 64, 16, "TTT-Linear forward at the configs[4] shape: B=64 H=24 seq=4096 (NC=64) cgs=16"),
+    "linear_c2": (4, 32, 128, 8, "TTT-Linear forward at the configs[2] shape: B=4 H=32 seq=8192 (NC=128) cgs=8"),
 }
 U_FLOP = 2 * 64 * 64 * 256            # one GEMM unit per mini-batch per (b,h)
 FWD_U, BWD_U = 7, 22                  # algorithmic GEMM units: forward; backward (7 recompute + 15 sweep)
@@ -593,6 +595,61 @@ def run_glue(args):
     }
 
 
+def run_linear(args):
+    """The TTT-Linear forward (the operator with a one-layer inner model): 3 x 2*64^3 FLOP against 514 bytes per
+    token-head, 48 FLOP per byte, far below the ridge: HBM is the roofline.  achieved = algorithmic bytes
+    (Q, K, V, eta in, Out out, initial state, checkpoints) / device time, against the measured copy bandwidth."""
+    from ttt_tk_b200 import ttt_linear_forward, take_status
+    B, H, NC, cgs, desc = WORKLOADS[args.workload]
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device=dev).manual_seed(0)
+    rn = lambda *s: torch.randn(*s, device=dev, generator=g)
+    n = -(-NC // cgs)
+    XQ, XK, XV = (rn(B, H, NC, 64, 64).bfloat16() for _ in range(3))
+    eta = (0.1 * torch.sigmoid(rn(B, H, NC, 64)) / 64).bfloat16()
+    gamma, beta = 1 + 0.02 * rn(1, H, 1, 64), 0.02 * rn(1, H, 1, 64)
+    W1, b1 = 0.02 * rn(B, H, 64, 64), 0.02 * rn(B, H, 1, 64)
+    ck = [torch.empty(B, H, n, 64, 64, device=dev), torch.empty(B, H, n, 1, 64, device=dev)]
+    out = torch.empty_like(XQ)
+    fn = lambda: ttt_linear_forward(XQ, XK, XV, eta, gamma, beta, W1, b1, *ck, out, cgs)
+    K, W = args.steps, max(args.warmup, 3)
+    sampler = ClockSampler(0)
+    sampler.start()
+    for _ in range(W):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    if take_status() != 0:
+        raise RuntimeError("a device-side wait ran out")
+    ms = e0.elapsed_time(e1) / K
+    state = (64 * 64 + 64) * 4
+    nbytes = B * H * (NC * 64 * 514 + state + 512 + n * state)
+    flops = B * H * NC * 3 * 2 * 64 ** 3
+    pk, pk_src = peaks()
+    gbs = nbytes / ms / 1e6
+    return {
+        "metric": "ttt_linear_fwd_tokens_per_s", "value": B * NC * 64 / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": K, "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": desc, "B": B, "H": H, "seq_len": NC * 64, "checkpoint_group_size": cgs,
+                   "l2": "inputs + outputs per step exceed the 126 MB L2; no explicit flush"},
+        "kernels": {"fwd_ms": ms, "fwd_tflops": flops / (ms * 1e-3) / 1e12,
+                    # three CTAs (streams) share an SM: 444 run at once on 148 SMs
+                    "waves": -(-(B * H) // 444), "us_per_mini_batch_per_wave": ms * 1e3 / (NC * -(-(B * H) // 444))},
+        "roofline": {"kernel": "ttt_linear_fwd_kernel", "bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"],
+                     "unit": "GB/s", "frac": gbs / pk["hbm_gbs"], "traffic": None,
+                     "peak_source": f"{pk_src} copy bandwidth"},
+        "gpu_launches": K, "clocks": clocks,
+    }
+
+
 def _emit(res, out_fd):
     os.write(out_fd, (json.dumps(res) + "\n").encode())
 
@@ -635,6 +692,10 @@ def main():
     if args.workload == "glue":
         if rank == 0:
             _emit(run_glue(args), out_fd)
+        return
+    if args.workload.startswith("linear"):
+        if rank == 0:
+            _emit(run_linear(args), out_fd)
         return
 
     if world > 1:

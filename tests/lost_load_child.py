@@ -58,6 +58,32 @@ def main():
                     e = orc.rel_l2(res[k].float().cpu(), g[k])
                     assert e <= 3e-2, (name, cluster, k, e)
             print(f"{name} cluster {cluster}: lost load reported, next launch correct", flush=True)
+    # the TTT-Linear forward has the same hook
+    from oracle import ttt_linear as lin
+    from ttt_tk_b200 import ttt_linear_forward
+    dl = lin.make_inputs(B, H, NC, seed=1)
+    tl = {k: v.to(dev) for k, v in dl.items()}
+    fl = lin.ttt_linear_forward(dl["XQ"], dl["XK"], dl["XV"], dl["last_eta"], dl["ttt_norm_weight"],
+                                dl["ttt_norm_bias"], dl["W1"], dl["b1"], cgs)
+
+    def linear(lost):
+        n = lin.num_checkpoints(NC, cgs)
+        ck = [torch.zeros(B, H, n, 64, 64, device=dev), torch.zeros(B, H, n, 1, 64, device=dev)]
+        out = torch.zeros_like(tl["XQ"])
+        ttt_linear_forward(tl["XQ"], tl["XK"], tl["XV"], tl["last_eta"], tl["ttt_norm_weight"], tl["ttt_norm_bias"],
+                           tl["W1"], tl["b1"], *ck, out, cgs, sync=True, _lost_load=lost)
+        return out
+
+    try:
+        linear(True)
+    except RuntimeError as e:
+        assert "code 3" in str(e) and "bounded wait" in str(e), str(e)
+    else:
+        raise AssertionError("linear forward: the lost load went unnoticed")
+    assert take_status() == 0
+    e = lin.rel_l2(linear(False).float().cpu(), fl["Out"])
+    assert e <= 1e-2, ("linear forward", e)
+    print("linear forward: lost load reported, next launch correct", flush=True)
     print("LOST_LOAD_OK")
 
 

@@ -16,9 +16,10 @@
 //
 // Before mini-batch i with i % checkpoint_group_size == 0 the state (W, b) is stored as checkpoint
 // i / checkpoint_group_size.  One CTA of 256 threads per (batch, head) stream; every tile is 64 x 64, read
-// out of tensor memory as the 16x256b fragments of TokMap by all eight warps; two CTAs share an SM when
-// there are more streams than SMs (96 KB of shared memory, 128 tensor-memory columns each), which hides
-// the latency of the three dependent MMA phases.  All waits are bounded; on expiry the CTA reports through
+// out of tensor memory as the 16x256b fragments of TokMap by all eight warps; up to three CTAs share an SM
+// when there are more streams than SMs (72 KB of shared memory with a two-stage input ring, 128
+// tensor-memory columns, 80 registers per thread each), which hides the latency of the three dependent MMA
+// phases (measured at 1536 streams: 1.43 ms with two CTAs per SM and a three-stage ring, 1.34 ms with three).  All waits are bounded; on expiry the CTA reports through
 // the status word, drains its own copies, frees its tensor memory and returns.
 #include <mutex>
 
@@ -29,7 +30,7 @@ using namespace tttcl;
 
 namespace {
 
-constexpr int kStages = 3;
+constexpr int kStages = 2;
 constexpr int kThreads = 256;
 constexpr int kProd = 128;     // issues the bulk copies; not the MMA issuer (lane 0 of warp 0)
 
@@ -48,7 +49,7 @@ constexpr uint32_t OFF_MISC = OFF_BAR + 64;
 constexpr uint32_t OFF_XCH = OFF_MISC + 64;             // fp32[2][64][8] row-sum exchange between warp pairs
 constexpr uint32_t SMEM_USED = OFF_XCH + 4096;
 constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;       // slack for the 1024-byte alignment
-static_assert(2 * (SMEM_BYTES + 1024) <= 233472, "two CTAs per SM");
+static_assert(3 * (SMEM_BYTES + 1024) <= 233472, "three CTAs per SM");
 
 constexpr uint32_t TM_W = 0;
 constexpr uint32_t TM_Z = 64;
@@ -80,7 +81,7 @@ __device__ __forceinline__ void mma_mn_accumulate(uint32_t tmem_d, uint32_t a_sm
   for (int j = 0; j < 4; ++j) mma_issue_rt(tmem_d, a0 + j * (2048u >> 4), b0 + j * (2048u >> 4), idesc, 1u);
 }
 
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 3)
 ttt_linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const LinParams p) {
   extern __shared__ uint8_t smem_raw[];
