@@ -555,8 +555,8 @@ def run_glue(args):
              ("eta_gate", lambda: glue.eta_gate(logits, 0.1 / 64), 2 * logits.numel() * 2),
              ("eta_gate_backward", lambda: glue.eta_gate_backward(logits, d_eta, 0.1 / 64), 3 * logits.numel() * 2),
              ("unpack_layernorm", lambda: glue.unpack_layernorm(ys[0], gamma, beta, 1e-6), 2 * tok + 2 * H * 64 * 4),
-             # backward: kernel 1 reads x and dy and writes dx; kernel 2 reads x and dy again for the parameter gradients
-             ("pack_layernorm_backward", lambda: glue.pack_layernorm_backward(xs[1], ys[0], gamma, stats), 5 * tok)]
+             # backward: one pass reads x and dy, writes dx and accumulates the parameter gradients
+             ("pack_layernorm_backward", lambda: glue.pack_layernorm_backward(xs[1], ys[0], gamma, stats), 3 * tok)]
     K, W = args.steps, max(args.warmup, 3)
     sampler = ClockSampler(0)
     out = {}

@@ -139,10 +139,21 @@ __global__ void __launch_bounds__(256, (kChunks <= 8 ? 4 : 2)) unpack_layernorm_
 // result is the operator's grad_L_XQW_mini_batch.  With xhat = (x - mean) rstd and g = dy gamma:
 //   dx = rstd (g - mean(g) - xhat mean(g xhat)).
 // Same work split as the forward: one warp per token, the token's x and dy in registers (packed bf16).
+// The parameter gradients d_gamma[f] += sum over tokens of dy xhat, d_beta[f] += sum of dy come out of the same
+// pass: every lane adds its 8 features per head row into the CTA's accumulators in shared memory
+// ([gamma | beta][k][head][piece]: the 32 lanes of a warp hit 32 consecutive words), and the CTA adds them to
+// the global sums with fp32 atomics when it has run out of tokens (the order of the CTAs is not fixed: the last
+// bits of the result can differ from run to run).  x and dy are read once.
 template <int kChunks>
 __global__ void __launch_bounds__(256, (kChunks <= 4 ? 4 : 2))
 pack_layernorm_backward_kernel(const uint4* __restrict__ dy, const uint4* __restrict__ x, const float* __restrict__ gamma,
-                               const float2* __restrict__ stats, uint4* __restrict__ dx, long tokens, int T, int H) {
+                               const float2* __restrict__ stats, uint4* __restrict__ dx, float* __restrict__ d_gamma,
+                               float* __restrict__ d_beta, long tokens, int T, int H) {
+  extern __shared__ float sacc[];          // [2][8][H][8]
+  const int nacc = 2 * 8 * H * 8;
+  for (int i = threadIdx.x; i < nacc; i += blockDim.x) sacc[i] = 0.f;
+  __syncthreads();
+  const int hs = H * 8;                    // words between the accumulators of neighbouring k
   const int lane = threadIdx.x & 31;
   const int sub = lane >> 3, piece = lane & 7;
   const long warp0 = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -204,46 +215,20 @@ pack_layernorm_backward_kernel(const uint4* __restrict__ dy, const uint4* __rest
           const float x0 = (fx.x - mean) * rstd, x1 = (fx.y - mean) * rstd;
           o[k] = __floats2bfloat162_rn(rstd * (fmaf(fg.x, gg[2 * k], -s1) - x0 * s2),
                                        rstd * (fmaf(fg.y, gg[2 * k + 1], -s1) - x1 * s2));
+          float* a = sacc + (2 * k) * hs + h * 8 + piece;
+          atomicAdd(a, fg.x * x0);
+          atomicAdd(a + hs, fg.y * x1);
+          atomicAdd(a + 8 * hs, fg.x);
+          atomicAdd(a + 9 * hs, fg.y);
         }
         __stcs(dx + (((b * H + h) * T + t) << 3) + piece, o4);
       }
     }
   }
-}
-
-// d_gamma[f] += sum over tokens of dy xhat, d_beta[f] += sum of dy.  One CTA per (batch element, head, block of
-// kTokBlock tokens): thread = (feature of the head, one of four token phases); x is read along its head-major
-// rows, dy along the token-major ones (128 bytes per token either way); the four phases are added in shared
-// memory and the block's 2 x 64 sums leave as fp32 atomic adds (the order of the blocks is not fixed: the last
-// bits of the result can differ from run to run).
-constexpr int kTokBlock = 256;
-__global__ void __launch_bounds__(256) layernorm_param_grad_kernel(const __nv_bfloat16* __restrict__ dy,
-                                                                   const __nv_bfloat16* __restrict__ x,
-                                                                   const float2* __restrict__ stats,
-                                                                   float* __restrict__ d_gamma, float* __restrict__ d_beta,
-                                                                   int T, int H) {
-  __shared__ float red[2][4][64];
-  const int f = threadIdx.x & 63, ph = threadIdx.x >> 6;
-  const int nblk = (T + kTokBlock - 1) / kTokBlock;
-  const int blk = blockIdx.x % nblk;
-  const long bh = blockIdx.x / nblk;
-  const long b = bh / H, h = bh - b * H;
-  const int t0 = blk * kTokBlock, t1 = min(T, t0 + kTokBlock);
-  float ag = 0.f, ab = 0.f;
-  for (int t = t0 + ph; t < t1; t += 4) {
-    const float2 st = stats[b * T + t];
-    const float xv = __bfloat162float(x[(bh * T + t) * 64 + f]);
-    const float gv = __bfloat162float(dy[((b * T + t) * H + h) * 64 + f]);
-    ag = fmaf(gv, (xv - st.x) * st.y, ag);
-    ab += gv;
-  }
-  red[0][ph][f] = ag;
-  red[1][ph][f] = ab;
   __syncthreads();
-  if (threadIdx.x < 128) {
-    const int k = threadIdx.x >> 6;
-    const float v = (red[k][0][f] + red[k][1][f]) + (red[k][2][f] + red[k][3][f]);
-    atomicAdd((k == 0 ? d_gamma : d_beta) + h * 64 + f, v);
+  for (int i = threadIdx.x; i < nacc; i += blockDim.x) {
+    const int pc = i & 7, h = (i >> 3) % H, k = ((i >> 3) / H) & 7, which = (i >> 3) / (8 * H);
+    atomicAdd((which ? d_beta : d_gamma) + h * 64 + pc * 8 + k, sacc[i]);
   }
 }
 
@@ -343,15 +328,18 @@ extern "C" int ttt_b200_pack_layernorm_backward(const void* grad_y, const void* 
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const long tokens = static_cast<long>(B) * T;
-  long blocks = (tokens + 7) / 8;
-  const long cap = static_cast<long>(sms) * 8;
-  if (blocks > cap) blocks = cap;
   const int chunks = (H + 3) / 4;
+  // one wave of CTAs (as many as are resident at once), each looping over its tokens: every CTA ends with
+  // 2 x 64 H atomic adds for the parameter gradients, so there should be no more of them than can run
+  long blocks = (tokens + 7) / 8;
+  const long cap = static_cast<long>(sms) * (chunks <= 4 ? 4 : 2);
+  if (blocks > cap) blocks = cap;
+  const size_t acc_bytes = static_cast<size_t>(2) * 8 * H * 8 * sizeof(float);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
 #define TTT_LNB_LAUNCH(CH)                                                                                       \
-  pack_layernorm_backward_kernel<CH><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(                         \
+  pack_layernorm_backward_kernel<CH><<<static_cast<unsigned>(blocks), 256, acc_bytes, stream>>>(                 \
       static_cast<const uint4*>(grad_y), static_cast<const uint4*>(x), gamma, reinterpret_cast<const float2*>(stats), \
-      static_cast<uint4*>(grad_x), tokens, T, H)
+      static_cast<uint4*>(grad_x), grad_gamma, grad_beta, tokens, T, H)
   if (chunks <= 1) TTT_LNB_LAUNCH(1);
   else if (chunks <= 2) TTT_LNB_LAUNCH(2);
   else if (chunks <= 3) TTT_LNB_LAUNCH(3);
@@ -361,13 +349,7 @@ extern "C" int ttt_b200_pack_layernorm_backward(const void* grad_y, const void* 
   else if (chunks <= 12) TTT_LNB_LAUNCH(12);
   else TTT_LNB_LAUNCH(16);
 #undef TTT_LNB_LAUNCH
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
-  const long grid2 = static_cast<long>(B) * H * ((T + kTokBlock - 1) / kTokBlock);
-  layernorm_param_grad_kernel<<<static_cast<unsigned>(grid2), 256, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(grad_y), static_cast<const __nv_bfloat16*>(x),
-      reinterpret_cast<const float2*>(stats), grad_gamma, grad_beta, T, H);
-  e = cudaGetLastError();
+  const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
   return TTT_B200_OK;
 }
