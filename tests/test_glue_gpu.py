@@ -48,7 +48,7 @@ def test_unpack_layernorm(B, NC, H):
     close(got, og.unpack_layernorm(out, gamma, beta, 1e-6), 2e-2)
 
 
-@pytest.mark.parametrize("B,NC,H", [(1, 1, 1), (2, 2, 3), (1, 5, 32), (2, 1, 12)])
+@pytest.mark.parametrize("B,NC,H", [(1, 1, 1), (2, 2, 3), (1, 5, 32), (2, 1, 12), (1, 1, 64), (1, 2, 38), (3, 9, 8)])
 def test_pack_layernorm_backward(B, NC, H):
     g = torch.Generator().manual_seed(B * 100 + NC * 10 + H + 7)
     out = (torch.randn(B, H, NC, 64, 64, generator=g) * 1.5 + 0.3).bfloat16()

@@ -137,98 +137,142 @@ __global__ void __launch_bounds__(256, (kChunks <= 8 ? 4 : 2)) unpack_layernorm_
 
 // ---- backward of the output norm, fused with the token-major -> head-major turn of the gradient: the
 // result is the operator's grad_L_XQW_mini_batch.  With xhat = (x - mean) rstd and g = dy gamma:
-//   dx = rstd (g - mean(g) - xhat mean(g xhat)).
-// Same work split as the forward: one warp per token, the token's x and dy in registers (packed bf16).
-// The parameter gradients d_gamma[f] += sum over tokens of dy xhat, d_beta[f] += sum of dy come out of the same
-// pass: every lane adds its 8 features per head row into the CTA's accumulators in shared memory
-// ([gamma | beta][k][head][piece]: the 32 lanes of a warp hit 32 consecutive words), and the CTA adds them to
-// the global sums with fp32 atomics when it has run out of tokens (the order of the CTAs is not fixed: the last
-// bits of the result can differ from run to run).  x and dy are read once.
-template <int kChunks>
-__global__ void __launch_bounds__(256, (kChunks <= 4 ? 4 : 2))
+//   dx = rstd (g - mean(g) - xhat mean(g xhat)),   d_gamma[f] += sum over tokens of dy xhat,   d_beta[f] += sum of dy.
+// One pass over x and dy.  A lane owns 8 features (one 16-byte piece of a head row) for every token its CTA
+// works on: warp w takes the heads 4 w .. 4 w + 3 (and 4 (w + 8) .. when H > 32), so the parameter gradients
+// accumulate in 16 registers per head group with no traffic at all, and a token's two row means are put
+// together from the eight warps' partial sums through shared memory, kTokBatch tokens per CTA barrier.  When
+// the CTA has run out of tokens every lane adds its sums to the global ones with fp32 atomics (the order of
+// the CTAs is not fixed: the last bits of the result can differ from run to run).
+constexpr int kTokBatch = 2;
+template <int kGroups>
+__global__ void __launch_bounds__(256, (kGroups == 1 ? 3 : 1))
 pack_layernorm_backward_kernel(const uint4* __restrict__ dy, const uint4* __restrict__ x, const float* __restrict__ gamma,
                                const float2* __restrict__ stats, uint4* __restrict__ dx, float* __restrict__ d_gamma,
                                float* __restrict__ d_beta, long tokens, int T, int H) {
-  extern __shared__ float sacc[];          // [2][8][H][8]
-  const int nacc = 2 * 8 * H * 8;
-  for (int i = threadIdx.x; i < nacc; i += blockDim.x) sacc[i] = 0.f;
-  __syncthreads();
-  const int hs = H * 8;                    // words between the accumulators of neighbouring k
-  const int lane = threadIdx.x & 31;
+  __shared__ float2 part[2][kTokBatch][8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane >> 3, piece = lane & 7;
-  const long warp0 = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const long nwarps = (static_cast<long>(gridDim.x) * blockDim.x) >> 5;
   const float inv_n = 1.f / static_cast<float>(H * 64);
-  for (long tok = warp0; tok < tokens; tok += nwarps) {
-    const long b = tok / T, t = tok - b * T;
-    uint4 rx[kChunks], rg[kChunks];
+  int hh[kGroups];
+  float gg[kGroups][8], ag[kGroups][8], ab[kGroups][8];
 #pragma unroll
-    for (int c = 0; c < kChunks; ++c) {
-      const int h = 4 * c + sub;
-      if (h < H) {
-        rx[c] = __ldcs(x + (((b * H + h) * T + t) << 3) + piece);
-        rg[c] = __ldcs(dy + ((tok * H + h) << 3) + piece);
+  for (int g = 0; g < kGroups; ++g) {
+    hh[g] = 4 * (warp + 8 * g) + sub;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      gg[g][k] = hh[g] < H ? gamma[hh[g] * 64 + piece * 8 + k] : 0.f;
+      ag[g][k] = 0.f;
+      ab[g][k] = 0.f;
+    }
+  }
+  const long nbatch = (tokens + kTokBatch - 1) / kTokBatch;
+  int buf = 0;
+  for (long bt = blockIdx.x; bt < nbatch; bt += gridDim.x, buf ^= 1) {
+    uint4 rx[kTokBatch][kGroups], rg[kTokBatch][kGroups];
+    float2 st[kTokBatch];
+    long xrow[kTokBatch];
+#pragma unroll
+    for (int q = 0; q < kTokBatch; ++q) {
+      const long tok = bt * kTokBatch + q;
+      const bool live = tok < tokens;
+      const long b = live ? tok / T : 0, t = live ? tok - b * T : 0;
+      xrow[q] = b * H * T + t;                      // row of head 0; head h is h * T rows further
+      st[q] = live ? stats[tok] : make_float2(0.f, 0.f);
+#pragma unroll
+      for (int g = 0; g < kGroups; ++g) {
+        if (live && hh[g] < H) {
+          rx[q][g] = __ldcs(x + ((xrow[q] + static_cast<long>(hh[g]) * T) << 3) + piece);
+          rg[q][g] = __ldcs(dy + ((tok * H + hh[g]) << 3) + piece);
+        } else {
+          rx[q][g] = make_uint4(0u, 0u, 0u, 0u);    // dy = 0: no contribution to any sum
+          rg[q][g] = make_uint4(0u, 0u, 0u, 0u);
+        }
       }
     }
-    const float2 st = stats[tok];
-    const float mean = st.x, rstd = st.y;
-    float s1 = 0.f, s2 = 0.f;
+    float s1[kTokBatch], s2[kTokBatch];
 #pragma unroll
-    for (int c = 0; c < kChunks; ++c) {
-      const int h = 4 * c + sub;
-      if (h < H) {
-        const __nv_bfloat162* vx = reinterpret_cast<const __nv_bfloat162*>(&rx[c]);
-        const __nv_bfloat162* vg = reinterpret_cast<const __nv_bfloat162*>(&rg[c]);
-        const int f0 = h * 64 + piece * 8;
-        const float4 g0 = *reinterpret_cast<const float4*>(gamma + f0), g1 = *reinterpret_cast<const float4*>(gamma + f0 + 4);
-        const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+    for (int q = 0; q < kTokBatch; ++q) {
+      s1[q] = 0.f;
+      s2[q] = 0.f;
+#pragma unroll
+      for (int g = 0; g < kGroups; ++g) {
+        const __nv_bfloat162* vx = reinterpret_cast<const __nv_bfloat162*>(&rx[q][g]);
+        const __nv_bfloat162* vg = reinterpret_cast<const __nv_bfloat162*>(&rg[q][g]);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const float2 fx = __bfloat1622float2(vx[k]), fg = __bfloat1622float2(vg[k]);
-          const float a0 = fg.x * gg[2 * k], a1 = fg.y * gg[2 * k + 1];
-          s1 += a0 + a1;
-          s2 = fmaf(a0, (fx.x - mean) * rstd, fmaf(a1, (fx.y - mean) * rstd, s2));
+          const float x0 = (fx.x - st[q].x) * st[q].y, x1 = (fx.y - st[q].x) * st[q].y;
+          const float a0 = fg.x * gg[g][2 * k], a1 = fg.y * gg[g][2 * k + 1];
+          s1[q] += a0 + a1;
+          s2[q] = fmaf(a0, x0, fmaf(a1, x1, s2[q]));
+          ag[g][2 * k] = fmaf(fg.x, x0, ag[g][2 * k]);
+          ag[g][2 * k + 1] = fmaf(fg.y, x1, ag[g][2 * k + 1]);
+          ab[g][2 * k] += fg.x;
+          ab[g][2 * k + 1] += fg.y;
         }
       }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
-      s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-      s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+#pragma unroll
+      for (int q = 0; q < kTokBatch; ++q) {
+        s1[q] += __shfl_xor_sync(0xffffffffu, s1[q], o);
+        s2[q] += __shfl_xor_sync(0xffffffffu, s2[q], o);
+      }
     }
-    s1 *= inv_n;
-    s2 *= inv_n;
+    if (lane < kTokBatch) {
+      float a = s1[0], c = s2[0];
 #pragma unroll
-    for (int c = 0; c < kChunks; ++c) {
-      const int h = 4 * c + sub;
-      if (h < H) {
-        const __nv_bfloat162* vx = reinterpret_cast<const __nv_bfloat162*>(&rx[c]);
-        const __nv_bfloat162* vg = reinterpret_cast<const __nv_bfloat162*>(&rg[c]);
-        const int f0 = h * 64 + piece * 8;
-        const float4 g0 = *reinterpret_cast<const float4*>(gamma + f0), g1 = *reinterpret_cast<const float4*>(gamma + f0 + 4);
-        const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-        uint4 o4;
-        __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&o4);
+      for (int q = 1; q < kTokBatch; ++q)
+        if (lane == q) { a = s1[q]; c = s2[q]; }
+      part[buf][lane][warp] = make_float2(a, c);
+    }
+    // one barrier per batch: the other buffer is written again only after the next barrier, which every thread
+    // passes after it has read this one
+    __syncthreads();
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const float2 fx = __bfloat1622float2(vx[k]), fg = __bfloat1622float2(vg[k]);
-          const float x0 = (fx.x - mean) * rstd, x1 = (fx.y - mean) * rstd;
-          o[k] = __floats2bfloat162_rn(rstd * (fmaf(fg.x, gg[2 * k], -s1) - x0 * s2),
-                                       rstd * (fmaf(fg.y, gg[2 * k + 1], -s1) - x1 * s2));
-          float* a = sacc + (2 * k) * hs + h * 8 + piece;
-          atomicAdd(a, fg.x * x0);
-          atomicAdd(a + hs, fg.y * x1);
-          atomicAdd(a + 8 * hs, fg.x);
-          atomicAdd(a + 9 * hs, fg.y);
+    for (int q = 0; q < kTokBatch; ++q) {
+      const long tok = bt * kTokBatch + q;
+      if (tok >= tokens) break;
+      float m1 = 0.f, m2 = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) {
+        const float2 pw = part[buf][q][w];
+        m1 += pw.x;
+        m2 += pw.y;
+      }
+      m1 *= inv_n;
+      m2 *= inv_n;
+      const float mean = st[q].x, rstd = st[q].y;
+#pragma unroll
+      for (int g = 0; g < kGroups; ++g) {
+        if (hh[g] < H) {
+          const __nv_bfloat162* vx = reinterpret_cast<const __nv_bfloat162*>(&rx[q][g]);
+          const __nv_bfloat162* vg = reinterpret_cast<const __nv_bfloat162*>(&rg[q][g]);
+          uint4 o4;
+          __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float2 fx = __bfloat1622float2(vx[k]), fg = __bfloat1622float2(vg[k]);
+            const float x0 = (fx.x - mean) * rstd, x1 = (fx.y - mean) * rstd;
+            o[k] = __floats2bfloat162_rn(rstd * (fmaf(fg.x, gg[g][2 * k], -m1) - x0 * m2),
+                                         rstd * (fmaf(fg.y, gg[g][2 * k + 1], -m1) - x1 * m2));
+          }
+          __stcs(dx + ((xrow[q] + static_cast<long>(hh[g]) * T) << 3) + piece, o4);
         }
-        __stcs(dx + (((b * H + h) * T + t) << 3) + piece, o4);
       }
     }
   }
-  __syncthreads();
-  for (int i = threadIdx.x; i < nacc; i += blockDim.x) {
-    const int pc = i & 7, h = (i >> 3) % H, k = ((i >> 3) / H) & 7, which = (i >> 3) / (8 * H);
-    atomicAdd((which ? d_beta : d_gamma) + h * 64 + pc * 8 + k, sacc[i]);
+#pragma unroll
+  for (int g = 0; g < kGroups; ++g) {
+    if (hh[g] < H) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        atomicAdd(d_gamma + hh[g] * 64 + piece * 8 + k, ag[g][k]);
+        atomicAdd(d_beta + hh[g] * 64 + piece * 8 + k, ab[g][k]);
+      }
+    }
   }
 }
 
@@ -328,26 +372,18 @@ extern "C" int ttt_b200_pack_layernorm_backward(const void* grad_y, const void* 
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const long tokens = static_cast<long>(B) * T;
-  const int chunks = (H + 3) / 4;
-  // one wave of CTAs (as many as are resident at once), each looping over its tokens: every CTA ends with
-  // 2 x 64 H atomic adds for the parameter gradients, so there should be no more of them than can run
-  long blocks = (tokens + 7) / 8;
-  const long cap = static_cast<long>(sms) * (chunks <= 4 ? 4 : 2);
+  // one wave of CTAs (as many as are resident at once), each looping over its token batches: every CTA ends
+  // with 2 x 64 H atomic adds for the parameter gradients, so there should be no more of them than can run
+  long blocks = (tokens + kTokBatch - 1) / kTokBatch;
+  const long cap = static_cast<long>(sms) * (H <= 32 ? 3 : 1);
   if (blocks > cap) blocks = cap;
-  const size_t acc_bytes = static_cast<size_t>(2) * 8 * H * 8 * sizeof(float);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-#define TTT_LNB_LAUNCH(CH)                                                                                       \
-  pack_layernorm_backward_kernel<CH><<<static_cast<unsigned>(blocks), 256, acc_bytes, stream>>>(                 \
+#define TTT_LNB_LAUNCH(G)                                                                                        \
+  pack_layernorm_backward_kernel<G><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(                          \
       static_cast<const uint4*>(grad_y), static_cast<const uint4*>(x), gamma, reinterpret_cast<const float2*>(stats), \
       static_cast<uint4*>(grad_x), grad_gamma, grad_beta, tokens, T, H)
-  if (chunks <= 1) TTT_LNB_LAUNCH(1);
-  else if (chunks <= 2) TTT_LNB_LAUNCH(2);
-  else if (chunks <= 3) TTT_LNB_LAUNCH(3);
-  else if (chunks <= 4) TTT_LNB_LAUNCH(4);
-  else if (chunks <= 6) TTT_LNB_LAUNCH(6);
-  else if (chunks <= 8) TTT_LNB_LAUNCH(8);
-  else if (chunks <= 12) TTT_LNB_LAUNCH(12);
-  else TTT_LNB_LAUNCH(16);
+  if (H <= 32) TTT_LNB_LAUNCH(1);
+  else TTT_LNB_LAUNCH(2);
 #undef TTT_LNB_LAUNCH
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
