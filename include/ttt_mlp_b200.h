@@ -44,7 +44,7 @@ enum {
   TTT_B200_FLAG_TEST_LOST_LOAD = 2u,
   /* Bits 8..11: how many CTAs (a thread-block cluster) share one (batch, head) stream, each owning
    * 256 / n hidden units; the reference fixes this at compile time (TP = 2 in kernels/ttt/ttt.cu:11-12,
-   * 4 in kernels/ttt_backward/ttt.cu:12-16).  0 = chosen per launch from B*H and the GPU's SM count
+   * 4 in kernels/ttt_backward/ttt.cu:12-16).  0 = chosen per launch from B*H and the number of clusters the GPU runs at once
    * (overridable with the environment variable TTT_B200_CLUSTER); 1, 2 or 4 = forced. */
   TTT_B200_FLAG_CLUSTER_SHIFT = 8,
   TTT_B200_FLAG_CLUSTER_MASK = 0xFu << 8
