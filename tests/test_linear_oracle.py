@@ -47,3 +47,27 @@ def test_driver_loop_checkpoints_and_final_state():
     assert torch.equal(t["Out"], r["Out"][:, :, 2:])
     assert torch.equal(t["W1_final"], r["W1_final"]) and torch.equal(t["b1_final"], r["b1_final"])
     assert torch.equal(t["W1_checkpoints"][:, :, 1], r["W1_checkpoints"][:, :, 2])
+
+
+def test_hand_derived_backward_equals_autograd():
+    """The reverse step the backward kernel follows, against torch.autograd through the forward, in fp64, with
+    non-zero upstream state gradients and a ragged last checkpoint group."""
+    torch.manual_seed(1)
+    B, H, NC, cgs = 2, 2, 5, 2
+    dt = torch.float64
+    d = lin.make_inputs(B, H, NC, seed=9)
+    d = {k: v.to(dt) for k, v in d.items()}
+    go = torch.randn(B, H, NC, 64, 64, dtype=dt)
+    gW = 1e-2 * torch.randn(B, H, 64, 64, dtype=dt)
+    gb = 1e-2 * torch.randn(B, H, 1, 64, dtype=dt)
+    f = lin.ttt_linear_forward(d["XQ"], d["XK"], d["XV"], d["last_eta"], d["ttt_norm_weight"], d["ttt_norm_bias"],
+                               d["W1"], d["b1"], cgs, dtype=dt)
+    a = lin.ttt_linear_backward_autograd(d["XQ"], d["XK"], d["XV"], d["last_eta"], d["ttt_norm_weight"],
+                                         d["ttt_norm_bias"], d["W1"], d["b1"], go, gW, gb, cgs, dtype=dt)
+    h = lin.ttt_linear_backward(d["XQ"], d["XK"], d["XV"], d["last_eta"], d["ttt_norm_weight"], d["ttt_norm_bias"],
+                                f["W1_checkpoints"], f["b1_checkpoints"], go, gW, gb, cgs, dtype=dt)
+    for k in ("grad_L_XQ", "grad_L_XK", "grad_L_XV", "grad_L_W1_init", "grad_L_b1_init"):
+        assert orc.rel_l2(h[k], a[k]) < 1e-9, k
+    assert orc.rel_l2(h["grad_L_last_eta"].squeeze(-1), a["grad_L_last_eta"]) < 1e-9
+    assert orc.rel_l2(h["grad_L_ttt_norm_weight"].sum(0, keepdim=True), a["grad_L_ttt_norm_weight"]) < 1e-9
+    assert orc.rel_l2(h["grad_L_ttt_norm_bias"].sum(0, keepdim=True), a["grad_L_ttt_norm_bias"]) < 1e-9
