@@ -106,6 +106,39 @@ typedef struct ttt_b200_linear_fwd_args {
   float* b1_final;
 } ttt_b200_linear_fwd_args;
 
+/* Arguments of the TTT-Linear backward: gradients of ttt_b200_linear_forward from its checkpoints (per
+ * checkpoint group: recompute, then reverse sweep).  `scratch` is caller-provided working memory of at least
+ * ttt_b200_linear_backward_scratch_bytes(B, H, checkpoint_group_size) bytes, 16-byte aligned, contents
+ * unspecified before and after.  Outputs are overwritten; the norm gradients come per batch element
+ * ([B,H,64]: the caller sums over B), like the MLP operator's.  No counterpart in the reference. */
+typedef struct ttt_b200_linear_bwd_args {
+  const void* XQ;                    /* bf16 [B,H,NC,64,64] */
+  const void* XK;
+  const void* XV;
+  const void* last_eta;              /* bf16 [B,H,NC,64] */
+  const float* ttt_norm_weight;      /* [H,64] */
+  const float* ttt_norm_bias;        /* [H,64] */
+  const float* W1_checkpoints;       /* [B,H,n,64,64] written by the forward */
+  const float* b1_checkpoints;       /* [B,H,n,64] */
+  const float* grad_L_W1_last;       /* [B,H,64,64] dL/d(state after the last mini-batch) */
+  const float* grad_L_b1_last;       /* [B,H,64] */
+  const void* grad_L_XQW_mini_batch; /* bf16 [B,H,NC,64,64] dL/dOut */
+  void* scratch;
+  float* grad_L_ttt_norm_weight;     /* [B,H,64] */
+  float* grad_L_ttt_norm_bias;       /* [B,H,64] */
+  float* grad_L_W1_init;             /* [B,H,64,64] */
+  float* grad_L_b1_init;             /* [B,H,64] */
+  void* grad_L_last_eta;             /* bf16 [B,H,NC,64] */
+  void* grad_L_XQ;                   /* bf16 [B,H,NC,64,64] */
+  void* grad_L_XK;
+  void* grad_L_XV;
+  int32_t B, H, NC;
+  int32_t checkpoint_group_size;
+  int32_t num_checkpoints;
+  uint32_t flags;                    /* TTT_B200_FLAG_SYNC, TTT_B200_FLAG_TEST_LOST_LOAD */
+  uint64_t scratch_bytes;            /* size of `scratch`, checked against the requirement */
+} ttt_b200_linear_bwd_args;
+
 /* Arguments of the backward.  Replaces ttt_backward(...43 positional arguments...)
  * -- kernels/ttt_backward/ttt.cu:1451-1495; same order.  The sixteen `*_group` tensors are
  * caller-provided scratch of the reference's shapes; this implementation uses a subset of
@@ -234,6 +267,12 @@ const char* ttt_b200_last_error(void);
 /* TTT-Linear forward (see ttt_b200_linear_fwd_args): one CTA per (batch, head) stream, stream-ordered,
  * same status codes and status-word protocol as ttt_b200_forward. */
 int ttt_b200_linear_forward(const ttt_b200_linear_fwd_args* args, void* cuda_stream);
+
+/* TTT-Linear backward (see ttt_b200_linear_bwd_args): one CTA per (batch, head) stream, stream-ordered, same
+ * status codes and status-word protocol as ttt_b200_backward. */
+int ttt_b200_linear_backward(const ttt_b200_linear_bwd_args* args, void* cuda_stream);
+/* Bytes of scratch ttt_b200_linear_backward needs (33 280 per stream and mini-batch of a checkpoint group). */
+uint64_t ttt_b200_linear_backward_scratch_bytes(int B, int H, int checkpoint_group_size);
 
 /* Take (read and clear) the device-side status word: 0, or TTT_B200_ERR_TIMEOUT if a kernel of
  * this process gave up on a bounded wait since the last take.  Call after synchronising. */

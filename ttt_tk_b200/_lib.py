@@ -40,6 +40,16 @@ class LinearFwdArgs(ctypes.Structure):
     _fields_ = [(n, c_void_p) for n in LINEAR_FWD_FIELDS] + _DIMS + [(n, c_void_p) for n in LINEAR_FWD_TAIL]
 
 
+LINEAR_BWD_FIELDS = ["XQ", "XK", "XV", "last_eta", "ttt_norm_weight", "ttt_norm_bias", "W1_checkpoints", "b1_checkpoints",
+                     "grad_L_W1_last", "grad_L_b1_last", "grad_L_XQW_mini_batch", "scratch", "grad_L_ttt_norm_weight",
+                     "grad_L_ttt_norm_bias", "grad_L_W1_init", "grad_L_b1_init", "grad_L_last_eta", "grad_L_XQ",
+                     "grad_L_XK", "grad_L_XV"]
+
+
+class LinearBwdArgs(ctypes.Structure):
+    _fields_ = [(n, c_void_p) for n in LINEAR_BWD_FIELDS] + _DIMS + [("scratch_bytes", ctypes.c_uint64)]
+
+
 class BwdArgs(ctypes.Structure):
     _fields_ = [(n, c_void_p) for n in BWD_FIELDS] + _DIMS
 
@@ -53,7 +63,7 @@ class BwdNoAllocArgs(ctypes.Structure):
     _fields_ = [(n, c_void_p) for n in BWD_NOALLOC_FIELDS] + _DIMS
 
 
-EXPORTS = ["ttt_b200_forward", "ttt_b200_linear_forward", "ttt_b200_backward", "ttt_b200_backward_noalloc", "ttt_b200_last_error", "ttt_b200_take_status",
+EXPORTS = ["ttt_b200_forward", "ttt_b200_linear_forward", "ttt_b200_linear_backward", "ttt_b200_linear_backward_scratch_bytes", "ttt_b200_backward", "ttt_b200_backward_noalloc", "ttt_b200_last_error", "ttt_b200_take_status",
            "ttt_b200_version", "ttt_b200_pick_cluster", "ttt_b200_cluster_capacity", "ttt_b200_umma_selftest", "ttt_b200_wait_selftest", "ttt_b200_pack_tokens",
            "ttt_b200_unpack_tokens", "ttt_b200_eta_gate", "ttt_b200_eta_gate_backward", "ttt_b200_unpack_layernorm",
            "ttt_b200_pack_layernorm_backward"]
@@ -72,6 +82,10 @@ def load():
     lib.ttt_b200_forward.restype = ctypes.c_int
     lib.ttt_b200_linear_forward.argtypes = [ctypes.POINTER(LinearFwdArgs), c_void_p]
     lib.ttt_b200_linear_forward.restype = ctypes.c_int
+    lib.ttt_b200_linear_backward.argtypes = [ctypes.POINTER(LinearBwdArgs), c_void_p]
+    lib.ttt_b200_linear_backward.restype = ctypes.c_int
+    lib.ttt_b200_linear_backward_scratch_bytes.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int]
+    lib.ttt_b200_linear_backward_scratch_bytes.restype = ctypes.c_uint64
     lib.ttt_b200_backward.argtypes = [ctypes.POINTER(BwdArgs), c_void_p]
     lib.ttt_b200_backward.restype = ctypes.c_int
     lib.ttt_b200_backward_noalloc.argtypes = [ctypes.POINTER(BwdNoAllocArgs), c_void_p]

@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libttt_mlp_b200.so")
-SOURCES = ["ttt_capi.cu", "ttt_fwd_sm100.cu", "ttt_bwd_sm100.cu", "ttt_fwd_cluster_sm100.cu", "ttt_bwd_cluster_sm100.cu", "ttt_linear_fwd_sm100.cu",
+SOURCES = ["ttt_capi.cu", "ttt_fwd_sm100.cu", "ttt_bwd_sm100.cu", "ttt_fwd_cluster_sm100.cu", "ttt_bwd_cluster_sm100.cu", "ttt_linear_fwd_sm100.cu", "ttt_linear_bwd_sm100.cu",
            "ttt_layout.cu", "ttt_glue.cu", "umma_selftest.cu"]
 HEADERS = ["sm100_ptx.cuh", "ttt_device.cuh", "ttt_cluster.cuh", "ttt_internal.h", os.path.join("..", "..", "include", "ttt_mlp_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

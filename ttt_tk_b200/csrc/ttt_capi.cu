@@ -23,6 +23,9 @@ int ttt_launch_backward_cluster(const ttt_b200_bwd_args* a, int cluster, cudaStr
                                 uint64_t limit_ns, int drop_load);
 int ttt_launch_linear_forward(const ttt_b200_linear_fwd_args* a, cudaStream_t stream, uint32_t* status,
                               uint64_t limit_ns, int drop_load);
+int ttt_launch_linear_backward(const ttt_b200_linear_bwd_args* a, cudaStream_t stream, uint32_t* status,
+                               uint64_t limit_ns, int drop_load);
+uint64_t ttt_linear_backward_scratch_bytes(int B, int H, int cgs);
 int ttt_forward_cluster_capacity(int cluster);
 int ttt_backward_cluster_capacity(int cluster);
 int ttt_launch_forward_cluster(const ttt_b200_fwd_args* a, int cluster, cudaStream_t stream, uint32_t* status,
@@ -247,6 +250,35 @@ extern "C" int ttt_b200_linear_forward(const ttt_b200_linear_fwd_args* a, void* 
   if (int rc = pre_launch(&status)) return rc;
   const int drop = (a->flags & TTT_B200_FLAG_TEST_LOST_LOAD) ? (a->NC > 1 ? 1 : 0) : -1;
   if (int rc = ttt_launch_linear_forward(a, stream, status, wait_limit_ns(), drop)) return rc;
+  if (a->flags & TTT_B200_FLAG_SYNC) return ttt_check_status(stream);
+  return TTT_B200_OK;
+}
+
+extern "C" uint64_t ttt_b200_linear_backward_scratch_bytes(int B, int H, int checkpoint_group_size) {
+  if (B < 1 || H < 1 || checkpoint_group_size < 1) return 0;
+  return ttt_linear_backward_scratch_bytes(B, H, checkpoint_group_size);
+}
+
+extern "C" int ttt_b200_linear_backward(const ttt_b200_linear_bwd_args* a, void* stream_) {
+  TTT_REQUIRE(a != nullptr, "args is NULL");
+  if (int rc = check_dims(a->B, a->H, a->NC, a->checkpoint_group_size, a->num_checkpoints)) return rc;
+  const void* ptrs[] = {a->XQ, a->XK, a->XV, a->last_eta, a->ttt_norm_weight, a->ttt_norm_bias, a->W1_checkpoints,
+                        a->b1_checkpoints, a->grad_L_W1_last, a->grad_L_b1_last, a->grad_L_XQW_mini_batch, a->scratch,
+                        a->grad_L_ttt_norm_weight, a->grad_L_ttt_norm_bias, a->grad_L_W1_init, a->grad_L_b1_init,
+                        a->grad_L_last_eta, a->grad_L_XQ, a->grad_L_XK, a->grad_L_XV};
+  for (const void* q : ptrs) {
+    TTT_REQUIRE(q != nullptr, "a required tensor pointer is NULL");
+    TTT_REQUIRE(aligned16(q), "tensor pointers must be 16-byte aligned");
+  }
+  TTT_REQUIRE(a->scratch_bytes >= ttt_linear_backward_scratch_bytes(a->B, a->H, a->checkpoint_group_size),
+              "scratch is smaller than ttt_b200_linear_backward_scratch_bytes(B, H, checkpoint_group_size)");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  uint32_t* status = nullptr;
+  if (int rc = pre_launch(&status)) return rc;
+  // the hook drops the recompute inputs of the last group's second mini-batch (its only one if it has one)
+  const int last0 = (a->num_checkpoints - 1) * a->checkpoint_group_size;
+  const int drop = (a->flags & TTT_B200_FLAG_TEST_LOST_LOAD) ? (last0 + 1 < a->NC ? last0 + 1 : last0) : -1;
+  if (int rc = ttt_launch_linear_backward(a, stream, status, wait_limit_ns(), drop)) return rc;
   if (a->flags & TTT_B200_FLAG_SYNC) return ttt_check_status(stream);
   return TTT_B200_OK;
 }

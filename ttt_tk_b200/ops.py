@@ -170,6 +170,61 @@ def ttt_linear_forward(XQ, XK, XV, last_eta, ttt_norm_weight, ttt_norm_bias, W1,
     return Out
 
 
+def ttt_linear_backward(XQ, XK, XV, last_eta, ttt_norm_weight, ttt_norm_bias, W1_checkpoints, b1_checkpoints,
+                        grad_L_W1_last, grad_L_b1_last, grad_L_XQW_mini_batch, grad_L_ttt_norm_weight,
+                        grad_L_ttt_norm_bias, grad_L_W1_init, grad_L_b1_init, grad_L_last_eta, grad_L_XQ, grad_L_XK,
+                        grad_L_XV, checkpoint_group_size, *, scratch=None, sync=False, _lost_load=False):
+    """TTT-Linear backward: gradients of `ttt_linear_forward` from its checkpoints.  Outputs (overwritten):
+    norm gradients per batch element fp32 [B,H,1,64], dL/d(initial state) fp32 [B,H,64,64] / [B,H,1,64],
+    grad_L_last_eta bf16 [B,H,NC,64] (or [..., 64, 1]), grad_L_XQ / XK / XV bf16 [B,H,NC,64,64].  `scratch`: a
+    uint8 CUDA tensor of at least `linear_backward_scratch_bytes(B, H, checkpoint_group_size)` bytes (allocated
+    here when not given).  The reference has no counterpart."""
+    lib = _lib.lib()
+    B, H, NC, cgs, n = _dims(XQ, checkpoint_group_size, W1_checkpoints)
+    dev = XQ.device
+    bf, f32 = torch.bfloat16, torch.float32
+    tok = (B, H, NC, CS, F)
+    for t, name in ((XQ, "XQ"), (XK, "XK"), (XV, "XV"), (grad_L_XQW_mini_batch, "grad_L_XQW_mini_batch"),
+                    (grad_L_XQ, "grad_L_XQ"), (grad_L_XK, "grad_L_XK"), (grad_L_XV, "grad_L_XV")):
+        _chk_tensor(t, name, bf, tok, dev)
+    _chk_eta(last_eta, "last_eta", B, H, NC, dev)
+    _chk_eta(grad_L_last_eta, "grad_L_last_eta", B, H, NC, dev)
+    _chk_tensor(ttt_norm_weight, "ttt_norm_weight", f32, (1, H, 1, F), dev)
+    _chk_tensor(ttt_norm_bias, "ttt_norm_bias", f32, (1, H, 1, F), dev)
+    _chk_tensor(W1_checkpoints, "W1_checkpoints", f32, (B, H, n, F, F), dev)
+    _chk_tensor(b1_checkpoints, "b1_checkpoints", f32, (B, H, n, 1, F), dev)
+    _chk_tensor(grad_L_W1_last, "grad_L_W1_last", f32, (B, H, F, F), dev)
+    _chk_tensor(grad_L_b1_last, "grad_L_b1_last", f32, (B, H, 1, F), dev)
+    _chk_tensor(grad_L_ttt_norm_weight, "grad_L_ttt_norm_weight", f32, (B, H, 1, F), dev)
+    _chk_tensor(grad_L_ttt_norm_bias, "grad_L_ttt_norm_bias", f32, (B, H, 1, F), dev)
+    _chk_tensor(grad_L_W1_init, "grad_L_W1_init", f32, (B, H, F, F), dev)
+    _chk_tensor(grad_L_b1_init, "grad_L_b1_init", f32, (B, H, 1, F), dev)
+    need = linear_backward_scratch_bytes(B, H, cgs)
+    if scratch is None:
+        scratch = torch.empty(need, dtype=torch.uint8, device=dev)
+    _check(isinstance(scratch, torch.Tensor) and scratch.is_cuda and scratch.device == dev and scratch.is_contiguous()
+           and scratch.dtype == torch.uint8 and scratch.numel() >= need,
+           f"scratch must be a contiguous uint8 CUDA tensor of at least {need} bytes")
+    a = _lib.LinearBwdArgs()
+    vals = [XQ, XK, XV, last_eta, ttt_norm_weight, ttt_norm_bias, W1_checkpoints, b1_checkpoints, grad_L_W1_last,
+            grad_L_b1_last, grad_L_XQW_mini_batch, scratch, grad_L_ttt_norm_weight, grad_L_ttt_norm_bias, grad_L_W1_init,
+            grad_L_b1_init, grad_L_last_eta, grad_L_XQ, grad_L_XK, grad_L_XV]
+    for name, t in zip(_lib.LINEAR_BWD_FIELDS, vals):
+        setattr(a, name, t.data_ptr())
+    a.B, a.H, a.NC, a.checkpoint_group_size, a.num_checkpoints = B, H, NC, cgs, n
+    a.flags = _flags(sync, None, _lost_load)
+    a.scratch_bytes = scratch.numel()
+    with torch.cuda.device(dev):
+        rc = lib.ttt_b200_linear_backward(ctypes.byref(a), _stream_ptr(dev))
+    if rc != 0:
+        _raise(lib, rc, "ttt_linear_backward")
+
+
+def linear_backward_scratch_bytes(B, H, checkpoint_group_size):
+    """Bytes of scratch `ttt_linear_backward` needs."""
+    return int(_lib.lib().ttt_b200_linear_backward_scratch_bytes(int(B), int(H), int(checkpoint_group_size)))
+
+
 def ttt_backward(XQ, XK, XV, last_eta, ttt_norm_weight, ttt_norm_bias,
                  W1_checkpoints, b1_checkpoints, W2_checkpoints, b2_checkpoints, Out,
                  W1_init_group, b1_init_group, W2_init_group, b2_init_group,
