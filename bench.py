@@ -613,6 +613,16 @@ def run_linear(args):
     ck = [torch.empty(B, H, n, 64, 64, device=dev), torch.empty(B, H, n, 1, 64, device=dev)]
     out = torch.empty_like(XQ)
     fn = lambda: ttt_linear_forward(XQ, XK, XV, eta, gamma, beta, W1, b1, *ck, out, cgs)
+    # the backward of the same problem, timed separately (reported under "kernels")
+    from ttt_tk_b200 import ttt_linear_backward
+    from ttt_tk_b200.ops import linear_backward_scratch_bytes
+    go = rn(B, H, NC, 64, 64).bfloat16()
+    gW, gb = 1e-3 * rn(B, H, 64, 64), 1e-3 * rn(B, H, 1, 64)
+    scratch = torch.empty(linear_backward_scratch_bytes(B, H, cgs), dtype=torch.uint8, device=dev)
+    bouts = [torch.empty(B, H, 1, 64, device=dev), torch.empty(B, H, 1, 64, device=dev), torch.empty(B, H, 64, 64, device=dev),
+             torch.empty(B, H, 1, 64, device=dev), torch.empty(B, H, NC, 64, device=dev, dtype=torch.bfloat16),
+             torch.empty_like(XQ), torch.empty_like(XQ), torch.empty_like(XQ)]
+    bfn = lambda: ttt_linear_backward(XQ, XK, XV, eta, gamma, beta, *ck, gW, gb, go, *bouts, cgs, scratch=scratch)
     K, W = args.steps, max(args.warmup, 3)
     sampler = ClockSampler(0)
     sampler.start()
@@ -625,10 +635,23 @@ def run_linear(args):
         fn()
     e1.record()
     torch.cuda.synchronize()
+    for _ in range(W):
+        bfn()
+    torch.cuda.synchronize()
+    b0, b1e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    b0.record()
+    for _ in range(K):
+        bfn()
+    b1e.record()
+    torch.cuda.synchronize()
     clocks = sampler.stop()
     if take_status() != 0:
         raise RuntimeError("a device-side wait ran out")
     ms = e0.elapsed_time(e1) / K
+    bwd_ms = b0.elapsed_time(b1e) / K
+    # backward: Q, K, V, eta, dOut in; dQ, dK, dV, d_eta out; checkpoints; state gradients in and out
+    bwd_bytes = B * H * (NC * 64 * 900 + (n + 2) * (64 * 64 + 64) * 4 + 1024)
+    bwd_scratch = B * H * NC * 2 * 33280         # every slot written once and read once
     state = (64 * 64 + 64) * 4
     nbytes = B * H * (NC * 64 * 514 + state + 512 + n * state)
     flops = B * H * NC * 3 * 2 * 64 ** 3
@@ -641,12 +664,16 @@ def run_linear(args):
         "config": {"workload": desc, "B": B, "H": H, "seq_len": NC * 64, "checkpoint_group_size": cgs,
                    "l2": "inputs + outputs per step exceed the 126 MB L2; no explicit flush"},
         "kernels": {"fwd_ms": ms, "fwd_tflops": flops / (ms * 1e-3) / 1e12,
+                    "bwd_ms": bwd_ms, "bwd_algorithmic_gbs": bwd_bytes / bwd_ms / 1e6,
+                    "bwd_frac_of_hbm_peak": bwd_bytes / bwd_ms / 1e6 / peaks()[0]["hbm_gbs"],
+                    "bwd_gbs_with_scratch": (bwd_bytes + bwd_scratch) / bwd_ms / 1e6,
+                    "fwd_bwd_tokens_per_s": B * NC * 64 / ((ms + bwd_ms) * 1e-3),
                     # three CTAs (streams) share an SM: 444 run at once on 148 SMs
                     "waves": -(-(B * H) // 444), "us_per_mini_batch_per_wave": ms * 1e3 / (NC * -(-(B * H) // 444))},
         "roofline": {"kernel": "ttt_linear_fwd_kernel", "bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"],
                      "unit": "GB/s", "frac": gbs / pk["hbm_gbs"], "traffic": None,
                      "peak_source": f"{pk_src} copy bandwidth"},
-        "gpu_launches": K, "clocks": clocks,
+        "gpu_launches": 2 * K, "clocks": clocks,
     }
 
 

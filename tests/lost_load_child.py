@@ -84,6 +84,36 @@ def main():
     e = lin.rel_l2(linear(False).float().cpu(), fl["Out"])
     assert e <= 1e-2, ("linear forward", e)
     print("linear forward: lost load reported, next launch correct", flush=True)
+    from ttt_tk_b200 import ttt_linear_backward
+    gl = torch.Generator().manual_seed(3)
+    go = torch.randn(B, H, NC, 64, 64, generator=gl).bfloat16()
+    gW, gb = 1e-3 * torch.randn(B, H, 64, 64, generator=gl), 1e-3 * torch.randn(B, H, 1, 64, generator=gl)
+    rl = lin.ttt_linear_backward(dl["XQ"], dl["XK"], dl["XV"], dl["last_eta"], dl["ttt_norm_weight"],
+                                 dl["ttt_norm_bias"], fl["W1_checkpoints"], fl["b1_checkpoints"], go, gW, gb, cgs)
+    ckl = [fl["W1_checkpoints"].to(dev).contiguous(), fl["b1_checkpoints"].to(dev).contiguous()]
+
+    def linear_bwd(lost):
+        outs = [torch.zeros(B, H, 1, 64, device=dev), torch.zeros(B, H, 1, 64, device=dev),
+                torch.zeros(B, H, 64, 64, device=dev), torch.zeros(B, H, 1, 64, device=dev),
+                torch.zeros(B, H, NC, 64, device=dev, dtype=torch.bfloat16), torch.zeros_like(tl["XQ"]),
+                torch.zeros_like(tl["XQ"]), torch.zeros_like(tl["XQ"])]
+        ttt_linear_backward(tl["XQ"], tl["XK"], tl["XV"], tl["last_eta"], tl["ttt_norm_weight"], tl["ttt_norm_bias"],
+                            *ckl, gW.to(dev), gb.to(dev), go.to(dev), *outs, cgs, sync=True, _lost_load=lost)
+        return outs
+
+    try:
+        linear_bwd(True)
+    except RuntimeError as e:
+        assert "code 3" in str(e) and "bounded wait" in str(e), str(e)
+    else:
+        raise AssertionError("linear backward: the lost load went unnoticed")
+    assert take_status() == 0
+    res = linear_bwd(False)
+    e = lin.rel_l2(res[5].float().cpu(), rl["grad_L_XQ"])
+    assert e <= 3e-2, ("linear backward", e)
+    e = lin.rel_l2(res[2].cpu(), rl["grad_L_W1_init"])
+    assert e <= 3e-2, ("linear backward", e)
+    print("linear backward: lost load reported, next launch correct", flush=True)
     print("LOST_LOAD_OK")
 
 

@@ -88,3 +88,44 @@ def test_linear_backward_rejects_small_scratch():
     d = make(1, 1, 2, seed=0)
     with pytest.raises(RuntimeError, match="scratch"):
         run(d, 2, scratch=torch.empty(1024, dtype=torch.uint8, device="cuda"))
+
+
+def test_linear_backward_stays_inside_its_scratch_and_leaves_inputs_alone():
+    """The scratch buffer and every output sit between guard zones; the kernel stores scratch as raw bulk copies at
+    computed slot offsets, so a mis-sized slot would land in a guard zone.  (compute-sanitizer is not available.)"""
+    from ttt_tk_b200.ops import linear_backward_scratch_bytes
+    B, H, NC, cgs = 2, 3, 5, 2
+    GUARD, PAT = 4096, 0xA5
+    dev = "cuda"
+    d = make(B, H, NC, seed=21)
+    f, ref = oracle(d, cgs)
+    t = {k: v.to(dev) for k, v in d.items()}
+    ck = [f["W1_checkpoints"].to(dev).contiguous(), f["b1_checkpoints"].to(dev).contiguous()]
+    need = linear_backward_scratch_bytes(B, H, cgs)
+    assert need == B * H * cgs * 33280
+    raws = []
+
+    def guarded(nbytes):
+        raw = torch.full((GUARD + nbytes + GUARD,), PAT, dtype=torch.uint8, device=dev)
+        raws.append((raw, nbytes))
+        return raw[GUARD:GUARD + nbytes]
+
+    scratch = guarded(need)
+    shapes = [((B, H, 1, 64), torch.float32)] * 2 + [((B, H, 64, 64), torch.float32), ((B, H, 1, 64), torch.float32),
+                                                    ((B, H, NC, 64), torch.bfloat16)] + [((B, H, NC, 64, 64), torch.bfloat16)] * 3
+    outs = []
+    for shp, dt in shapes:
+        n = 1
+        for x in shp:
+            n *= x
+        outs.append(guarded(n * (4 if dt == torch.float32 else 2)).view(dt).view(*shp))
+    before = {k: v.clone() for k, v in t.items()}
+    ttt_linear_backward(t["XQ"], t["XK"], t["XV"], t["last_eta"], t["ttt_norm_weight"], t["ttt_norm_bias"], *ck,
+                        t["grad_W1_last"], t["grad_b1_last"], t["grad_out"], *outs, cgs, scratch=scratch)
+    torch.cuda.synchronize()
+    assert take_status() == 0
+    for i, (raw, nbytes) in enumerate(raws):
+        assert bool((raw[:GUARD] == PAT).all()) and bool((raw[GUARD + nbytes:] == PAT).all()), f"guard zone of buffer {i}"
+    for k, v in t.items():
+        assert torch.equal(v, before[k]), k
+    check({k: o.float().cpu() for k, o in zip(NAMES, outs)}, ref)
