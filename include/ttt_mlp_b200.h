@@ -85,7 +85,7 @@ typedef struct ttt_b200_fwd_args {
 /* Arguments of the TTT-Linear forward: the same operator with the inner model reduced to one linear layer,
  * f(x) = x W1 + b1 with W1 [64 x 64] (the hidden layer, W2 and b2 dropped; everything else, the checkpoint
  * rule included, as in ttt_b200_fwd_args).  The reference has no counterpart: it ships the TTT-MLP operator
- * only (README.md:18).  Forward only. */
+ * only (README.md:18).  Its backward: ttt_b200_linear_bwd_args. */
 typedef struct ttt_b200_linear_fwd_args {
   const void* XQ;                /* bf16 [B,H,NC,64,64] */
   const void* XK;                /* bf16 [B,H,NC,64,64] */
