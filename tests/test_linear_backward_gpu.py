@@ -129,3 +129,28 @@ def test_linear_backward_stays_inside_its_scratch_and_leaves_inputs_alone():
     for k, v in t.items():
         assert torch.equal(v, before[k]), k
     check({k: o.float().cpu() for k, o in zip(NAMES, outs)}, ref)
+
+
+def test_linear_autograd_function_against_oracle_autograd():
+    """The torch.autograd.Function over the operator pair: loss.backward() through it gives the oracle's autograd
+    gradients (norm gradients summed over the batch, the final state an output with its own upstream gradient)."""
+    from ttt_tk_b200.autograd import ttt_linear
+    B, H, NC = 2, 2, 6
+    d = make(B, H, NC, seed=31)
+    ref = lin.ttt_linear_backward_autograd(d["XQ"], d["XK"], d["XV"], d["last_eta"], d["ttt_norm_weight"],
+                                           d["ttt_norm_bias"], d["W1"], d["b1"], d["grad_out"], d["grad_W1_last"],
+                                           d["grad_b1_last"], cgs=1)
+    keys = ["XQ", "XK", "XV", "last_eta", "ttt_norm_weight", "ttt_norm_bias", "W1", "b1"]
+    leaves = {k: d[k].cuda().requires_grad_(True) for k in keys}
+    out, (Wf, bf) = ttt_linear(*[leaves[k] for k in keys], checkpoint_group_size=4)
+    loss = (out.float() * d["grad_out"].cuda().float()).sum() + (Wf * d["grad_W1_last"].cuda()).sum() + \
+        (bf * d["grad_b1_last"].cuda()).sum()
+    loss.backward()
+    torch.cuda.synchronize()
+    assert take_status() == 0
+    names = {"XQ": "grad_L_XQ", "XK": "grad_L_XK", "XV": "grad_L_XV", "last_eta": "grad_L_last_eta",
+             "ttt_norm_weight": "grad_L_ttt_norm_weight", "ttt_norm_bias": "grad_L_ttt_norm_bias",
+             "W1": "grad_L_W1_init", "b1": "grad_L_b1_init"}
+    for k, n in names.items():
+        err = lin.rel_l2(leaves[k].grad.float().cpu(), ref[n])
+        assert err <= TOL, f"{k}: rel-L2 {err:.3e}"

@@ -85,3 +85,69 @@ def ttt_mlp(XQ, XK, XV, last_eta, ttt_norm_weight, ttt_norm_bias, W1, b1, W2, b2
     r = TTTMLPFunction.apply(XQ, XK, XV, last_eta, ttt_norm_weight, ttt_norm_bias, W1, b1, W2, b2,
                              checkpoint_group_size)
     return r[0], tuple(r[1:])
+
+
+_linear_scratch_cache = {}
+
+
+def _linear_scratch(B, H, cgs, device):
+    from .ops import linear_backward_scratch_bytes
+    key = (B, H, cgs, str(device), torch.cuda.current_stream(device).cuda_stream)
+    if key not in _linear_scratch_cache:
+        _linear_scratch_cache[key] = torch.empty(linear_backward_scratch_bytes(B, H, cgs), dtype=torch.uint8,
+                                                 device=device)
+    return _linear_scratch_cache[key]
+
+
+class TTTLinearFunction(torch.autograd.Function):
+    """(XQW, W1_last, b1_last) = f(XQ, XK, XV, last_eta, norm_weight, norm_bias, W1, b1, checkpoint_group_size):
+    the TTT-Linear operator pair (`ttt_linear_forward` / `ttt_linear_backward`)."""
+
+    @staticmethod
+    def forward(ctx, XQ, XK, XV, last_eta, ttt_norm_weight, ttt_norm_bias, W1, b1, checkpoint_group_size):
+        from .ops import ttt_linear_forward
+        B, H, NC = XQ.shape[:3]
+        cgs = int(checkpoint_group_size)
+        dev = XQ.device
+        args = [t.contiguous() for t in (XQ, XK, XV, last_eta, ttt_norm_weight, ttt_norm_bias, W1, b1)]
+        n = math.ceil(NC / cgs)
+        ck = (torch.empty(B, H, n, 64, 64, dtype=torch.float32, device=dev),
+              torch.empty(B, H, n, 1, 64, dtype=torch.float32, device=dev))
+        out = torch.empty_like(args[0])
+        final = (torch.empty_like(args[6]), torch.empty_like(args[7]))
+        ttt_linear_forward(*args, *ck, out, cgs, final_state=final)
+        ctx.save_for_backward(*args[:6], *ck)
+        ctx.cgs = cgs
+        ctx.eta_shape = last_eta.shape
+        return (out,) + final
+
+    @staticmethod
+    def backward(ctx, g_out, g_W1, g_b1):
+        from .ops import ttt_linear_backward
+        XQ, XK, XV, last_eta, gamma, beta, Wc, bc = ctx.saved_tensors
+        B, H, NC = XQ.shape[:3]
+        cgs, dev = ctx.cgs, XQ.device
+        f32 = torch.float32
+        g_W1 = torch.zeros(B, H, 64, 64, dtype=f32, device=dev) if g_W1 is None else g_W1.contiguous().to(f32)
+        g_b1 = torch.zeros(B, H, 1, 64, dtype=f32, device=dev) if g_b1 is None else g_b1.contiguous().to(f32)
+        g_out = torch.zeros_like(XQ) if g_out is None else g_out.contiguous().to(torch.bfloat16)
+        d_gamma = torch.empty(B, H, 1, 64, dtype=f32, device=dev)
+        d_beta = torch.empty(B, H, 1, 64, dtype=f32, device=dev)
+        d_W1 = torch.empty(B, H, 64, 64, dtype=f32, device=dev)
+        d_b1 = torch.empty(B, H, 1, 64, dtype=f32, device=dev)
+        d_eta = torch.empty(B, H, NC, 64, dtype=torch.bfloat16, device=dev)
+        dq, dk, dv = torch.empty_like(XQ), torch.empty_like(XQ), torch.empty_like(XQ)
+        eta4 = last_eta.reshape(B, H, NC, 64)
+        ttt_linear_backward(XQ, XK, XV, eta4, gamma, beta, Wc, bc, g_W1, g_b1, g_out, d_gamma, d_beta, d_W1, d_b1, d_eta,
+                            dq, dk, dv, cgs, scratch=_linear_scratch(B, H, cgs, dev))
+        return (dq, dk, dv, d_eta.reshape(ctx.eta_shape), d_gamma.sum(dim=0, keepdim=True),
+                d_beta.sum(dim=0, keepdim=True), d_W1, d_b1, None)
+
+
+def ttt_linear(XQ, XK, XV, last_eta, ttt_norm_weight, ttt_norm_bias, W1, b1, checkpoint_group_size=None):
+    """Differentiable TTT-Linear layer core.  Returns (XQW, (W1, b1) after the last mini-batch)."""
+    NC = XQ.shape[2]
+    if checkpoint_group_size is None:
+        checkpoint_group_size = max(1, int(math.sqrt(NC)))
+    r = TTTLinearFunction.apply(XQ, XK, XV, last_eta, ttt_norm_weight, ttt_norm_bias, W1, b1, checkpoint_group_size)
+    return r[0], tuple(r[1:])
