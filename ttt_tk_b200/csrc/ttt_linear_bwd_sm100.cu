@@ -25,6 +25,7 @@
 //   C    dK = gamma Bt - eta T1 + gZin W^T;  G^T += gZin^T K;  G_b += colsum gZin
 // All waits are bounded; on expiry the CTA reports through the status word, drains its own copies, frees its
 // tensor memory and returns.
+#include <cstdlib>
 #include <mutex>
 
 #include "ttt_cluster.cuh"
@@ -45,35 +46,42 @@ constexpr uint32_t SL_XL = 3 * TILE;
 constexpr uint32_t SL_SIG = 4 * TILE;          // fp32[64] 1/std of the fused LayerNorm, fp32[64] of the output one
 constexpr uint32_t SLOT_BYTES = 4 * TILE + 512;
 
-// shared memory: two stages of the per-mini-batch tiles
-constexpr uint32_t OFF_K = 0;
-constexpr uint32_t OFF_Q = OFF_K + 2 * TILE;
-constexpr uint32_t OFF_V = OFF_Q + 2 * TILE;
-constexpr uint32_t OFF_GO = OFF_V + 2 * TILE;
-constexpr uint32_t OFF_XL = OFF_GO + 2 * TILE;
-constexpr uint32_t OFF_XF = OFF_XL + 2 * TILE;
-constexpr uint32_t OFF_GZ = OFF_XF + 2 * TILE;
-constexpr uint32_t OFF_WP = OFF_GZ + 2 * TILE;      // pre-update W^T of the sweep's mini-batch
-constexpr uint32_t OFF_W = OFF_WP + 2 * TILE;       // bf16 operand copy of the current state W^T
-constexpr uint32_t OFF_A = OFF_W + TILE;            // U (recompute) / gZb (sweep)
-constexpr uint32_t OFF_G = OFF_A + TILE;            // bf16 operand copy of G^T
-constexpr uint32_t OFF_ZIN = OFF_G + TILE;          // gZin
-constexpr uint32_t OFF_DGA = OFF_ZIN + TILE;        // d_gamma addends of the second-order stage
-constexpr uint32_t OFF_ETA = OFF_DGA + TILE;        // bf16[2][64]
-constexpr uint32_t OFF_SIG = OFF_ETA + 256;         // fp32[2][128]: both 1/std vectors of the sweep's mini-batch
-constexpr uint32_t OFF_B = OFF_SIG + 1024;
-constexpr uint32_t OFF_GB = OFF_B + 256;
-constexpr uint32_t OFF_GAMMA = OFF_GB + 256;
-constexpr uint32_t OFF_BETA = OFF_GAMMA + 256;
-constexpr uint32_t OFF_DG = OFF_BETA + 256;
-constexpr uint32_t OFF_DB = OFF_DG + 256;
-constexpr uint32_t OFF_PART = OFF_DB + 256;         // fp32[3][4][64] column-sum partials
-constexpr uint32_t OFF_BAR = OFF_PART + 3072;
-constexpr uint32_t OFF_MISC = OFF_BAR + 64;
-constexpr uint32_t OFF_XCH = OFF_MISC + 64;         // fp32[2][64][8] row-sum exchange between warp pairs
-constexpr uint32_t SMEM_USED = OFF_XCH + 4096;
-constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;
-static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB per-CTA shared memory of sm_100");
+// Shared memory.  kStages = 2: every per-mini-batch tile has two stages, the next mini-batch's loads are issued a
+// whole step ahead, one CTA per SM (for launches with no more streams than SMs, where nothing else could hide
+// the load latency).  kStages = 1: single tiles, loads issued when the step before has ended, half the shared
+// memory and a 128-register budget: two CTAs per SM, which hide each other's latencies (for launches with more
+// streams than SMs).  Tiles that are never live at the same time share their place: the bf16 copy of G^T with the
+// state copy W^T (read as the post-update state by the first reverse step only, before G^T is first copied), gZin
+// with gZb / U, the d_gamma addends with dL/dOut.
+template <int kStages>
+struct Lay {
+  static constexpr uint32_t OFF_K = 0;
+  static constexpr uint32_t OFF_Q = OFF_K + kStages * TILE;
+  static constexpr uint32_t OFF_V = OFF_Q + kStages * TILE;
+  static constexpr uint32_t OFF_GO = OFF_V + kStages * TILE;
+  static constexpr uint32_t OFF_XL = OFF_GO + kStages * TILE;
+  static constexpr uint32_t OFF_XF = OFF_XL + kStages * TILE;
+  static constexpr uint32_t OFF_GZ = OFF_XF + kStages * TILE;
+  static constexpr uint32_t OFF_WP = OFF_GZ + kStages * TILE;   // pre-update W^T of the sweep's mini-batch (always two)
+  static constexpr uint32_t OFF_W = OFF_WP + 2 * TILE;          // bf16 operand copy of the current state W^T / of G^T
+  static constexpr uint32_t OFF_A = OFF_W + TILE;               // U (recompute) / gZb, then gZin (sweep)
+  static constexpr uint32_t OFF_ETA = OFF_A + TILE;             // bf16[kStages][64]
+  static constexpr uint32_t OFF_SIG = OFF_ETA + 256;            // fp32[kStages][128]: both 1/std vectors of the sweep's mini-batch
+  static constexpr uint32_t OFF_B = OFF_SIG + 1024;
+  static constexpr uint32_t OFF_GB = OFF_B + 256;
+  static constexpr uint32_t OFF_GAMMA = OFF_GB + 256;
+  static constexpr uint32_t OFF_BETA = OFF_GAMMA + 256;
+  static constexpr uint32_t OFF_DG = OFF_BETA + 256;
+  static constexpr uint32_t OFF_DB = OFF_DG + 256;
+  static constexpr uint32_t OFF_PART = OFF_DB + 256;            // fp32[3][4][64] column-sum partials
+  static constexpr uint32_t OFF_BAR = OFF_PART + 3072;
+  static constexpr uint32_t OFF_MISC = OFF_BAR + 64;
+  static constexpr uint32_t OFF_XCH = OFF_MISC + 64;            // fp32[2][64][8] row-sum exchange between warp pairs
+  static constexpr uint32_t SMEM_USED = OFF_XCH + 4096;
+  static constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;
+  static constexpr int kCtasPerSm = kStages == 1 ? 2 : 1;
+  static_assert(kCtasPerSm * (SMEM_BYTES + 1024) <= 233472, "exceeds the shared memory of an SM of sm_100");
+};
 
 constexpr int BAR_IN = 0;      // +stage: K, Q, V, eta (and dL/dOut in the sweep)
 constexpr int BAR_SC = 2;      // +stage: scratch tiles of the sweep
@@ -119,10 +127,18 @@ __device__ __forceinline__ void mma_mn_accumulate(uint32_t tmem_d, uint32_t a_sm
   for (int j = 0; j < 4; ++j) mma_issue_rt(tmem_d, a0 + j * (2048u >> 4), b0 + j * (2048u >> 4), idesc, 1u);
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+template <int kStages>
+__global__ void __launch_bounds__(kThreads, Lay<kStages>::kCtasPerSm)
 ttt_linear_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmGo,
                       const LinBwdParams p) {
+  using L = Lay<kStages>;
+  constexpr uint32_t OFF_K = L::OFF_K, OFF_Q = L::OFF_Q, OFF_V = L::OFF_V, OFF_GO = L::OFF_GO, OFF_XL = L::OFF_XL,
+                     OFF_XF = L::OFF_XF, OFF_GZ = L::OFF_GZ, OFF_WP = L::OFF_WP, OFF_W = L::OFF_W, OFF_A = L::OFF_A,
+                     OFF_ETA = L::OFF_ETA, OFF_SIG = L::OFF_SIG, OFF_B = L::OFF_B, OFF_GB = L::OFF_GB,
+                     OFF_GAMMA = L::OFF_GAMMA, OFF_BETA = L::OFF_BETA, OFF_DG = L::OFF_DG, OFF_DB = L::OFF_DB,
+                     OFF_PART = L::OFF_PART, OFF_BAR = L::OFF_BAR, OFF_MISC = L::OFF_MISC, OFF_XCH = L::OFF_XCH;
+  constexpr int kSt = kStages - 1;            // stage of mini-batch j: j & kSt
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -144,9 +160,8 @@ ttt_linear_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   auto tWP = [&](int s) { return smem + OFF_WP + s * TILE; };
   uint8_t* sW = smem + OFF_W;
   uint8_t* sA = smem + OFF_A;
-  uint8_t* sG = smem + OFF_G;
-  uint8_t* sZin = smem + OFF_ZIN;
-  uint8_t* sDga = smem + OFF_DGA;
+  uint8_t* sG = sW;        // see Lay
+  uint8_t* sZin = sA;
   __nv_bfloat16* sEta = reinterpret_cast<__nv_bfloat16*>(smem + OFF_ETA);
   float* sSig = reinterpret_cast<float*>(smem + OFF_SIG);
   float* sB = reinterpret_cast<float*>(smem + OFF_B);
@@ -263,7 +278,7 @@ ttt_linear_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
     auto issue_inputs = [&](int j, bool with_go) {   // kProd
       if (!with_go && i0 + j == p.drop_load && sid == 0) return;
-      const int s = j & 1;
+      const int s = j & kSt;
       const int row0 = static_cast<int>(tok_rows0 + (long)(i0 + j) * 64);
       mbar_expect_tx(&bars[BAR_IN + s], (with_go ? 4 : 3) * TILE + 128);
       tma_load_2d(tK(s), &tmK, &bars[BAR_IN + s], 0, row0);
@@ -276,11 +291,10 @@ ttt_linear_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     // The barrier is armed with all the bytes of the slot; the pre-update state copy follows separately
     // (issue_wp) when its tile, which holds the post-update state of the step before, is free.
     auto issue_wp = [&](int j) {                     // kProd
-      const int s = j & 1;
-      bulk_load_1d(tWP(s), slots + static_cast<long>(j) * SLOT_BYTES + SL_W, TILE, &bars[BAR_SC + s]);
+      bulk_load_1d(tWP(j & 1), slots + static_cast<long>(j) * SLOT_BYTES + SL_W, TILE, &bars[BAR_SC + (j & kSt)]);
     };
     auto issue_scratch = [&](int j) {                // kProd
-      const int s = j & 1;
+      const int s = j & kSt;
       const uint8_t* sl = slots + static_cast<long>(j) * SLOT_BYTES;
       mbar_expect_tx(&bars[BAR_SC + s], 4 * TILE + 512);
       bulk_load_1d(tXF(s), sl + SL_XF, TILE, &bars[BAR_SC + s]);
@@ -291,7 +305,7 @@ ttt_linear_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     };
     if (tid == kProd) {
       issue_inputs(0, false);
-      if (gsz > 1) issue_inputs(1, false);
+      if (kStages == 2 && gsz > 1) issue_inputs(1, false);
     }
     // ---- checkpoint -> tensor memory (fp32) + shared memory (bf16)
     {
@@ -306,7 +320,7 @@ ttt_linear_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
     // ================================================================== recompute the group
     for (int j = 0; j < gsz; ++j) {
-      const int s = j & 1;
+      const int s = j & kSt;
       uint8_t* sl = slots + static_cast<long>(j) * SLOT_BYTES;
       float* sig = reinterpret_cast<float*>(sl + SL_SIG);
       const __nv_bfloat16* eta = sEta + s * 64;
@@ -422,7 +436,7 @@ ttt_linear_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       if (tid == kProd && !aborted) {
         bulk_store_1d(sl + SL_XL, tXL(s), TILE);
         tma_commit_group();
-        if (j + 2 < gsz) issue_inputs(j + 2, false);   // this stage's K, Q, V have been read by everybody
+        if (j + kStages < gsz) issue_inputs(j + kStages, false);   // this stage's K, Q, V have been read by everybody
       }
       if (aborted) break;
     }
@@ -440,13 +454,14 @@ ttt_linear_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       issue_wp(gsz - 1);
     }
     for (int j = gsz - 1; j >= 0; --j) {
-      const int s = j & 1;
+      const int s = j & kSt;
       const int row0 = static_cast<int>(tok_rows0 + (long)(i0 + j) * 64);
+      uint8_t* sDga = tGo(s);      // see Lay
       // the state after this mini-batch's update: the next mini-batch's pre-update copy, loaded for the previous
       // step, or the group's last state
-      const uint8_t* Wpost = (j == gsz - 1) ? sW : tWP(s ^ 1);
-      // the other stage is free (the previous step has ended): the next step's tiles are requested now
-      if (tid == kProd && j > 0) {
+      const uint8_t* Wpost = (j == gsz - 1) ? sW : tWP((j & 1) ^ 1);
+      // two stages: the other stage is free (the previous step has ended), the next step's tiles are requested now
+      if (kStages == 2 && tid == kProd && j > 0) {
         issue_inputs(j - 1, true);
         issue_scratch(j - 1);
       }
@@ -511,7 +526,7 @@ ttt_linear_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         }
       }
       wait_mma();
-      if (tid == kProd && j > 0) issue_wp(j - 1);     // the post-update copy has been read: its tile takes the next step's
+      if (kStages == 2 && tid == kProd && j > 0) issue_wp(j - 1);   // the post-update copy has been read: its tile takes the next step's
       {
         float dq[16], go[16], w[16];
         tok_ld(tm, tmem + TM_A, dq);
@@ -621,7 +636,7 @@ ttt_linear_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       }
       publish();
       // ---- C: dK part = gZin W^T;  G^T += gZin^T K
-      TTT_ISSUE1(mma_hid64<true>(tmem + TM_A, smem_u32(sZin), smem_u32(tWP(s)), 0u);
+      TTT_ISSUE1(mma_hid64<true>(tmem + TM_A, smem_u32(sZin), smem_u32(tWP(j & 1)), 0u);
                  mma_mn_accumulate(tmem + TM_G, smem_u32(sZin), smem_u32(tK(s))))
       {
         part[tid] = colsum16(sZin);
@@ -644,6 +659,12 @@ ttt_linear_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       }
       aborted = publish_vote();
       if (aborted) break;
+      // one stage: everything of this step has been read, the next step's tiles are requested now
+      if (kStages == 1 && tid == kProd && j > 0) {
+        issue_inputs(j - 1, true);
+        issue_scratch(j - 1);
+        issue_wp(j - 1);
+      }
     }
   }
 #undef TTT_ISSUE1
@@ -721,14 +742,32 @@ int ttt_launch_linear_backward(const ttt_b200_linear_bwd_args* a, cudaStream_t s
   p.wait_limit_ns = limit_ns;
   static std::once_flag once[64];
   static cudaError_t attr_err[64];
+  static int sms[64];
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return ttt_set_error(TTT_B200_ERR_LAUNCH, "device index out of range");
   std::call_once(once[dev], [&] {
-    attr_err[dev] = cudaFuncSetAttribute(ttt_linear_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    attr_err[dev] = cudaFuncSetAttribute(ttt_linear_bwd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Lay<1>::SMEM_BYTES);
+    if (attr_err[dev] == cudaSuccess)
+      attr_err[dev] = cudaFuncSetAttribute(ttt_linear_bwd_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           Lay<2>::SMEM_BYTES);
+    sms[dev] = 148;
+    cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
   });
   if (attr_err[dev] != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(attr_err[dev]));
-  ttt_linear_bwd_kernel<<<dim3(a->B * a->H), dim3(kThreads), SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmGo, p);
+  // more streams than SMs: the form of which two CTAs fit on an SM; else the one that prefetches a step ahead
+  // (TTT_B200_LINEAR_BWD_STAGES = 1 or 2 overrides, for measurements)
+  static const int forced = [] {
+    const char* e = std::getenv("TTT_B200_LINEAR_BWD_STAGES");
+    return e ? std::atoi(e) : 0;
+  }();
+  const int streams = a->B * a->H;
+  const bool two_per_sm = forced == 1 || (forced != 2 && streams > sms[dev]);
+  if (two_per_sm)
+    ttt_linear_bwd_kernel<1><<<dim3(streams), dim3(kThreads), Lay<1>::SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmGo, p);
+  else
+    ttt_linear_bwd_kernel<2><<<dim3(streams), dim3(kThreads), Lay<2>::SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmGo, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return ttt_set_error(TTT_B200_ERR_LAUNCH, cudaGetErrorString(e));
   return TTT_B200_OK;
