@@ -20,6 +20,7 @@ CASES = [
     (64, 64, 256, 1, 1, 0, 1 | 256),   # same product, result read back as 16x256b fragments
     (64, 64, 64, 0, 0, 1, 2 | 256),
     (64, 64, 64, 0, 1, 0, 1 | 256),    # 64-row block of the cluster-sharded kernels: state update form at M = 64
+    (64, 8, 64, 1, 0, 0, 1),           # column sums of a token tile on the tensor pipe: A = the tile read MN-major, B = 8 rows of ones
 ]
 
 

@@ -99,7 +99,8 @@ struct Cfg {
   // CTA's own rows ([2][64])
   static constexpr uint32_t OFF_SIGAG = OFF_XCH + 4096;
   static constexpr uint32_t OFF_DGP = OFF_SIGAG + 256;
-  static constexpr uint32_t SMEM_USED = OFF_DGP + 512;
+  static constexpr uint32_t OFF_ONES = (OFF_DGP + 512 + 1023) & ~1023u;   // bf16[8][64] ones: B operand of the column sums
+  static constexpr uint32_t SMEM_USED = OFF_ONES + (NB == 1 ? 1024 : 0);
   static constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;
   static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB per-CTA shared memory of sm_100");
   static_assert(NUM_BARS * 8 <= 192, "barrier area");
@@ -109,8 +110,11 @@ struct Cfg {
   static constexpr uint32_t TM_S2 = 64 * NB;
   static constexpr uint32_t TM_A = 128 * NB;
   static constexpr uint32_t TM_B = 128 * NB + (NB > 1 ? 64 * NB : 64);
+  // four CTAs per stream only (tensor memory is full at two): 8 columns each for column sums taken by the tensor pipe
+  static constexpr bool kMmaColsum = NB == 1;
+  static constexpr uint32_t TM_CS = TM_B + 128;
   static constexpr uint32_t TM_COLS = 512;
-  static_assert(TM_B + 128 <= 512, "tensor memory");
+  static_assert(TM_B + 128 + (kMmaColsum ? 16 : 0) <= 512, "tensor memory");
 };
 
 struct BwdClParams {
@@ -211,6 +215,7 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     sDGp[tid] = 0.f;
     sDGp[64 + tid] = 0.f;
   }
+  if constexpr (C::kMmaColsum) reinterpret_cast<uint32_t*>(smem + C::OFF_ONES)[tid] = 0x3F803F80u;     // 256 x two bf16 ones
   float Gb1[NB][2];
 #pragma unroll
   for (int b = 0; b < NB; ++b) {
@@ -679,14 +684,28 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         bulk_store_1d(p.sc_gZ2 + slot * TILE, tGZ2, TILE);
         tma_commit_group();
       }
-      TTT_ISSUE4(HID_ONE(false, C::TM_A, bW2, tGZ2, 0u, 0),
-                 if (NB > 1) HID_ONE(false, C::TM_A, bW2, tGZ2, 0u, NB - 1),
-                 ,
-                 )
-      part[tid] = colsum16(tU2);
-      __syncthreads();
-      if (tid < 64) sB2[tid] += part_sum(0);
-      wait_mma();
+      if constexpr (C::kMmaColsum) {
+        // b2 += column sums of U2, taken by the tensor pipe in the same phase (the window of these small MMAs is
+        // too short to hide a pass over the tile by the warps)
+        TTT_ISSUE4(HID_ONE(false, C::TM_A, bW2, tGZ2, 0u, 0),
+                   mma_colsum(tmem + C::TM_CS, smem_u32(tU2), smem_u32(smem + C::OFF_ONES)),
+                   ,
+                   )
+        wait_mma();
+        if (warp < 4) {
+          const float cs = colsum_read(tmem + C::TM_CS, warp);
+          if (lane < 16) sB2[16 * warp + lane] += cs;
+        }
+      } else {
+        TTT_ISSUE4(HID_ONE(false, C::TM_A, bW2, tGZ2, 0u, 0),
+                   if (NB > 1) HID_ONE(false, C::TM_A, bW2, tGZ2, 0u, NB - 1),
+                   ,
+                   )
+        part[tid] = colsum16(tU2);
+        __syncthreads();
+        if (tid < 64) sB2[tid] += part_sum(0);
+        wait_mma();
+      }
       {
         float et[8];
         ld_eta_cols(eta, et);
@@ -1365,10 +1384,27 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         }
       }
       TTT_ISSUE4(HID_ONE(false, C::TM_B, big(ib1), t_q, 0u, 0); HID_ONE(false, C::TM_B, big(ib3), t_g, 1u, 0),
-                 if (NB > 1) { HID_ONE(false, C::TM_B, big(ib1), t_q, 0u, NB - 1); HID_ONE(false, C::TM_B, big(ib3), t_g, 1u, NB - 1); },
+                 if (NB > 1) { HID_ONE(false, C::TM_B, big(ib1), t_q, 0u, NB - 1); HID_ONE(false, C::TM_B, big(ib3), t_g, 1u, NB - 1); }
+                 else if (C::kMmaColsum) mma_colsum(tmem + C::TM_CS + 8, smem_u32(t_q), smem_u32(smem + C::OFF_ONES)),
                  HID_ONE(false, C::TM_A, big(ib1), t_gz2, 0u, 0),
                  if (NB > 1) HID_ONE(false, C::TM_A, big(ib1), t_gz2, 0u, NB - 1))
-      if constexpr (C::kRowSplit) {
+      if constexpr (C::kRowSplit && C::kMmaColsum) {
+        // the second-order stage's d_gamma / d_beta partials (this CTA's rows only: summed over the cluster at
+        // the end) are read out of the row-sum exchange area before the barrier below; the next epilogue, which
+        // uses that area again, comes after it.  The column sums of the gathered gZ2in tile (G_b2 stays
+        // replicated) come from the tensor pipe after the phase.
+        if (tid < 64) {
+          float a = 0.f, v = 0.f;
+#pragma unroll
+          for (int w = 0; w < 8; ++w) {
+            a += sXch[w * 64 + tid];
+            v += sXch[512 + w * 64 + tid];
+          }
+          sDGp[tid] += a;
+          sDGp[64 + tid] += v;
+        }
+        __syncthreads();
+      } else if constexpr (C::kRowSplit) {
         // the second-order stage's d_gamma / d_beta partials (this CTA's rows only: summed over the cluster at
         // the end) are read out of the row-sum exchange area before the barrier below; the next epilogue, which
         // uses that area again, comes after it
@@ -1399,6 +1435,12 @@ ttt_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         }
       }
       wait_mma();
+      if constexpr (C::kRowSplit && C::kMmaColsum) {
+        if (warp < 4) {
+          const float cs = colsum_read(tmem + C::TM_CS + 8, warp);
+          if (lane < 16) sGb2[16 * warp + lane] += cs;
+        }
+      }
       if (tid == kProd) {
         // the W2 state-gradient snapshot is consumed: X2 comes back into its buffer for G14; dV has left
         // its tile, the d_gamma addends and x_hat_fused are consumed: the next step's first tiles are

@@ -126,6 +126,26 @@ __device__ __forceinline__ void mma_tok_partial(uint32_t tmem_d, uint32_t x_smem
   for (int j = 1; j < 4 * nblk; ++j) mma_issue_rt(tmem_d, a0 + j * (2048u >> 4), b0 + j * (2048u >> 4), idesc, 1u);
 }
 
+// Column sums of a [64 tok][64] bf16 tile on the (otherwise idle) tensor pipe: D[64 feat x 8] = T^T * ones, the
+// tile read MN-major (row = token = contraction index) against 8 rows of bf16 ones (1 KB, 1024-byte aligned,
+// read K-major); every one of the 8 columns of D holds the sums.  Read back with colsum_read by warps 0..3.
+__device__ __forceinline__ void mma_colsum(uint32_t tmem_d, uint32_t tile_smem, uint32_t ones_smem) {
+  constexpr uint32_t idesc = umma_idesc_bf16(64, 8, true, false, false);
+  const uint32_t a0 = desc_lo(tile_smem, TILE);
+  const uint32_t b0 = desc_lo(ones_smem, 16);
+  mma_issue_rt(tmem_d, a0, b0, idesc, 0u);
+#pragma unroll
+  for (int j = 1; j < 4; ++j) mma_issue_rt(tmem_d, a0 + j * (2048u >> 4), b0 + j * (32u >> 4), idesc, 1u);
+}
+// Warp q of warps 0..3 (all 32 lanes call): lanes 0..15 return the sum of column 16 q + lane (row r of an M = 64
+// accumulator sits in tensor-memory lane r % 16 + 32 (r / 16)); the other lanes return garbage.
+__device__ __forceinline__ float colsum_read(uint32_t tmem_d, int warp) {
+  uint32_t v[8];
+  tmem_ld8(tmem_d + (static_cast<uint32_t>(warp * 32) << 16), v);
+  tmem_wait_ld();
+  return __uint_as_float(v[0]);
+}
+
 // the thread's 16 values of a token-major fragment, rounded to bf16, straight to a row-major [64][64] bf16
 // tile in global memory (`tile` = its first element): used by the CTA that owns the rows after a
 // reduce-scatter, where only a quarter or half of the tile is this CTA's to store

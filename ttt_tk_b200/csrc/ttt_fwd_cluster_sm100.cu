@@ -64,7 +64,8 @@ struct Cfg {
   static constexpr uint32_t OFF_MISC = OFF_BAR + 128;
   static constexpr uint32_t OFF_PART = OFF_MISC + 64;              // fp32[4][64] column-sum partials
   static constexpr uint32_t OFF_XCH = OFF_PART + 1024;             // fp32[2][64][8] row-sum exchange between warp pairs
-  static constexpr uint32_t SMEM_USED = OFF_XCH + 4096;
+  static constexpr uint32_t OFF_ONES = (OFF_XCH + 4096 + 1023) & ~1023u;   // bf16[8][64] ones: B operand of the column sums
+  static constexpr uint32_t SMEM_USED = OFF_ONES + 1024;
   static constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;         // slack for the 1024-byte alignment
   static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB per-CTA shared memory of sm_100");
   // tensor-memory columns (fp32), one 64-column M = 64 accumulator per block
@@ -72,7 +73,8 @@ struct Cfg {
   static constexpr uint32_t TM_W2 = 64 * NB;
   static constexpr uint32_t TM_A = 128 * NB;
   static constexpr uint32_t TM_Z = 192 * NB;
-  static constexpr uint32_t TM_COLS = kC == 2 ? 512 : 256;
+  static constexpr uint32_t TM_S = 192 * NB + 64;                  // 8 columns: column sums of U2
+  static constexpr uint32_t TM_COLS = 512;
 };
 
 struct FwdClParams {
@@ -162,6 +164,7 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     sBeta[tid] = p.beta[head * 64 + tid];
     sB2[tid] = p.b2[stream_id * 64 + tid];
   }
+  reinterpret_cast<uint32_t*>(smem + C::OFF_ONES)[tid] = 0x3F803F80u;     // 256 x two bf16 ones
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -525,21 +528,18 @@ ttt_fwd_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     }
 
     // ---- MMA3: R^T = W2 U2^T
+    // the column sums of U2 (the bf16 operand the W2 update sees) for b2 are taken by the tensor pipe in the same
+    // phase: the window of these small MMAs is too short to hide a pass over the tile by the warps
     TTT_ISSUE4(mma_hid64<false>(tmem + C::TM_A, smem_u32(sW2), smem_u32(sU2), 0u),
                if (NB > 1) mma_hid64<false>(tmem + C::TM_A + 64, smem_u32(sW2 + TILE), smem_u32(sU2), 0u),
-               ,
+               mma_colsum(tmem + C::TM_S, smem_u32(sU2), smem_u32(smem + C::OFF_ONES)),
                )
-    // b2 += column sums of U2 (the bf16 operand the W2 update sees), the same in every CTA of the cluster
-    {
-      const int q = tid >> 6, f = tid & 63;
-      float acc = 0.f;
-#pragma unroll 8
-      for (int t = q * 16; t < q * 16 + 16; ++t) acc += ld_elem(sU2, t, f);
-      sPart[tid] = acc;
-      __syncthreads();
-      if (tid < 64) sB2[tid] += (sPart[tid] + sPart[64 + tid]) + (sPart[128 + tid] + sPart[192 + tid]);
-    }
     wait_mma();
+    // b2 += column sums, the same in every CTA of the cluster (its next reader comes after the barrier below)
+    if (warp < 4) {
+      const float cs = colsum_read(tmem + C::TM_S, warp);
+      if (lane < 16) sB2[16 * warp + lane] += cs;
+    }
     // ---- EPI3: U1^T = R^T * G' (= -eta dl/dZ1), b1 += row sums
     {
       float ra[NB], rb[NB];

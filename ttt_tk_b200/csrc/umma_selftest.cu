@@ -127,7 +127,9 @@ extern "C" int ttt_b200_umma_selftest(const float* A, const float* B, float* D, 
   const int frag_ld = (repeat_and_mode >> 8) & 1;
   if (frag_ld && (M != 64 || (N % 32) != 0))
     return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "umma_selftest: fragment read-back needs M = 64 and N % 32 == 0");
-  if (!(M == 64 || M == 128) || N < 16 || N > 256 || (N % 16) || K < 64 || K > 256 || (K % 64) || repeat < 1)
+  // N: a multiple of 8 from 8 up with M = 64, a multiple of 16 from 16 up with M = 128
+  if (!(M == 64 || M == 128) || N < (M == 64 ? 8 : 16) || N > 256 || (N % (M == 64 ? 8 : 16)) || K < 64 || K > 256 ||
+      (K % 64) || repeat < 1)
     return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "umma_selftest: unsupported shape");
   if ((a_mn && M > 128) || N * K * 2 > 131072)
     return ttt_set_error(TTT_B200_ERR_BAD_ARGS, "umma_selftest: operand too large");
