@@ -154,3 +154,21 @@ def test_linear_autograd_function_against_oracle_autograd():
     for k, n in names.items():
         err = lin.rel_l2(leaves[k].grad.float().cpu(), ref[n])
         assert err <= TOL, f"{k}: rel-L2 {err:.3e}"
+
+
+def test_linear_pair_at_the_longest_configured_sequence():
+    """NC = 1024 mini-batches (the sequence length of the longest benchmark configuration) on two heads: the
+    errors do not grow past the gates over a thousand state updates."""
+    B, H, NC, cgs = 1, 2, 1024, 32
+    d = make(B, H, NC, seed=3)
+    f, ref = oracle(d, cgs)
+    t = {k: v.cuda() for k, v in d.items()}
+    n = lin.num_checkpoints(NC, cgs)
+    ck = [torch.empty(B, H, n, 64, 64, device="cuda"), torch.empty(B, H, n, 1, 64, device="cuda")]
+    out = torch.empty_like(t["XQ"])
+    fin = (torch.empty(B, H, 64, 64, device="cuda"), torch.empty(B, H, 1, 64, device="cuda"))
+    ttt_linear_forward(t["XQ"], t["XK"], t["XV"], t["last_eta"], t["ttt_norm_weight"], t["ttt_norm_bias"], t["W1"],
+                       t["b1"], *ck, out, cgs, final_state=fin)
+    assert lin.rel_l2(out.float().cpu(), f["Out"]) <= 1e-2
+    assert lin.rel_l2(fin[0].cpu(), f["W1_final"]) <= 1e-2 and lin.rel_l2(ck[0].cpu(), f["W1_checkpoints"]) <= 1e-2
+    check(run(d, cgs, ck=ck), ref)
