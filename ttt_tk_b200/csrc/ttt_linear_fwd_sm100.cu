@@ -43,11 +43,11 @@ constexpr uint32_t OFF_ETA = OFF_U + TILE;
 constexpr uint32_t OFF_B = OFF_ETA + kStages * 128;
 constexpr uint32_t OFF_GAMMA = OFF_B + 256;
 constexpr uint32_t OFF_BETA = OFF_GAMMA + 256;
-constexpr uint32_t OFF_PART = OFF_BETA + 256;           // fp32[4][64] column-sum partials
-constexpr uint32_t OFF_BAR = OFF_PART + 1024;
+constexpr uint32_t OFF_BAR = OFF_BETA + 256;
 constexpr uint32_t OFF_MISC = OFF_BAR + 64;
 constexpr uint32_t OFF_XCH = OFF_MISC + 64;             // fp32[2][64][8] row-sum exchange between warp pairs
-constexpr uint32_t SMEM_USED = OFF_XCH + 4096;
+constexpr uint32_t OFF_ONES = (OFF_XCH + 4096 + 1023) & ~1023u;   // bf16[8][64] ones: B operand of the column sums
+constexpr uint32_t SMEM_USED = OFF_ONES + 1024;
 constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;       // slack for the 1024-byte alignment
 static_assert(3 * (SMEM_BYTES + 1024) <= 233472, "three CTAs per SM");
 
@@ -98,7 +98,6 @@ ttt_linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   float* sB = reinterpret_cast<float*>(smem + OFF_B);
   float* sGamma = reinterpret_cast<float*>(smem + OFF_GAMMA);
   float* sBeta = reinterpret_cast<float*>(smem + OFF_BETA);
-  float* sPart = reinterpret_cast<float*>(smem + OFF_PART);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + OFF_BAR);   // [kStages]
   uint64_t* mma_bar = full + kStages;
   uint64_t* drain_bar = mma_bar + 1;        // abort path only
@@ -130,6 +129,7 @@ ttt_linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     sBeta[tid] = p.beta[head * 64 + tid];
     sB[tid] = p.b[stream_id * 64 + tid];
   }
+  reinterpret_cast<uint32_t*>(smem + OFF_ONES)[tid] = 0x3F803F80u;     // 256 x two bf16 ones
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -272,19 +272,15 @@ ttt_linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
     publish();
 
-    // ---- MMA2: W^T += U^T K
-    TTT_ISSUE1(mma_mn_accumulate(tmem + TM_W, smem_u32(sU), smem_u32(sK)))
-    // b += column sums of U (the bf16 operand the update sees), fp32 accumulate, while the MMA runs
-    {
-      const int q = tid >> 6, f = tid & 63;
-      float acc = 0.f;
-#pragma unroll 8
-      for (int t = q * 16; t < q * 16 + 16; ++t) acc += ld_elem(sU, t, f);
-      sPart[tid] = acc;
-      __syncthreads();
-      if (tid < 64) sB[tid] += (sPart[tid] + sPart[64 + tid]) + (sPart[128 + tid] + sPart[192 + tid]);
-    }
+    // ---- MMA2: W^T += U^T K; the column sums of U (the bf16 operand the update sees) for b are taken by the
+    // tensor pipe in the same phase, into the accumulator columns that are free between Z and Zb
+    TTT_ISSUE1(mma_mn_accumulate(tmem + TM_W, smem_u32(sU), smem_u32(sK));
+               mma_colsum(tmem + TM_Z, smem_u32(sU), smem_u32(smem + OFF_ONES)))
     wait_mma();
+    if (warp < 4) {
+      const float cs = colsum_read(tmem + TM_Z, warp);
+      if (lane < 16) sB[16 * warp + lane] += cs;       // its next reader comes after the barrier below
+    }
     // ---- EPI: refresh the bf16 operand copy of the state
     {
       float w[16];
