@@ -77,7 +77,8 @@ struct Lay {
   static constexpr uint32_t OFF_BAR = OFF_PART + 3072;
   static constexpr uint32_t OFF_MISC = OFF_BAR + 64;
   static constexpr uint32_t OFF_XCH = OFF_MISC + 64;            // fp32[2][64][8] row-sum exchange between warp pairs
-  static constexpr uint32_t SMEM_USED = OFF_XCH + 4096;
+  static constexpr uint32_t OFF_ONES = (OFF_XCH + 4096 + 1023) & ~1023u;   // bf16[8][64] ones: B operand of the column sums
+  static constexpr uint32_t SMEM_USED = OFF_ONES + 1024;
   static constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;
   static constexpr int kCtasPerSm = kStages == 1 ? 2 : 1;
   static_assert(kCtasPerSm * (SMEM_BYTES + 1024) <= 233472, "exceeds the shared memory of an SM of sm_100");
@@ -199,10 +200,21 @@ ttt_linear_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     sDG[tid] = 0.f;
     sDB[tid] = 0.f;
   }
+  reinterpret_cast<uint32_t*>(smem + L::OFF_ONES)[tid] = 0x3F803F80u;     // 256 x two bf16 ones
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
+  const uint32_t sOnes = smem_u32(smem + L::OFF_ONES);
+  // Column sums over the tokens of a bf16 tile are taken by the tensor pipe (mma_colsum: the MMA windows of
+  // these 64 x 64 products are too short to hide a pass over the tile by the warps), into accumulator columns
+  // that are free in that phase; warps 0..3 read them back after the phase (16 sums per warp).
+  auto add_colsum = [&](float* vec, uint32_t tm_cols, float sign) {
+    if (warp < 4) {
+      const float cs = colsum_read(tmem + tm_cols, warp);
+      if (lane < 16) vec[16 * warp + lane] += sign * cs;
+    }
+  };
 
   // ---- barrier bookkeeping: every thread waits on every barrier use, in program order
   uint32_t ph = 0;        // expected parity per barrier
@@ -394,12 +406,12 @@ ttt_linear_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       }
 
       // MMA2: W^T += U^T K;  b += column sums of U
-      TTT_ISSUE1(mma_mn_accumulate(tmem + TM_W, smem_u32(sA), smem_u32(tK(s))))
-      part[tid] = colsum16(sA);
+      TTT_ISSUE1(mma_mn_accumulate(tmem + TM_W, smem_u32(sA), smem_u32(tK(s)));
+                 mma_colsum(tmem + TM_B, smem_u32(sA), sOnes))
       if (tid == kProd) tma_wait_group_read<0>();   // the state copy has left shared memory: the refresh below may overwrite it
       __syncthreads();
-      if (tid < 64) sB[tid] += part_sum(0);
       wait_mma();
+      add_colsum(sB, TM_B, 1.f);
       {
         float w[16];
         tok_ld(tm, tmem + TM_W, w);
@@ -505,27 +517,22 @@ ttt_linear_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       publish();
       // ---- A: dQ part = gZb W+^T;  G^T += gZb^T Q
       TTT_ISSUE1(mma_hid64<true>(tmem + TM_A, smem_u32(sA), smem_u32(Wpost), 0u);
-                 mma_mn_accumulate(tmem + TM_G, smem_u32(sA), smem_u32(tQ(s))))
+                 mma_mn_accumulate(tmem + TM_G, smem_u32(sA), smem_u32(tQ(s)));
+                 mma_colsum(tmem + TM_B, smem_u32(sA), sOnes);
+                 mma_colsum(tmem + TM_B + 8, smem_u32(tGo(s)), sOnes))
       {
-        // column sums over the tokens: d_beta += sum go, d_gamma += sum go * x_ln, G_b += sum gZb
-        float a = 0.f, bsum = 0.f;
+        // column sums over the tokens: d_beta += sum go and G_b += sum gZb by the tensor pipe, d_gamma += sum
+        // go * x_ln (a product of two tiles) by the warps
+        float a = 0.f;
 #pragma unroll 8
-        for (int r = cs_q * 16; r < cs_q * 16 + 16; ++r) {
-          const float go = ld_elem(tGo(s), r, cs_f);
-          bsum += go;
-          a = fmaf(go, ld_elem(tXL(s), r, cs_f), a);
-        }
-        part[tid] = bsum;
-        part[256 + tid] = a;
-        part[512 + tid] = colsum16(sA);
+        for (int r = cs_q * 16; r < cs_q * 16 + 16; ++r) a = fmaf(ld_elem(tGo(s), r, cs_f), ld_elem(tXL(s), r, cs_f), a);
+        part[tid] = a;
         __syncthreads();
-        if (tid < 64) {
-          sDB[tid] += part_sum(0);
-          sDG[tid] += part_sum(1);
-          sGb[tid] += part_sum(2);
-        }
+        if (tid < 64) sDG[tid] += part_sum(0);
       }
       wait_mma();
+      add_colsum(sGb, TM_B, 1.f);
+      add_colsum(sDB, TM_B + 8, 1.f);
       if (kStages == 2 && tid == kProd && j > 0) issue_wp(j - 1);   // the post-update copy has been read: its tile takes the next step's
       {
         float dq[16], go[16], w[16];
@@ -636,20 +643,16 @@ ttt_linear_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       }
       publish();
       // ---- C: dK part = gZin W^T;  G^T += gZin^T K
+      // (T1 in the second accumulator has been read: its columns take the three column sums of this phase)
       TTT_ISSUE1(mma_hid64<true>(tmem + TM_A, smem_u32(sZin), smem_u32(tWP(j & 1)), 0u);
-                 mma_mn_accumulate(tmem + TM_G, smem_u32(sZin), smem_u32(tK(s))))
-      {
-        part[tid] = colsum16(sZin);
-        part[256 + tid] = colsum16(sDga);
-        part[512 + tid] = colsum16(tV(s));
-        __syncthreads();
-        if (tid < 64) {
-          sGb[tid] += part_sum(0);
-          sDG[tid] += part_sum(1);
-          sDB[tid] -= part_sum(2);
-        }
-      }
+                 mma_mn_accumulate(tmem + TM_G, smem_u32(sZin), smem_u32(tK(s)));
+                 mma_colsum(tmem + TM_B, smem_u32(sZin), sOnes);
+                 mma_colsum(tmem + TM_B + 8, smem_u32(sDga), sOnes);
+                 mma_colsum(tmem + TM_B + 16, smem_u32(tV(s)), sOnes))
       wait_mma();
+      add_colsum(sGb, TM_B, 1.f);
+      add_colsum(sDG, TM_B + 8, 1.f);
+      add_colsum(sDB, TM_B + 16, -1.f);
       {
         float acc[16];
         tok_ld(tm, tmem + TM_A, acc);
